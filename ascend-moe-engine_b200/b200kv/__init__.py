@@ -1,0 +1,329 @@
+"""ctypes binding of libb200kv.so, the C ABI of the B200 KV-cache path (include/b200kv.h).
+
+The binding is plumbing for tests, the benchmark and Python callers: it turns torch tensors into raw
+device pointers and the current CUDA stream into a handle, and calls the C entry points. There is no
+fallback: if the library is missing, importing this package raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_double, c_float, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200kv.so")
+
+LATENT_DIM = 512
+ROPE_DIM = 64
+ROW_DIM = LATENT_DIM + ROPE_DIM
+HEADS = 64
+
+OK = 0
+ERR_NULLPTR = 161001
+ERR_INVALID = 161002
+ERR_RUNTIME = 361001
+
+DEV_OK, DEV_BAD_SLOT, DEV_BAD_BLOCK, DEV_TIMEOUT, DEV_BAD_PLAN = 0, 1, 2, 3, 4
+
+DECODE_AUTO, DECODE_SIMT, DECODE_TCGEN05 = 0, 1, 2
+
+
+class B200KVError(RuntimeError):
+    def __init__(self, code: int, text: str):
+        super().__init__(f"b200kv error {code}: {text}")
+        self.code = code
+
+
+class PoolView(Structure):
+    _fields_ = [
+        ("latent", c_void_p),
+        ("rope", c_void_p),
+        ("latent_row_stride", c_int64),
+        ("rope_row_stride", c_int64),
+        ("pool_rows", c_int64),
+    ]
+
+
+class DecodeArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p),
+        ("q_seq_stride", c_int64),
+        ("q_head_stride", c_int64),
+        ("pool", PoolView),
+        ("block_table", c_void_p),
+        ("max_blocks", c_int64),
+        ("kv_len", c_void_p),
+        ("kv_begin", c_void_p),
+        ("batch", c_int32),
+        ("heads", c_int32),
+        ("block_size", c_int32),
+        ("scale", c_float),
+        ("out", c_void_p),
+        ("lse", c_void_p),
+        ("partial_o", c_void_p),
+        ("partial_m", c_void_p),
+        ("partial_l", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+        ("variant", c_int32),
+        ("max_ctas", c_int32),
+    ]
+
+
+class Reservation(Structure):
+    _fields_ = [
+        ("blocks_per_layer", c_int64),
+        ("total_blocks", c_int64),
+        ("latent_bytes", c_int64),
+        ("rope_bytes", c_int64),
+        ("block_table_bytes", c_int64),
+        ("slot_mapping_bytes", c_int64),
+    ]
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python ascend-moe-engine_b200/build.py` "
+            "(there is no CPU or eager fallback for this path)"
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.b200kv_last_error.restype = c_char_p
+    lib.b200kv_abi_version.restype = c_int32
+    lib.b200kv_append.restype = c_int32
+    lib.b200kv_append.argtypes = [POINTER(PoolView), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                  c_void_p, c_void_p]
+    lib.b200kv_gather.restype = c_int32
+    lib.b200kv_gather.argtypes = [POINTER(PoolView), c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
+                                  c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p]
+    lib.b200kv_mla_decode_workspace_bytes.restype = c_size_t
+    lib.b200kv_mla_decode_workspace_bytes.argtypes = [c_int32, c_int32, c_int32]
+    lib.b200kv_mla_decode.restype = c_int32
+    lib.b200kv_mla_decode.argtypes = [POINTER(DecodeArgs), c_void_p, c_void_p]
+    lib.b200kv_lse_merge.restype = c_int32
+    lib.b200kv_lse_merge.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p]
+    lib.b200kv_fill_normal_bf16.restype = c_int32
+    lib.b200kv_fill_normal_bf16.argtypes = [c_void_p, c_int64, c_uint64, c_uint64, c_uint64, c_double, c_void_p]
+    lib.b200kv_block_pool_create.restype = c_void_p
+    lib.b200kv_block_pool_create.argtypes = [c_int32, c_int32, c_int32, c_int32, c_void_p]
+    lib.b200kv_block_pool_destroy.argtypes = [c_void_p]
+    lib.b200kv_block_pool_destroy.restype = None
+    for name in ("admit", "release"):
+        fn = getattr(lib, f"b200kv_block_pool_{name}")
+        fn.restype = c_int32
+        fn.argtypes = [c_void_p, c_int32]
+    lib.b200kv_block_pool_grow.restype = c_int32
+    lib.b200kv_block_pool_grow.argtypes = [c_void_p, c_int32, c_int32, c_void_p]
+    lib.b200kv_block_pool_free_count.restype = c_int32
+    lib.b200kv_block_pool_free_count.argtypes = [c_void_p]
+    lib.b200kv_block_pool_seq_len.restype = c_int32
+    lib.b200kv_block_pool_seq_len.argtypes = [c_void_p, c_int32]
+    lib.b200kv_block_pool_table.restype = POINTER(c_int32)
+    lib.b200kv_block_pool_table.argtypes = [c_void_p]
+    lib.b200kv_block_pool_lens.restype = POINTER(c_int32)
+    lib.b200kv_block_pool_lens.argtypes = [c_void_p]
+    lib.b200kv_block_pool_export_free.restype = c_int32
+    lib.b200kv_block_pool_export_free.argtypes = [c_void_p, c_void_p, c_int32]
+    lib.b200kv_block_pool_validate.restype = c_int32
+    lib.b200kv_block_pool_validate.argtypes = [c_void_p]
+    lib.b200kv_plan_reservation.restype = c_int32
+    lib.b200kv_plan_reservation.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int64, POINTER(Reservation)]
+    lib.b200kv_utilisation.restype = c_double
+    lib.b200kv_utilisation.argtypes = [c_int64, c_int64, c_int64]
+    return lib
+
+
+lib = _load()
+
+
+def last_error() -> str:
+    return (lib.b200kv_last_error() or b"").decode()
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise B200KVError(code, last_error())
+
+
+# ---------------------------------------------------------------------------------------------------
+# Device operations on torch tensors
+# ---------------------------------------------------------------------------------------------------
+def _stream_handle(stream=None) -> int:
+    import torch
+
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return int(s.cuda_stream)
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else int(t.data_ptr())
+
+
+def pool_view(latent, rope=None) -> PoolView:
+    """A layer's pool as a view. `latent`: bf16 [rows, 576] (fused row: rope is columns 512..575) when
+    `rope` is None, else bf16 [rows, >=512] with `rope` bf16 [rows, >=64] (the reference's two caches)."""
+    assert latent.dim() == 2 and latent.stride(1) == 1
+    view = PoolView()
+    view.latent = _ptr(latent)
+    view.latent_row_stride = latent.stride(0)
+    view.pool_rows = latent.shape[0]
+    if rope is None:
+        assert latent.shape[1] == ROW_DIM
+        view.rope = _ptr(latent) + LATENT_DIM * 2
+        view.rope_row_stride = latent.stride(0)
+    else:
+        assert rope.dim() == 2 and rope.stride(1) == 1 and rope.shape[0] == latent.shape[0]
+        view.rope = _ptr(rope)
+        view.rope_row_stride = rope.stride(0)
+    return view
+
+
+def new_status(device="cuda"):
+    import torch
+
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def append(view: PoolView, latent_src, rope_src, slot_mapping, status=None, stream=None) -> None:
+    """latent_src bf16 [T, >=512] and rope_src bf16 [T, >=64] (row strides taken from the tensors),
+    slot_mapping int32 [T] on the device."""
+    n = int(slot_mapping.shape[0])
+    check(lib.b200kv_append(ctypes.byref(view), _ptr(latent_src), latent_src.stride(0) if n else LATENT_DIM,
+                            _ptr(rope_src), rope_src.stride(0) if n else ROPE_DIM, _ptr(slot_mapping), n,
+                            _stream_handle(stream), _ptr(status)))
+
+
+def gather(view: PoolView, block_table, kv_len, block_size: int, out_latent, out_rope, out_row_offsets,
+           total_rows: int, status=None, stream=None) -> None:
+    batch = int(kv_len.shape[0])
+    check(lib.b200kv_gather(ctypes.byref(view), _ptr(block_table), block_table.stride(0) if batch else 1,
+                            _ptr(kv_len), batch, block_size, _ptr(out_latent),
+                            out_latent.stride(0) if total_rows else LATENT_DIM, _ptr(out_rope),
+                            out_rope.stride(0) if total_rows else ROPE_DIM, _ptr(out_row_offsets), total_rows,
+                            _stream_handle(stream), _ptr(status)))
+
+
+def decode_workspace_bytes(batch: int, heads: int = HEADS, max_ctas: int = 0) -> int:
+    return int(lib.b200kv_mla_decode_workspace_bytes(batch, heads, max_ctas))
+
+
+def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: float, out=None, lse=None,
+               kv_begin=None, partial=None, workspace=None, variant: int = DECODE_AUTO, max_ctas: int = 0,
+               status=None, stream=None) -> None:
+    """q bf16 [B, H, 576]; out bf16 [B, H, 512]; lse fp32 [B, H]; partial = (o fp32 [B,H,512], m, l)."""
+    args = DecodeArgs()
+    args.q = _ptr(q)
+    args.q_seq_stride = q.stride(0)
+    args.q_head_stride = q.stride(1)
+    args.pool = view
+    args.block_table = _ptr(block_table)
+    args.max_blocks = block_table.stride(0)
+    args.kv_len = _ptr(kv_len)
+    args.kv_begin = _ptr(kv_begin)
+    args.batch = q.shape[0]
+    args.heads = q.shape[1]
+    args.block_size = block_size
+    args.scale = scale
+    args.out = _ptr(out)
+    args.lse = _ptr(lse)
+    if partial is not None:
+        args.partial_o, args.partial_m, args.partial_l = (_ptr(t) for t in partial)
+    args.workspace = _ptr(workspace)
+    args.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    args.variant = variant
+    args.max_ctas = max_ctas
+    check(lib.b200kv_mla_decode(ctypes.byref(args), _stream_handle(stream), _ptr(status)))
+
+
+def lse_merge(partial_o, partial_m, partial_l, out, lse=None, stream=None) -> None:
+    """partial_o fp32 [P, rows, 512], partial_m / partial_l fp32 [P, rows] -> out bf16 [rows, 512]."""
+    n_parts, rows = int(partial_m.shape[0]), int(partial_m.shape[1])
+    check(lib.b200kv_lse_merge(_ptr(partial_o), _ptr(partial_m), _ptr(partial_l), n_parts, rows, _ptr(out),
+                               _ptr(lse), _stream_handle(stream)))
+
+
+def fill_normal_bf16(dst, seed: int, stream_id: int, first_element: int = 0, scale: float = 1.0, stream=None) -> None:
+    check(lib.b200kv_fill_normal_bf16(_ptr(dst), dst.numel(), seed, stream_id, first_element, scale,
+                                      _stream_handle(stream)))
+
+
+# ---------------------------------------------------------------------------------------------------
+# Host bookkeeping
+# ---------------------------------------------------------------------------------------------------
+class BlockPool:
+    """KV block allocator: FIFO free list, per-sequence block tables (include/b200kv.h)."""
+
+    def __init__(self, num_blocks: int, block_size: int, max_seqs: int, max_blocks_per_seq: int, free_order=None):
+        import numpy as np
+
+        order = None
+        if free_order is not None:
+            order = np.ascontiguousarray(free_order, dtype=np.int32)
+            assert order.shape == (num_blocks,)
+        self._h = lib.b200kv_block_pool_create(num_blocks, block_size, max_seqs, max_blocks_per_seq,
+                                               None if order is None else order.ctypes.data)
+        if not self._h:
+            raise B200KVError(ERR_INVALID, last_error())
+        self.num_blocks, self.block_size = num_blocks, block_size
+        self.max_seqs, self.max_blocks_per_seq = max_seqs, max_blocks_per_seq
+
+    def close(self) -> None:
+        if self._h:
+            lib.b200kv_block_pool_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def admit(self, seq: int) -> None:
+        check(lib.b200kv_block_pool_admit(self._h, seq))
+
+    def grow(self, seq: int, n_tokens: int):
+        import numpy as np
+
+        slots = np.empty(max(n_tokens, 1), dtype=np.int32)
+        check(lib.b200kv_block_pool_grow(self._h, seq, n_tokens, slots.ctypes.data))
+        return slots[:n_tokens]
+
+    def release(self, seq: int) -> None:
+        check(lib.b200kv_block_pool_release(self._h, seq))
+
+    def validate(self) -> None:
+        check(lib.b200kv_block_pool_validate(self._h))
+
+    @property
+    def free_count(self) -> int:
+        return int(lib.b200kv_block_pool_free_count(self._h))
+
+    def seq_len(self, seq: int) -> int:
+        return int(lib.b200kv_block_pool_seq_len(self._h, seq))
+
+    def table(self):
+        import numpy as np
+
+        ptr = lib.b200kv_block_pool_table(self._h)
+        return np.ctypeslib.as_array(ptr, shape=(self.max_seqs, self.max_blocks_per_seq)).copy()
+
+    def lens(self):
+        import numpy as np
+
+        ptr = lib.b200kv_block_pool_lens(self._h)
+        return np.ctypeslib.as_array(ptr, shape=(self.max_seqs,)).copy()
+
+    def free_list(self):
+        import numpy as np
+
+        out = np.empty(self.num_blocks, dtype=np.int32)
+        n = lib.b200kv_block_pool_export_free(self._h, out.ctypes.data, self.num_blocks)
+        return out[:n].copy()
+
+
+def plan_reservation(max_context: int, block_size: int, layers: int = 43, max_seqs: int = 1,
+                     tokens_per_step: int = 1) -> Reservation:
+    out = Reservation()
+    check(lib.b200kv_plan_reservation(max_context, block_size, layers, max_seqs, tokens_per_step, ctypes.byref(out)))
+    return out
+
+
+def utilisation(active_tokens: int, blocks_per_layer: int, block_size: int) -> float:
+    return float(lib.b200kv_utilisation(active_tokens, blocks_per_layer, block_size))

@@ -1,0 +1,55 @@
+// Shared device/host helpers for the KV-cache path kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b200kv.h"
+
+namespace b200kv {
+
+// Host: per-thread error text behind b200kv_last_error().
+void SetLastError(const char* fmt, ...);
+int32_t CheckCuda(cudaError_t err, const char* what);
+
+// Device: record the first error in the caller's status word and carry on. Kernels never trap:
+// the failing access is skipped and the host reads the word after its next synchronisation.
+__device__ __forceinline__ void RecordError(int32_t* status, int32_t code, int32_t d0, int32_t d1, int32_t d2 = 0) {
+  if (status == nullptr) return;
+  if (atomicCAS(status, 0, code) == 0) {
+    status[1] = d0;
+    status[2] = d1;
+    status[3] = d2;
+  }
+}
+
+__device__ __forceinline__ int4 LoadStream16(const void* p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void StoreStream16(void* p, int4 v) {
+  asm volatile("st.global.L1::no_allocate.v4.s32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+inline int32_t CurrentDeviceSmCount() {
+  static thread_local int cached_device = -1;
+  static thread_local int cached_sms = 0;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return 148;
+  if (device != cached_device) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+    cached_device = device;
+    cached_sms = sms;
+  }
+  return cached_sms;
+}
+
+}  // namespace b200kv

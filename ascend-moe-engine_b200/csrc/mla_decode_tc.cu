@@ -1,0 +1,791 @@
+// Split-KV absorbed-MLA decode attention on tcgen05 tensor cores (sm_100a), 64 heads x (512+64).
+//
+// Work partition. A sequence of L tokens is ceil(L/32) tiles. The tiles of all sequences form one flat
+// list; CTA c of G takes the contiguous range [c*T/G, (c+1)*T/G). A CTA therefore walks a few
+// "segments" (a tile range inside one sequence). A segment that covers its whole sequence writes the
+// result directly; otherwise it writes an un-normalised partial (m, l, O) to the workspace and the
+// finalize kernel merges the parts with a log-sum-exp reduction. Only the first and the last segment
+// of a CTA can be partial, so the workspace holds two partial slots per CTA.
+//
+// Per tile of 32 tokens (one KV stage of 36,864 bytes, TMA-loaded, 128-byte swizzled):
+//   S[64 heads x 32 tok]  = Q[64 x 576] . K_tile^T            36 MMAs M=64  N=32 K=16 (K-major A, B)
+//   P = exp2(S*scale*log2e - m)  (softmax warps, fp32 -> bf16, written to shared memory)
+//   O^T[512 x 64 heads]  += V_tile^T[512 x 32] . P^T[32 x 64]   8 MMAs M=128 N=64 K=16 (MN-major A)
+// V is the first 512 columns of the same shared-memory tile that served as K: the tile is read from
+// HBM once. O^T lives in TMEM (4 accumulators of 128 lanes x 64 columns), S double-buffered beside it.
+//
+// Warp roles: warps 0-3 softmax + epilogue (TMEM lanes 32w..32w+31), warp 4 TMA producer, warp 5 MMA
+// issuer and TMEM owner. QK of tile i+1 is issued before PV of tile i so the tensor pipe works while
+// the softmax warps handle tile i. Four KV stages keep three tile loads in flight per SM.
+//
+// Every wait is bounded: when a wait runs out the kernel records B200KV_DEV_TIMEOUT in the status
+// word, raises a CTA-wide abort flag, waits (bounded) for its own TMA loads, frees TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200kv {
+
+namespace {
+
+constexpr int kHeads = 64;
+constexpr int kLatent = B200KV_LATENT_DIM;
+constexpr int kRope = B200KV_ROPE_DIM;
+constexpr int kTile = 32;      // tokens per tile / KV stage
+constexpr int kStages = 4;
+constexpr int kSlabBytes = kTile * 128;                 // one 64-column slab of a tile: 32 rows x 128 B
+constexpr int kStageBytes = 9 * kSlabBytes;             // 36,864
+constexpr int kQSlabBytes = kHeads * 128;               // 8,192
+constexpr int kQBytes = 9 * kQSlabBytes;                // 73,728
+constexpr int kPBytes = kHeads * 128;                   // 8,192 (64 rows x 128 B, first 64 B of a row used)
+constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemColS = 256;                     // S buffers at columns 256 and 288
+constexpr float kRescaleThreshold = 8.0f;               // log2 units: rescale O only when max grows by > 2^8
+
+// Shared memory carve-up (offsets from a 1024-byte aligned base).
+constexpr int kOffQ = 0;
+constexpr int kOffKv = kOffQ + kQBytes;
+constexpr int kOffP = kOffKv + kStages * kStageBytes;
+constexpr int kOffMisc = kOffP + kPBytes;
+constexpr int kMiscBytes = 1024;
+constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + slack for the manual 1024-byte alignment
+static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+
+struct Misc {
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t s_full[2];
+  uint64_t s_empty[2];
+  uint64_t p_full;
+  uint64_t p_empty;
+  uint64_t q_full;
+  uint64_t o_full;
+  uint64_t o_empty;
+  uint64_t drain;
+  uint32_t tmem_base;
+  int32_t abort_flag;
+  int32_t start_seq;
+  int32_t start_tile;
+  int32_t n_tiles;
+  float factor[kHeads];
+  float inv_l[kHeads];
+};
+static_assert(sizeof(Misc) <= kMiscBytes, "Misc does not fit its reservation");
+
+struct TcParams {
+  const __nv_bfloat16* q;
+  int64_t q_seq_stride;
+  int64_t q_head_stride;
+  const int32_t* block_table;
+  int64_t max_blocks;
+  const int32_t* kv_len;
+  const int32_t* kv_begin;
+  int64_t pool_rows;
+  int32_t batch;
+  int32_t block_size;
+  float scale_log2;  // scale * log2(e)
+  __nv_bfloat16* out;
+  float* lse;
+  float* user_o;  // caller's partial buffers (shard mode) or null
+  float* user_m;
+  float* user_l;
+  float* ws_o;  // [G*2][64][512]
+  float* ws_m;  // [G*2][64]
+  float* ws_l;
+  int32_t* status;
+};
+
+__device__ __forceinline__ int TilesOf(int len) { return (len + kTile - 1) / kTile; }
+
+// Bounded mbarrier wait. Returns false when the CTA is aborting or this wait ran out (about one
+// second), after recording where.
+__device__ __noinline__ bool BoundedWait(uint32_t bar, uint32_t parity, Misc* misc, int32_t* status, int site) {
+  uint64_t start = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (ptx::MbarTryWait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (*reinterpret_cast<volatile int32_t*>(&misc->abort_flag)) return false;
+      const uint64_t now = ptx::GlobalTimerNs();
+      if (start == 0) start = now;
+      if (now - start > 1000000000ull) {
+        *reinterpret_cast<volatile int32_t*>(&misc->abort_flag) = 1;
+        RecordError(status, B200KV_DEV_TIMEOUT, site, static_cast<int32_t>(blockIdx.x), static_cast<int32_t>(parity));
+        return false;
+      }
+    }
+  }
+}
+
+// Walks the segments of this CTA's tile range. All roles run the same iterator.
+struct SegmentWalker {
+  const int32_t* kv_len;
+  int batch;
+  int seq;
+  int tile;       // first tile of the segment inside `seq`
+  int remaining;  // tiles left for this CTA
+  __device__ SegmentWalker(const int32_t* lens, int batch_, int seq_, int tile_, int remaining_)
+      : kv_len(lens), batch(batch_), seq(seq_), tile(tile_), remaining(remaining_) {}
+  // Fills the current segment; returns false when the CTA's range is exhausted.
+  __device__ bool Next(int* seq_out, int* tile_lo, int* tile_hi, int* seq_tiles, int* seq_len) {
+    while (remaining > 0 && seq < batch) {
+      const int len = kv_len[seq];
+      const int tiles = TilesOf(len);
+      if (tile < tiles) {
+        const int take = min(remaining, tiles - tile);
+        *seq_out = seq;
+        *tile_lo = tile;
+        *tile_hi = tile + take;
+        *seq_tiles = tiles;
+        *seq_len = len;
+        remaining -= take;
+        tile += take;
+        if (tile == tiles) {
+          tile = 0;
+          ++seq;
+        }
+        return true;
+      }
+      tile = 0;
+      ++seq;
+    }
+    return false;
+  }
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+    MlaDecodeTcKernel(const __grid_constant__ CUtensorMap latent_map, const __grid_constant__ CUtensorMap rope_map,
+                      TcParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = ptx::SmemAddr(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* smem = smem_dyn + (base - raw);
+  Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
+  const uint32_t q_addr = base + kOffQ;
+  const uint32_t kv_addr = base + kOffKv;
+  const uint32_t p_addr = base + kOffP;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int cta = blockIdx.x;
+  const int n_ctas = gridDim.x;
+
+  auto bar = [&](const uint64_t* b) { return ptx::SmemAddr(b); };
+
+  // ---- setup ----------------------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::MbarInit(bar(&misc->kv_full[s]), 1);
+      ptx::MbarInit(bar(&misc->kv_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::MbarInit(bar(&misc->s_full[s]), 1);
+      ptx::MbarInit(bar(&misc->s_empty[s]), kSoftmaxThreads);
+    }
+    ptx::MbarInit(bar(&misc->p_full), kSoftmaxThreads);
+    ptx::MbarInit(bar(&misc->p_empty), 1);
+    ptx::MbarInit(bar(&misc->q_full), kSoftmaxThreads);
+    ptx::MbarInit(bar(&misc->o_full), 1);
+    ptx::MbarInit(bar(&misc->o_empty), kSoftmaxThreads);
+    ptx::MbarInit(bar(&misc->drain), 1);
+    misc->abort_flag = 0;
+    ptx::FenceBarrierInit();
+  }
+  if (warp == 0) {
+    // This CTA's slice of the flat tile list: total, then the sequence holding the first tile.
+    long long total = 0;
+    for (int b = lane; b < p.batch; b += 32) total += TilesOf(p.kv_len[b]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    const long long lo = total * cta / n_ctas;
+    const long long hi = total * (cta + 1) / n_ctas;
+    int start_seq = p.batch, start_tile = 0;
+    long long before = 0;
+    for (int b0 = 0; b0 < p.batch && start_seq == p.batch; b0 += 32) {
+      const int b = b0 + lane;
+      const long long mine = b < p.batch ? TilesOf(p.kv_len[b]) : 0;
+      long long incl = mine;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const long long up = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += up;
+      }
+      const bool hit = (before + incl > lo) && mine > 0;
+      const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+      if (ballot != 0 && hi > lo) {
+        const int src = __ffs(ballot) - 1;
+        const long long incl_src = __shfl_sync(0xffffffffu, incl, src);
+        const long long mine_src = __shfl_sync(0xffffffffu, mine, src);
+        start_seq = b0 + src;
+        start_tile = static_cast<int>(lo - (before + incl_src - mine_src));
+      }
+      before += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      misc->start_seq = start_seq;
+      misc->start_tile = start_tile;
+      misc->n_tiles = static_cast<int>(hi - lo);
+    }
+  }
+  if (warp == 5) {
+    ptx::TmemAlloc(ptx::SmemAddr(&misc->tmem_base), kTmemCols);
+    ptx::TmemRelinquish();
+  }
+  if (warp == 4 && lane == 0) {
+    ptx::PrefetchTensorMap(&latent_map);
+    ptx::PrefetchTensorMap(&rope_map);
+  }
+  ptx::TcFenceBeforeSync();
+  __syncthreads();
+  ptx::TcFenceAfterSync();
+
+  const uint32_t tmem = misc->tmem_base;
+  const int start_seq = misc->start_seq;
+  const int start_tile = misc->start_tile;
+  const int my_tiles = misc->n_tiles;
+
+  if (warp == 4) {
+    // ======================= TMA producer =======================================================
+    if (lane == 0) {
+      SegmentWalker walk(p.kv_len, p.batch, start_seq, start_tile, my_tiles);
+      int seq, t_lo, t_hi, seq_tiles, seq_len;
+      int g = 0;  // tiles issued
+      bool ok = true;
+      while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
+        const int begin = p.kv_begin ? p.kv_begin[seq] : 0;
+        for (int t = t_lo; t < t_hi; ++t, ++g) {
+          const int stage = g % kStages;
+          if (g >= kStages) {
+            ok = BoundedWait(bar(&misc->kv_empty[stage]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
+            if (!ok) break;
+          }
+          const int tok = begin + t * kTile;
+          const int64_t table_col = tok / p.block_size;
+          const int64_t block =
+              table_col < p.max_blocks ? p.block_table[static_cast<int64_t>(seq) * p.max_blocks + table_col] : -1;
+          int64_t row = block * p.block_size + tok % p.block_size;
+          if (block < 0 || row + kTile > p.pool_rows) {
+            RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, tok / p.block_size, static_cast<int32_t>(block));
+            row = 0;  // keep the pipeline moving on addressable memory; the status word tells the host
+          }
+          const uint32_t full = bar(&misc->kv_full[stage]);
+          const uint32_t dst = kv_addr + stage * kStageBytes;
+          ptx::MbarArriveExpectTx(full, kStageBytes);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            ptx::TmaLoad2D(dst + c * kSlabBytes, &latent_map, 64 * c, static_cast<int32_t>(row), full);
+          }
+          ptx::TmaLoad2D(dst + 8 * kSlabBytes, &rope_map, 0, static_cast<int32_t>(row), full);
+        }
+      }
+      if (!ok) {
+        // Aborting: let the loads this thread issued land before the CTA exits. A stage whose load
+        // was issued at count i (the last one for that stage) completes phase (i / kStages) & 1.
+        for (int s = 0; s < kStages; ++s) {
+          int last = -1;
+          for (int i = g - 1; i >= 0 && i >= g - kStages; --i) {
+            if (i % kStages == s) {
+              last = i;
+              break;
+            }
+          }
+          if (last < 0) continue;
+          const uint32_t full = bar(&misc->kv_full[s]);
+          const uint32_t parity = (last / kStages) & 1;
+          const uint64_t t0 = ptx::GlobalTimerNs();
+          while (!ptx::MbarTryWait(full, parity)) {
+            if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ======================= MMA issuer ==========================================================
+    if (lane == 0) {
+      constexpr uint32_t kIdescQk = ptx::InstrDescBf16(64, kTile, 0, 0);
+      constexpr uint32_t kIdescPv = ptx::InstrDescBf16(128, kHeads, 1, 0);
+      SegmentWalker walk(p.kv_len, p.batch, start_seq, start_tile, my_tiles);
+      int seq, t_lo, t_hi, seq_tiles, seq_len;
+      int g = 0;    // tiles whose QK has been issued
+      int seg = 0;  // segment counter
+      bool ok = true;
+
+      auto issue_pv = [&](int g_tile, bool first_of_segment) -> bool {
+        // P of tile g_tile is ready when the softmax warps have arrived g_tile+1 times on p_full.
+        if (!BoundedWait(bar(&misc->p_full), g_tile & 1, misc, p.status, 21)) return false;
+        ptx::TcFenceAfterSync();
+        const uint32_t stage_addr = kv_addr + (g_tile % kStages) * kStageBytes;
+#pragma unroll
+        for (int ks = 0; ks < kTile / 16; ++ks) {
+#pragma unroll
+          for (int tm = 0; tm < 4; ++tm) {
+            const uint64_t a = ptx::SmemDescSw128(stage_addr + 2 * tm * kSlabBytes + ks * 2048, kSlabBytes, 1024);
+            const uint64_t b = ptx::SmemDescSw128(p_addr + ks * 32, 16, 1024);
+            ptx::MmaF16SS(tmem + 64 * tm, a, b, kIdescPv, (first_of_segment && ks == 0) ? 0u : 1u);
+          }
+        }
+        ptx::TcCommit(bar(&misc->kv_empty[g_tile % kStages]));
+        ptx::TcCommit(bar(&misc->p_empty));
+        return true;
+      };
+
+      while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
+        ok = BoundedWait(bar(&misc->q_full), seg & 1, misc, p.status, 22);
+        if (!ok) break;
+        if (seg > 0) {
+          // The previous segment's accumulators must have been drained by the epilogue.
+          ok = BoundedWait(bar(&misc->o_empty), (seg - 1) & 1, misc, p.status, 23);
+          if (!ok) break;
+        }
+        const int n = t_hi - t_lo;
+        for (int i = 0; i < n && ok; ++i, ++g) {
+          const int stage = g % kStages;
+          const int buf = g & 1;
+          ok = BoundedWait(bar(&misc->kv_full[stage]), (g / kStages) & 1, misc, p.status, 24);
+          if (!ok) break;
+          if (g >= 2) {
+            ok = BoundedWait(bar(&misc->s_empty[buf]), ((g >> 1) & 1) ^ 1, misc, p.status, 25);
+            if (!ok) break;
+          }
+          ptx::TcFenceAfterSync();
+          const uint32_t stage_addr = kv_addr + stage * kStageBytes;
+#pragma unroll
+          for (int ks = 0; ks < 36; ++ks) {
+            const int c = ks >> 2, kk = ks & 3;
+            const uint64_t a = ptx::SmemDescSw128(q_addr + c * kQSlabBytes + kk * 32, 16, 1024);
+            const uint64_t b = ptx::SmemDescSw128(stage_addr + c * kSlabBytes + kk * 32, 16, 1024);
+            ptx::MmaF16SS(tmem + kTmemColS + 32 * buf, a, b, kIdescQk, ks > 0 ? 1u : 0u);
+          }
+          ptx::TcCommit(bar(&misc->s_full[buf]));
+          if (i > 0) ok = issue_pv(g - 1, i - 1 == 0);
+        }
+        if (!ok) break;
+        ok = issue_pv(g - 1, n == 1);
+        if (!ok) break;
+        ptx::TcCommit(bar(&misc->o_full));
+        ++seg;
+      }
+      // Nothing of this thread's tensor work may be in flight when TMEM is freed.
+      ptx::TcCommit(bar(&misc->drain));
+      {
+        const uint64_t t0 = ptx::GlobalTimerNs();
+        while (!ptx::MbarTryWait(bar(&misc->drain), 0)) {
+          if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
+        }
+      }
+    }
+  } else {
+    // ======================= softmax + epilogue warps ============================================
+    const int tid = threadIdx.x;                 // 0..127
+    const bool row_ok = lane < 16;               // M=64 accumulators use lanes 0..15 of each 32-lane quarter
+    const int head = warp * 16 + (lane & 15);
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    SegmentWalker walk(p.kv_len, p.batch, start_seq, start_tile, my_tiles);
+    int seq, t_lo, t_hi, seq_tiles, seq_len;
+    int g = 0;
+    int seg = 0;
+    bool ok = true;
+    bool first_segment_of_cta = true;
+
+    while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
+      // ---- stage Q (64 x 576 bf16) into the 128-byte swizzled K-major layout ----
+      {
+        const __nv_bfloat16* qb = p.q + static_cast<int64_t>(seq) * p.q_seq_stride;
+        for (int idx = tid; idx < kHeads * 72; idx += kSoftmaxThreads) {
+          const int h = idx / 72;
+          const int cc = idx - h * 72;
+          const int4 v = *reinterpret_cast<const int4*>(qb + h * p.q_head_stride + 8 * cc);
+          const int slab = cc >> 3, j = cc & 7;
+          unsigned char* dst = smem + kOffQ + slab * kQSlabBytes + h * 128 + ((j ^ (h & 7)) << 4);
+          *reinterpret_cast<int4*>(dst) = v;
+        }
+        ptx::FenceProxyAsyncShared();
+        ptx::MbarArrive(bar(&misc->q_full));
+      }
+      float m_run = -INFINITY;  // reference maximum, log2 domain (s * scale * log2e)
+      float l_run = 0.0f;
+      const int n = t_hi - t_lo;
+      for (int i = 0; i < n && ok; ++i, ++g) {
+        const int buf = g & 1;
+        const int tok0 = (t_lo + i) * kTile;
+        const int valid = min(kTile, seq_len - tok0);
+        ok = BoundedWait(bar(&misc->s_full[buf]), (g >> 1) & 1, misc, p.status, 30);
+        if (!ok) break;
+        ptx::TcFenceAfterSync();
+        uint32_t sr[32];
+        ptx::TmemLd32(tmem + lane_base + kTmemColS + 32 * buf, sr);
+        ptx::TmemWaitLd();
+        ptx::TcFenceBeforeSync();
+        ptx::MbarArrive(bar(&misc->s_empty[buf]));
+
+        float tile_max = -INFINITY;
+        float sv[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          sv[j] = (j < valid) ? __uint_as_float(sr[j]) * p.scale_log2 : -INFINITY;
+          tile_max = fmaxf(tile_max, sv[j]);
+        }
+        float factor = 1.0f;
+        bool rescale = false;
+        if (row_ok) {
+          if (m_run == -INFINITY) {
+            m_run = tile_max;  // first tile of the segment: nothing accumulated yet
+          } else if (tile_max > m_run + kRescaleThreshold) {
+            factor = exp2f(m_run - tile_max);
+            m_run = tile_max;
+            rescale = true;
+          }
+          misc->factor[head] = factor;
+        }
+        uint32_t packed[16];
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float p0 = exp2f(sv[2 * j] - m_run);
+          const float p1 = exp2f(sv[2 * j + 1] - m_run);
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          packed[j] = *reinterpret_cast<const uint32_t*>(&pb);
+          // The denominator sums the values the tensor core will actually multiply.
+          sum += __low2float(pb) + __high2float(pb);
+        }
+        l_run = l_run * factor + sum;
+
+        // P may be overwritten once PV of the previous tile has drained (also orders the O rescale).
+        if (g >= 1) {
+          ok = BoundedWait(bar(&misc->p_empty), (g - 1) & 1, misc, p.status, 31);
+          if (!ok) break;
+        }
+        const bool any_rescale = ptx::NamedBarrierOr(1, kSoftmaxThreads, rescale);
+        if (any_rescale) {
+          // Rare path: scale the accumulated O^T columns (heads) by their factors.
+          ptx::TcFenceAfterSync();
+#pragma unroll 1
+          for (int tm = 0; tm < 4; ++tm) {
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+              uint32_t o[32];
+              const uint32_t addr = tmem + lane_base + 64 * tm + 32 * half;
+              ptx::TmemLd32(addr, o);
+              ptx::TmemWaitLd();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * misc->factor[32 * half + j]);
+              ptx::TmemSt32(addr, o);
+            }
+          }
+          ptx::TmemWaitSt();
+          ptx::TcFenceBeforeSync();
+        }
+        if (row_ok) {
+          // Row `head` of P: 32 bf16 = logical 16-byte chunks 0..3 of a 128-byte swizzled row.
+          unsigned char* prow = smem + kOffP + head * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            *reinterpret_cast<int4*>(prow + ((c ^ (head & 7)) << 4)) =
+                make_int4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          }
+        }
+        if (valid < kTile) {
+          // Rows past the sequence end hold whatever the pool held; zero them so 0 * NaN cannot reach O.
+          unsigned char* stage_ptr = smem + kOffKv + (g % kStages) * kStageBytes;
+          const int rows = kTile - valid;
+          for (int idx = tid; idx < rows * 8 * 8; idx += kSoftmaxThreads) {
+            const int chunk = idx & 7;
+            const int slab = (idx >> 3) & 7;
+            const int r = valid + (idx >> 6);
+            *reinterpret_cast<int4*>(stage_ptr + slab * kSlabBytes + r * 128 + chunk * 16) = make_int4(0, 0, 0, 0);
+          }
+        }
+        ptx::FenceProxyAsyncShared();
+        if (any_rescale) ptx::NamedBarrier(2, kSoftmaxThreads);  // factors are read before the next tile rewrites them
+        ptx::MbarArrive(bar(&misc->p_full));
+      }
+      if (!ok) break;
+
+      // ---- epilogue of the segment ----
+      ok = BoundedWait(bar(&misc->o_full), seg & 1, misc, p.status, 32);
+      if (!ok) break;
+      ptx::TcFenceAfterSync();
+      const bool whole = (t_lo == 0 && t_hi == seq_tiles);
+      const bool to_user_partial = whole && p.user_o != nullptr;
+      const bool to_ws = !whole;
+      const int slot = cta * 2 + (first_segment_of_cta ? 0 : 1);
+      const float m_nat = m_run * 0.6931471805599453f;
+      if (row_ok) {
+        misc->inv_l[head] = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        if (to_ws) {
+          p.ws_m[slot * kHeads + head] = m_nat;
+          p.ws_l[slot * kHeads + head] = l_run;
+        } else if (to_user_partial) {
+          p.user_m[static_cast<int64_t>(seq) * kHeads + head] = m_nat;
+          p.user_l[static_cast<int64_t>(seq) * kHeads + head] = l_run;
+        } else if (p.lse != nullptr) {
+          p.lse[static_cast<int64_t>(seq) * kHeads + head] = m_nat + logf(l_run);
+        }
+      }
+      ptx::NamedBarrier(1, kSoftmaxThreads);
+#pragma unroll 1
+      for (int tm = 0; tm < 4; ++tm) {
+        const int dv = 128 * tm + warp * 32 + lane;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint32_t o[32];
+          ptx::TmemLd32(tmem + lane_base + 64 * tm + 32 * half, o);
+          ptx::TmemWaitLd();
+          if (to_ws) {
+            float* dst = p.ws_o + (static_cast<int64_t>(slot) * kHeads + 32 * half) * kLatent + dv;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) dst[j * kLatent] = __uint_as_float(o[j]);
+          } else if (to_user_partial) {
+            float* dst = p.user_o + (static_cast<int64_t>(seq) * kHeads + 32 * half) * kLatent + dv;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) dst[j * kLatent] = __uint_as_float(o[j]);
+          } else {
+            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(seq) * kHeads + 32 * half) * kLatent + dv;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              dst[j * kLatent] = __float2bfloat16_rn(__uint_as_float(o[j]) * misc->inv_l[32 * half + j]);
+            }
+          }
+        }
+      }
+      ptx::TcFenceBeforeSync();
+      ptx::MbarArrive(bar(&misc->o_empty));
+      first_segment_of_cta = false;
+      ++seg;
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------------------
+  ptx::TcFenceBeforeSync();
+  __syncthreads();
+  if (warp == 5) {
+    ptx::TcFenceAfterSync();
+    ptx::TmemDealloc(tmem, kTmemCols);
+  }
+}
+
+// Merges the partial segments of every sequence that straddles CTAs, and writes the result of empty
+// sequences. One warp per (sequence, head). Recomputes the flat partition arithmetic of the decode
+// kernel: sequence b owns tiles [P_b, P_b + n_b) of T; CTA c owns [c*T/G, (c+1)*T/G).
+__global__ void __launch_bounds__(256)
+    MlaFinalizeKernel(TcParams p, int32_t n_ctas) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (row >= static_cast<int64_t>(p.batch) * kHeads) return;
+  const int b = static_cast<int>(row / kHeads);
+  const int h = static_cast<int>(row % kHeads);
+  long long before = 0, total = 0;
+  for (int s = lane; s < p.batch; s += 32) {
+    const long long t = TilesOf(p.kv_len[s]);
+    total += t;
+    if (s < b) before += t;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    total += __shfl_xor_sync(0xffffffffu, total, off);
+    before += __shfl_xor_sync(0xffffffffu, before, off);
+  }
+  const long long mine = TilesOf(p.kv_len[b]);
+  const bool want_partial = p.user_o != nullptr;
+
+  float big = -INFINITY, sum_l = 0.0f;
+  float4 acc[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+
+  if (mine > 0) {
+    // CTA owning tile x: the largest c with floor(c*T/G) <= x.
+    const long long c_first = ((before + 1) * n_ctas - 1) / total;
+    const long long c_last = ((before + mine) * n_ctas - 1) / total;
+    if (c_first == c_last) return;  // written directly by the decode kernel
+    for (long long c = c_first; c <= c_last; ++c) {
+      const long long lo = total * c / n_ctas;
+      if (total * (c + 1) / n_ctas == lo) continue;  // a CTA with an empty range wrote nothing
+      const int slot = static_cast<int>(c * 2 + (lo >= before ? 0 : 1));
+      if (p.ws_l[slot * kHeads + h] > 0.0f) big = fmaxf(big, p.ws_m[slot * kHeads + h]);
+    }
+    for (long long c = c_first; c <= c_last; ++c) {
+      const long long lo = total * c / n_ctas;
+      if (total * (c + 1) / n_ctas == lo) continue;
+      const int slot = static_cast<int>(c * 2 + (lo >= before ? 0 : 1));
+      const float l = p.ws_l[slot * kHeads + h];
+      if (!(l > 0.0f)) continue;
+      const float w = expf(p.ws_m[slot * kHeads + h] - big);
+      sum_l += l * w;
+      const float4* src = reinterpret_cast<const float4*>(p.ws_o + (static_cast<int64_t>(slot) * kHeads + h) * kLatent);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 v = src[lane + 32 * i];
+        acc[i].x = fmaf(v.x, w, acc[i].x);
+        acc[i].y = fmaf(v.y, w, acc[i].y);
+        acc[i].z = fmaf(v.z, w, acc[i].z);
+        acc[i].w = fmaf(v.w, w, acc[i].w);
+      }
+    }
+  }
+  if (want_partial) {
+    float4* dst = reinterpret_cast<float4*>(p.user_o + row * kLatent);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = acc[i];
+    if (lane == 0) {
+      p.user_m[row] = big;
+      p.user_l[row] = sum_l;
+    }
+    return;
+  }
+  const float inv = sum_l > 0.0f ? 1.0f / sum_l : 0.0f;
+  uint2* dst = reinterpret_cast<uint2*>(p.out + row * kLatent);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[i].x * inv, acc[i].y * inv);
+    const __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc[i].z * inv, acc[i].w * inv);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&lo2);
+    packed.y = *reinterpret_cast<const uint32_t*>(&hi2);
+    dst[lane + 32 * i] = packed;
+  }
+  if (lane == 0 && p.lse) p.lse[row] = sum_l > 0.0f ? big + logf(sum_l) : -INFINITY;
+}
+
+// ---- tensor maps ----------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn ResolveEncodeTiled() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      return static_cast<EncodeTiledFn>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  int64_t stride;
+  int64_t rows;
+  int32_t width;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && stride == o.stride && rows == o.rows && width == o.width;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h ^= static_cast<size_t>(k.stride) * 0x9E3779B97F4A7C15ull;
+    h ^= static_cast<size_t>(k.rows) * 0xC2B2AE3D27D4EB4Full;
+    return h ^ static_cast<size_t>(k.width);
+  }
+};
+
+// Row-major [rows][width] bf16 view with row stride `stride` elements; box = 64 columns x 32 rows,
+// 128-byte swizzle. Maps are cached: a decode step reuses the same 2 x layers views every token.
+int32_t GetRowMap(const void* base, int64_t stride, int64_t rows, int32_t width, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, stride, rows, width};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return B200KV_OK;
+    }
+  }
+  EncodeTiledFn encode = ResolveEncodeTiled();
+  if (encode == nullptr) {
+    SetLastError("cuTensorMapEncodeTiled could not be resolved from the CUDA driver");
+    return B200KV_ERR_RUNTIME;
+  }
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(stride) * 2};
+  const cuuint32_t box[2] = {64, kTile};
+  const cuuint32_t elem[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    SetLastError("cuTensorMapEncodeTiled failed with CUresult %d (base %p, stride %lld, rows %lld, width %d)",
+                 static_cast<int>(rc), base, static_cast<long long>(stride), static_cast<long long>(rows), width);
+    return B200KV_ERR_RUNTIME;
+  }
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, map);
+  }
+  *out = map;
+  return B200KV_OK;
+}
+
+}  // namespace
+
+size_t TcWorkspaceBytes(int32_t n_ctas) {
+  return static_cast<size_t>(n_ctas) * 2 * kHeads * (kLatent + 2) * sizeof(float);
+}
+
+bool TcSupports(const b200kv_decode_args& a) {
+  return a.heads == kHeads && a.block_size % kTile == 0 && a.q_head_stride % 8 == 0 && a.q_seq_stride % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0 && a.pool.pool_rows <= INT32_MAX &&
+         a.pool.latent_row_stride * 2 < (1ll << 40);
+}
+
+int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status) {
+  static thread_local int configured_device = -1;
+  int device = 0;
+  if (int32_t rc = CheckCuda(cudaGetDevice(&device), "cudaGetDevice")) return rc;
+  if (device != configured_device) {
+    if (int32_t rc = CheckCuda(cudaFuncSetAttribute(MlaDecodeTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    kSmemBytes),
+                               "tcgen05 decode smem opt-in")) {
+      return rc;
+    }
+    configured_device = device;
+  }
+  CUtensorMap latent_map, rope_map;
+  if (int32_t rc = GetRowMap(a.pool.latent, a.pool.latent_row_stride, a.pool.pool_rows, kLatent, &latent_map)) return rc;
+  if (int32_t rc = GetRowMap(a.pool.rope, a.pool.rope_row_stride, a.pool.pool_rows, kRope, &rope_map)) return rc;
+
+  TcParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(a.q);
+  p.q_seq_stride = a.q_seq_stride;
+  p.q_head_stride = a.q_head_stride;
+  p.block_table = a.block_table;
+  p.max_blocks = a.max_blocks;
+  p.kv_len = a.kv_len;
+  p.kv_begin = a.kv_begin;
+  p.pool_rows = a.pool.pool_rows;
+  p.batch = a.batch;
+  p.block_size = a.block_size;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.out = static_cast<__nv_bfloat16*>(a.out);
+  p.lse = a.lse;
+  p.user_o = a.partial_o;
+  p.user_m = a.partial_m;
+  p.user_l = a.partial_l;
+  float* ws = static_cast<float*>(a.workspace);
+  const size_t slots = static_cast<size_t>(n_ctas) * 2;
+  p.ws_o = ws;
+  p.ws_m = ws + slots * kHeads * kLatent;
+  p.ws_l = p.ws_m + slots * kHeads;
+  p.status = status;
+
+  MlaDecodeTcKernel<<<n_ctas, kThreads, kSmemBytes, stream>>>(latent_map, rope_map, p);
+  if (int32_t rc = CheckCuda(cudaGetLastError(), "tcgen05 decode launch")) return rc;
+  const int64_t rows = static_cast<int64_t>(a.batch) * kHeads;
+  MlaFinalizeKernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(p, n_ctas);
+  return CheckCuda(cudaGetLastError(), "decode finalize launch");
+}
+
+}  // namespace b200kv

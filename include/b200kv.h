@@ -1,0 +1,204 @@
+/*
+ * b200kv.h: C ABI of the B200 (sm_100a) decode-time KV-cache path.
+ *
+ * Three device operations and the host bookkeeping around them:
+ *   append  : scatter each new token's MLA latent row (c_kv | k_rope, bf16) into the block-paged pool;
+ *   gather  : copy a sequence's rows out of the pool through its block table;
+ *   decode  : dense absorbed-MLA decode attention over the paged pool (split-KV on tcgen05 tensor
+ *             cores) with a log-sum-exp merge of the split partials.
+ *
+ * Every entry point takes plain pointers, sizes and a CUDA stream handle passed as void*; nothing here
+ * depends on a framework type. Device entry points enqueue work and return; an asynchronous fault
+ * surfaces at the caller's next synchronisation, exactly as with the two-phase operator launches they
+ * replace (reference: include/moe/core/op_table.hpp:1015). Return value: 0 on success, otherwise one
+ * of the B200KV_ERR_* codes, whose values follow the reference's status convention
+ * (include/moe/core/op_table.hpp:142-147). b200kv_last_error() gives the text for the calling thread.
+ *
+ * Pool layout (reference: src/memory/static_arena_manager.cpp:315-318, 571-580): a layer's cache is
+ * two co-indexed row arrays, latent [rows][latent_dim] and rope [rows][rope_dim], rows = blocks x
+ * block_size. Strides are in ELEMENTS (bf16). The fused 576-wide row of the benchmarks is the same
+ * view with rope = latent + 512 and both row strides 576. The layer is chosen by the caller's base
+ * pointers, as in src/pipeline/pipeline.cpp:391-395.
+ */
+#ifndef B200KV_H_
+#define B200KV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200KV_OK 0
+#define B200KV_ERR_NULLPTR 161001 /* a required pointer was null            */
+#define B200KV_ERR_INVALID 161002 /* a size, stride or alignment is refused */
+#define B200KV_ERR_RUNTIME 361001 /* the CUDA runtime reported a failure    */
+
+/* Codes a kernel records in the caller's status word (first error wins). */
+#define B200KV_DEV_OK 0
+#define B200KV_DEV_BAD_SLOT 1    /* append: slot >= pool_rows; detail = token index, slot           */
+#define B200KV_DEV_BAD_BLOCK 2   /* gather/decode: block id out of range; detail = sequence, index  */
+#define B200KV_DEV_TIMEOUT 3     /* a bounded wait inside a kernel ran out; detail = site, phase    */
+#define B200KV_DEV_BAD_PLAN 4    /* decode: work partition inconsistent; detail = cta, value        */
+
+/* MLA geometry of the reference model (include/moe/core/config.hpp:47,78-79,95). */
+#define B200KV_LATENT_DIM 512
+#define B200KV_ROPE_DIM 64
+#define B200KV_HEADS 64
+
+/* One layer's paged cache (device pointers, bf16). */
+typedef struct b200kv_pool_view {
+  void* latent;              /* [pool_rows][latent_row_stride] bf16, 16-byte aligned            */
+  void* rope;                /* [pool_rows][rope_row_stride]  bf16, 16-byte aligned             */
+  int64_t latent_row_stride; /* elements; multiple of 8                                          */
+  int64_t rope_row_stride;   /* elements; multiple of 8                                          */
+  int64_t pool_rows;         /* num_blocks * block_size                                          */
+} b200kv_pool_view;
+
+/* Device status word: int32[4] = {code, detail0, detail1, detail2}, zeroed by the caller. */
+typedef int32_t b200kv_status_word;
+
+const char* b200kv_last_error(void);
+int32_t b200kv_abi_version(void);
+
+/*
+ * Append. Replaces the launch of aclnnScatterPaKvCache planned at src/pipeline/pipeline.cpp:226-234
+ * (prototype include/moe/core/op_table.hpp:365-372, cache mode "Norm"): for each token row t,
+ *   pool.latent[slot[t]] = latent_src[t],  pool.rope[slot[t]] = rope_src[t].
+ * slot is the flat row (block * block_size + offset); a negative slot marks padding and is skipped;
+ * a slot >= pool_rows is recorded in `status` and skipped. Source strides in elements, multiple of 8.
+ */
+int32_t b200kv_append(const b200kv_pool_view* pool, const void* latent_src, int64_t src_latent_stride,
+                      const void* rope_src, int64_t src_rope_stride, const int32_t* slot_mapping, int64_t n_tokens,
+                      void* stream, b200kv_status_word* status);
+
+/*
+ * Gather. The standalone form of the block-table addressing that the reference hands to its fused
+ * attention operator (block_table and block_size arguments, src/pipeline/pipeline.cpp:241,244):
+ * logical token j of sequence b is pool row block_table[b*max_blocks + j/block_size]*block_size +
+ * j%block_size; its latent and rope rows are copied to output row out_row_offsets[b] + j.
+ * kv_len, block_table and out_row_offsets are device arrays (int32, int32, int64).
+ */
+int32_t b200kv_gather(const b200kv_pool_view* pool, const int32_t* block_table, int64_t max_blocks,
+                      const int32_t* kv_len, int64_t batch, int64_t block_size, void* out_latent,
+                      int64_t out_latent_stride, void* out_rope, int64_t out_rope_stride,
+                      const int64_t* out_row_offsets, int64_t total_rows, void* stream,
+                      b200kv_status_word* status);
+
+/*
+ * Decode attention. Replaces the launch of aclnnFusedInferAttentionScoreV5 planned at
+ * src/pipeline/pipeline.cpp:235-249 (prototype include/moe/core/op_table.hpp:438-454; one query token
+ * per sequence, layout TND, 64 query heads over one latent KV head): per sequence b and head h, over
+ * logical tokens [kv_begin[b], kv_begin[b]+kv_len[b]) of the sequence's block table,
+ *   s_j = scale*(q_lat[h].c_j + q_rope[h].r_j), p = softmax_j(s), out[h] = sum_j p_j c_j,
+ *   lse[h] = max_j s_j + log sum_j exp(s_j - max).
+ * q: bf16, element (b,h,k) at q[b*q_seq_stride + h*q_head_stride + k], k in [0,576).
+ * out: bf16 [batch][heads][512]; lse: fp32 [batch][heads] or null.
+ * partial_o/m/l: when non-null the call writes the UN-normalised shard result instead of out/lse
+ *   (fp32 [batch][heads][512], [batch][heads], [batch][heads]) for a later b200kv_lse_merge across
+ *   KV-range shards; kv_begin (device int32, multiple of block_size, or null for zero) selects the
+ *   shard's first token.
+ * workspace: device scratch of at least b200kv_mla_decode_workspace_bytes(); reused across calls on
+ *   one stream. variant: B200KV_DECODE_AUTO, or force one implementation (tests, profiling).
+ */
+#define B200KV_DECODE_AUTO 0
+#define B200KV_DECODE_SIMT 1   /* CUDA-core kernel: any geometry                            */
+#define B200KV_DECODE_TCGEN05 2 /* tensor-core kernel: 64 heads, 512+64, block_size % 64 == 0 */
+
+typedef struct b200kv_decode_args {
+  const void* q;
+  int64_t q_seq_stride;
+  int64_t q_head_stride;
+  b200kv_pool_view pool;
+  const int32_t* block_table; /* device int32 [batch][max_blocks] */
+  int64_t max_blocks;
+  const int32_t* kv_len;   /* device int32 [batch]           */
+  const int32_t* kv_begin; /* device int32 [batch] or null   */
+  int32_t batch;
+  int32_t heads;
+  int32_t block_size;
+  float scale;
+  void* out;        /* bf16 [batch][heads][512] or null when partials are requested */
+  float* lse;       /* fp32 [batch][heads] or null                                  */
+  float* partial_o; /* fp32 [batch][heads][512] or null                             */
+  float* partial_m; /* fp32 [batch][heads] or null                                  */
+  float* partial_l; /* fp32 [batch][heads] or null                                  */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t variant;
+  int32_t max_ctas; /* 0 = one CTA per SM of the current device                     */
+} b200kv_decode_args;
+
+size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas);
+int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* stream, b200kv_status_word* status);
+
+/*
+ * LSE merge of n_parts shard partials (the reduction that follows the KV-range split):
+ *   M = max_r m_r, L = sum_r l_r e^{m_r-M}, out = sum_r O_r e^{m_r-M} / L, lse = M + log L.
+ * partial_o: fp32 [n_parts][rows][512]; partial_m, partial_l: fp32 [n_parts][rows]; rows = batch*heads.
+ * No counterpart in the reference (single device, include/moe/core/config.hpp:280).
+ */
+int32_t b200kv_lse_merge(const float* partial_o, const float* partial_m, const float* partial_l, int32_t n_parts,
+                         int64_t rows, void* out_bf16, float* lse, void* stream);
+
+/*
+ * Seeded synthetic data on the device: dst[i] = bf16(scale * N(0,1)) for element counters
+ * first_element + i of stream (seed, stream_id); splitmix64 counters, Box-Muller in double.
+ * Bench and test utility; no counterpart in the reference.
+ */
+int32_t b200kv_fill_normal_bf16(void* dst, int64_t count, uint64_t seed, uint64_t stream_id,
+                                uint64_t first_element, double scale, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Host bookkeeping: KV block pool (free list, per-sequence block tables, admission and release).
+ * The reference reserves one block table and one slot per step and never fills the table
+ * (src/memory/static_arena_manager.cpp:298-300, 581-582; slot = position,
+ * src/pipeline/pipeline.cpp:515-519); batched decode needs the allocator below. It follows the
+ * fixed-capacity, plan-then-commit, validate-with-arithmetic pattern of the reference's expert slot
+ * pool (src/memory/exclusive_staging.cpp:313-399, 529-572): no allocation after create, a failed call
+ * changes nothing.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct b200kv_block_pool b200kv_block_pool;
+
+/* free_order: initial free-list order (num_blocks ids) or null for 0..num_blocks-1. */
+b200kv_block_pool* b200kv_block_pool_create(int32_t num_blocks, int32_t block_size, int32_t max_seqs,
+                                            int32_t max_blocks_per_seq, const int32_t* free_order);
+void b200kv_block_pool_destroy(b200kv_block_pool* pool);
+int32_t b200kv_block_pool_admit(b200kv_block_pool* pool, int32_t seq);
+/* Extends `seq` by n_tokens; writes the new tokens' slots (flat pool rows) to slots_out[0..n). */
+int32_t b200kv_block_pool_grow(b200kv_block_pool* pool, int32_t seq, int32_t n_tokens, int32_t* slots_out);
+int32_t b200kv_block_pool_release(b200kv_block_pool* pool, int32_t seq);
+int32_t b200kv_block_pool_free_count(const b200kv_block_pool* pool);
+int32_t b200kv_block_pool_seq_len(const b200kv_block_pool* pool, int32_t seq);
+/* Host views: table [max_seqs][max_blocks_per_seq] (unused entries 0), lens [max_seqs]. */
+const int32_t* b200kv_block_pool_table(const b200kv_block_pool* pool);
+const int32_t* b200kv_block_pool_lens(const b200kv_block_pool* pool);
+/* Free list in queue order; returns the count written (<= capacity). */
+int32_t b200kv_block_pool_export_free(const b200kv_block_pool* pool, int32_t* out, int32_t capacity);
+/* O(blocks) invariant check; 0 when every block is owned exactly once, else B200KV_ERR_INVALID. */
+int32_t b200kv_block_pool_validate(const b200kv_block_pool* pool);
+
+/*
+ * KV reservation geometry and paged-attention counters, as the reference computes them
+ * (blocks per layer: src/memory/static_arena_manager.cpp:197; pool bytes: :315-318; reported block
+ * count and utilisation: src/pipeline/pipeline.cpp:134-136, 532-534;
+ * include/moe/diagnostics/inference_stats.hpp:21-28).
+ */
+typedef struct b200kv_reservation {
+  int64_t blocks_per_layer;
+  int64_t total_blocks;
+  int64_t latent_bytes;
+  int64_t rope_bytes;
+  int64_t block_table_bytes;
+  int64_t slot_mapping_bytes;
+} b200kv_reservation;
+
+int32_t b200kv_plan_reservation(int64_t max_context, int64_t block_size, int64_t layers, int64_t max_seqs,
+                                int64_t tokens_per_step, b200kv_reservation* out);
+double b200kv_utilisation(int64_t active_tokens, int64_t blocks_per_layer, int64_t block_size);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200KV_H_ */
