@@ -111,7 +111,7 @@ extern "C" int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* strea
   }
   const bool tc_ok = TcSupports(a);
   if (a.variant == B200KV_DECODE_TCGEN05 && !tc_ok) {
-    SetLastError("decode: the tcgen05 kernel needs 64 heads, block_size %% 32 == 0, 16-byte aligned q with strides "
+    SetLastError("decode: the tcgen05 kernel needs 64 heads, block_size %% 64 == 0, 16-byte aligned q with strides "
                  "that are multiples of 8 elements");
     return B200KV_ERR_INVALID;
   }

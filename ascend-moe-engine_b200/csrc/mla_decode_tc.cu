@@ -1,22 +1,27 @@
 // Split-KV absorbed-MLA decode attention on tcgen05 tensor cores (sm_100a), 64 heads x (512+64).
 //
-// Work partition. A sequence of L tokens is ceil(L/32) tiles. The tiles of all sequences form one flat
+// Work partition. A sequence of L tokens is ceil(L/64) tiles. The tiles of all sequences form one flat
 // list; CTA c of G takes the contiguous range [c*T/G, (c+1)*T/G). A CTA therefore walks a few
 // "segments" (a tile range inside one sequence). A segment that covers its whole sequence writes the
 // result directly; otherwise it writes an un-normalised partial (m, l, O) to the workspace and the
 // finalize kernel merges the parts with a log-sum-exp reduction. Only the first and the last segment
 // of a CTA can be partial, so the workspace holds two partial slots per CTA.
 //
-// Per tile of 32 tokens (one KV stage of 36,864 bytes, TMA-loaded, 128-byte swizzled):
-//   S[64 heads x 32 tok]  = Q[64 x 576] . K_tile^T            36 MMAs M=64  N=32 K=16 (K-major A, B)
-//   P = exp2(S*scale*log2e - m)  (softmax warps, fp32 -> bf16, written to shared memory)
-//   O^T[512 x 64 heads]  += V_tile^T[512 x 32] . P^T[32 x 64]   8 MMAs M=128 N=64 K=16 (MN-major A)
-// V is the first 512 columns of the same shared-memory tile that served as K: the tile is read from
-// HBM once. O^T lives in TMEM (4 accumulators of 128 lanes x 64 columns), S double-buffered beside it.
+// Per tile of 64 tokens (one KV stage of 73,728 bytes: nine 64-column slabs, TMA-loaded, 128-byte
+// swizzled):
+//   S[64 heads x 64 tok]  = Q[64 x 576] . K_tile^T            36 MMAs M=64  N=64 K=16 (K-major A, B)
+//   P = exp2(S*scale*log2e - m)  (softmax warps, fp32 -> bf16, written over the stage's rope slab,
+//                                 which QK has finished with)
+//   O^T[512 x 64 heads]  += V_tile^T[512 x 64] . P^T[64 x 64]  16 MMAs M=128 N=64 K=16 (MN-major A)
+// V is the first 512 columns of the same shared-memory tile that served as K: a tile is read from HBM
+// once. O^T lives in TMEM (4 accumulators of 128 lanes x 64 columns), S double-buffered beside it.
+// Measured on B200: one tcgen05.mma costs max(45, N/2) cycles whatever M is, so the tile is 64 tokens
+// (N = 64 costs the same as N = 32) and PV runs transposed to use M = 128.
 //
 // Warp roles: warps 0-3 softmax + epilogue (TMEM lanes 32w..32w+31), warp 4 TMA producer, warp 5 MMA
-// issuer and TMEM owner. QK of tile i+1 is issued before PV of tile i so the tensor pipe works while
-// the softmax warps handle tile i. Four KV stages keep three tile loads in flight per SM.
+// issuer and TMEM owner. The issuer polls: PV of tile i goes out as soon as P is ready, QK of tile i+1
+// as soon as its stage has landed, whichever comes first, so the tensor pipe works on the next tile's
+// scores while the softmax warps handle this one. Shared memory holds Q (72 KB) and two KV stages.
 //
 // Every wait is bounded: when a wait runs out the kernel records B200KV_DEV_TIMEOUT in the status
 // word, raises a CTA-wide abort flag, waits (bounded) for its own TMA loads, frees TMEM and returns.
@@ -35,24 +40,22 @@ namespace {
 constexpr int kHeads = 64;
 constexpr int kLatent = B200KV_LATENT_DIM;
 constexpr int kRope = B200KV_ROPE_DIM;
-constexpr int kTile = 32;      // tokens per tile / KV stage
-constexpr int kStages = 4;
-constexpr int kSlabBytes = kTile * 128;                 // one 64-column slab of a tile: 32 rows x 128 B
-constexpr int kStageBytes = 9 * kSlabBytes;             // 36,864
+constexpr int kTile = 64;      // tokens per tile / KV stage
+constexpr int kStages = 2;
+constexpr int kSlabBytes = kTile * 128;                 // one 64-column slab of a tile: kTile rows x 128 B
+constexpr int kStageBytes = 9 * kSlabBytes;             // 73,728
 constexpr int kQSlabBytes = kHeads * 128;               // 8,192
 constexpr int kQBytes = 9 * kQSlabBytes;                // 73,728
-constexpr int kPBytes = kHeads * 128;                   // 8,192 (64 rows x 128 B, first 64 B of a row used)
 constexpr int kSoftmaxThreads = 128;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemColS = 256;                     // S buffers at columns 256 and 288
+constexpr uint32_t kTmemColS = 256;                     // S buffers at columns 256 and 256 + kTile
 constexpr float kRescaleThreshold = 8.0f;               // log2 units: rescale O only when max grows by > 2^8
 
 // Shared memory carve-up (offsets from a 1024-byte aligned base).
 constexpr int kOffQ = 0;
 constexpr int kOffKv = kOffQ + kQBytes;
-constexpr int kOffP = kOffKv + kStages * kStageBytes;
-constexpr int kOffMisc = kOffP + kPBytes;
+constexpr int kOffMisc = kOffKv + kStages * kStageBytes;
 constexpr int kMiscBytes = 1024;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + slack for the manual 1024-byte alignment
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
@@ -62,9 +65,9 @@ struct Misc {
   uint64_t kv_empty[kStages];
   uint64_t s_full[2];
   uint64_t s_empty[2];
-  uint64_t p_full;
-  uint64_t p_empty;
+  uint64_t p_full[kStages];
   uint64_t q_full;
+  uint64_t q_empty;
   uint64_t o_full;
   uint64_t o_empty;
   uint64_t drain;
@@ -99,9 +102,25 @@ struct TcParams {
   float* ws_m;  // [G*2][64]
   float* ws_l;
   int32_t* status;
+  long long* trace;  // debug builds only: [cta][tile][8] clock64 stamps, or null
 };
 
+#ifdef B200KV_TRACE
+#define TRACE(tile, slot) do { if (p.trace != nullptr && (tile) < 64) p.trace[(static_cast<long long>(blockIdx.x) * 64 + (tile)) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(tile, slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ int TilesOf(int len) { return (len + kTile - 1) / kTile; }
+
+__device__ __forceinline__ bool Aborting(const Misc* misc) {
+  return *reinterpret_cast<const volatile int32_t*>(&misc->abort_flag) != 0;
+}
+
+__device__ __noinline__ void RaiseTimeout(Misc* misc, int32_t* status, int site, uint32_t parity) {
+  *reinterpret_cast<volatile int32_t*>(&misc->abort_flag) = 1;
+  RecordError(status, B200KV_DEV_TIMEOUT, site, static_cast<int32_t>(blockIdx.x), static_cast<int32_t>(parity));
+}
 
 // Bounded mbarrier wait. Returns false when the CTA is aborting or this wait ran out (about one
 // second), after recording where.
@@ -110,12 +129,11 @@ __device__ __noinline__ bool BoundedWait(uint32_t bar, uint32_t parity, Misc* mi
   for (uint32_t it = 0;; ++it) {
     if (ptx::MbarTryWait(bar, parity)) return true;
     if ((it & 255u) == 255u) {
-      if (*reinterpret_cast<volatile int32_t*>(&misc->abort_flag)) return false;
+      if (Aborting(misc)) return false;
       const uint64_t now = ptx::GlobalTimerNs();
       if (start == 0) start = now;
       if (now - start > 1000000000ull) {
-        *reinterpret_cast<volatile int32_t*>(&misc->abort_flag) = 1;
-        RecordError(status, B200KV_DEV_TIMEOUT, site, static_cast<int32_t>(blockIdx.x), static_cast<int32_t>(parity));
+        RaiseTimeout(misc, status, site, parity);
         return false;
       }
     }
@@ -158,9 +176,27 @@ struct SegmentWalker {
   }
 };
 
+// A 64-bit shared-memory descriptor whose start address is advanced by adding to the low word.
+__device__ __forceinline__ uint64_t DescAt(uint64_t base_desc, uint32_t byte_offset) {
+  return base_desc + static_cast<uint64_t>(byte_offset >> 4);
+}
+
+// Twelve QK k-steps (three 64-column slabs) starting at slab kFirstSlab; called by the whole MMA warp.
+template <int kFirstSlab>
+__device__ __forceinline__ void IssueQkGroup(uint64_t q_desc, uint64_t kdesc, uint32_t d) {
+  constexpr uint32_t kIdescQk = ptx::InstrDescBf16(64, kTile, 0, 0);
+#pragma unroll
+  for (int i = 0; i < 12; ++i) {
+    const int c = kFirstSlab + (i >> 2), kk = i & 3;
+    const uint64_t a = DescAt(q_desc, c * kQSlabBytes + kk * 32);
+    const uint64_t b = DescAt(kdesc, c * kSlabBytes + kk * 32);
+    if (ptx::ElectOne()) ptx::MmaF16SS(d, a, b, kIdescQk, (kFirstSlab + i) > 0 ? 1u : 0u);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
     MlaDecodeTcKernel(const __grid_constant__ CUtensorMap latent_map, const __grid_constant__ CUtensorMap rope_map,
-                      TcParams p) {
+                      const __grid_constant__ CUtensorMap q_map, TcParams p) {
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = ptx::SmemAddr(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -168,7 +204,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
   const uint32_t q_addr = base + kOffQ;
   const uint32_t kv_addr = base + kOffKv;
-  const uint32_t p_addr = base + kOffP;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -182,14 +217,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int s = 0; s < kStages; ++s) {
       ptx::MbarInit(bar(&misc->kv_full[s]), 1);
       ptx::MbarInit(bar(&misc->kv_empty[s]), 1);
+      ptx::MbarInit(bar(&misc->p_full[s]), kSoftmaxThreads);
     }
     for (int s = 0; s < 2; ++s) {
       ptx::MbarInit(bar(&misc->s_full[s]), 1);
       ptx::MbarInit(bar(&misc->s_empty[s]), kSoftmaxThreads);
     }
-    ptx::MbarInit(bar(&misc->p_full), kSoftmaxThreads);
-    ptx::MbarInit(bar(&misc->p_empty), 1);
-    ptx::MbarInit(bar(&misc->q_full), kSoftmaxThreads);
+    ptx::MbarInit(bar(&misc->q_full), 1);
+    ptx::MbarInit(bar(&misc->q_empty), 1);
     ptx::MbarInit(bar(&misc->o_full), 1);
     ptx::MbarInit(bar(&misc->o_empty), kSoftmaxThreads);
     ptx::MbarInit(bar(&misc->drain), 1);
@@ -239,6 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 4 && lane == 0) {
     ptx::PrefetchTensorMap(&latent_map);
     ptx::PrefetchTensorMap(&rope_map);
+    ptx::PrefetchTensorMap(&q_map);
   }
   ptx::TcFenceBeforeSync();
   __syncthreads();
@@ -256,7 +292,21 @@ __global__ void __launch_bounds__(kThreads, 1)
       int seq, t_lo, t_hi, seq_tiles, seq_len;
       int g = 0;  // tiles issued
       bool ok = true;
+      int seg = 0;
       while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
+        // Q of this segment's sequence: nine 64-column slabs of 64 head rows, once the previous
+        // segment's last QK has finished reading the buffer.
+        if (seg > 0) {
+          ok = BoundedWait(bar(&misc->q_empty), (seg - 1) & 1, misc, p.status, 11);
+          if (!ok) break;
+        }
+        {
+          const uint32_t qbar = bar(&misc->q_full);
+          ptx::MbarArriveExpectTx(qbar, kQBytes);
+#pragma unroll
+          for (int c = 0; c < 9; ++c) ptx::TmaLoad3D(q_addr + c * kQSlabBytes, &q_map, 64 * c, 0, seq, qbar);
+        }
+        ++seg;
         const int begin = p.kv_begin ? p.kv_begin[seq] : 0;
         for (int t = t_lo; t < t_hi; ++t, ++g) {
           const int stage = g % kStages;
@@ -275,6 +325,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           const uint32_t full = bar(&misc->kv_full[stage]);
           const uint32_t dst = kv_addr + stage * kStageBytes;
+          TRACE(g, 0);
           ptx::MbarArriveExpectTx(full, kStageBytes);
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -306,78 +357,141 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 5) {
     // ======================= MMA issuer ==========================================================
-    if (lane == 0) {
-      constexpr uint32_t kIdescQk = ptx::InstrDescBf16(64, kTile, 0, 0);
+    // The whole warp runs this loop in lockstep and each tcgen05 instruction sits under elect.sync:
+    // measured on B200, that form issues an M=64 N=64 MMA every 34 cycles (the tensor pipe's own
+    // rate), against 46-58 for a single-thread loop or a lane-predicated one. elect.sync picks the
+    // same lane every time, so the commits track the MMAs they follow.
+    {
       constexpr uint32_t kIdescPv = ptx::InstrDescBf16(128, kHeads, 1, 0);
+      // Descriptor templates; the start address is advanced by adding to the low word.
+      const uint64_t q_desc = ptx::SmemDescSw128(q_addr, 16, 1024);            // K-major, 8-row groups 1024 B apart
+      const uint64_t k_desc0 = ptx::SmemDescSw128(kv_addr, 16, 1024);          // K-major B (tile rows = N)
+      const uint64_t v_desc0 = ptx::SmemDescSw128(kv_addr, kSlabBytes, 1024);  // MN-major A: next 64 dv at +slab
       SegmentWalker walk(p.kv_len, p.batch, start_seq, start_tile, my_tiles);
       int seq, t_lo, t_hi, seq_tiles, seq_len;
-      int g = 0;    // tiles whose QK has been issued
+      int g0 = 0;   // global index of the segment's first tile
       int seg = 0;  // segment counter
       bool ok = true;
+      // Values that steer this loop come from memory; broadcasting them from lane 0 is what tells the
+      // compiler they are warp-uniform, which keeps the descriptor arithmetic on the uniform datapath.
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
 
-      auto issue_pv = [&](int g_tile, bool first_of_segment) -> bool {
-        // P of tile g_tile is ready when the softmax warps have arrived g_tile+1 times on p_full.
-        if (!BoundedWait(bar(&misc->p_full), g_tile & 1, misc, p.status, 21)) return false;
-        ptx::TcFenceAfterSync();
-        const uint32_t stage_addr = kv_addr + (g_tile % kStages) * kStageBytes;
-#pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks) {
-#pragma unroll
-          for (int tm = 0; tm < 4; ++tm) {
-            const uint64_t a = ptx::SmemDescSw128(stage_addr + 2 * tm * kSlabBytes + ks * 2048, kSlabBytes, 1024);
-            const uint64_t b = ptx::SmemDescSw128(p_addr + ks * 32, 16, 1024);
-            ptx::MmaF16SS(tmem + 64 * tm, a, b, kIdescPv, (first_of_segment && ks == 0) ? 0u : 1u);
-          }
-        }
-        ptx::TcCommit(bar(&misc->kv_empty[g_tile % kStages]));
-        ptx::TcCommit(bar(&misc->p_empty));
-        return true;
-      };
-
-      while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
-        ok = BoundedWait(bar(&misc->q_full), seg & 1, misc, p.status, 22);
+      while (ok) {
+        const int have = walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len) ? 1 : 0;
+        if (__shfl_sync(0xffffffffu, have, 0) == 0) break;
+        ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_full), seg & 1, misc, p.status, 22));
         if (!ok) break;
         if (seg > 0) {
           // The previous segment's accumulators must have been drained by the epilogue.
-          ok = BoundedWait(bar(&misc->o_empty), (seg - 1) & 1, misc, p.status, 23);
+          ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->o_empty), (seg - 1) & 1, misc, p.status, 23));
           if (!ok) break;
         }
-        const int n = t_hi - t_lo;
-        for (int i = 0; i < n && ok; ++i, ++g) {
-          const int stage = g % kStages;
-          const int buf = g & 1;
-          ok = BoundedWait(bar(&misc->kv_full[stage]), (g / kStages) & 1, misc, p.status, 24);
-          if (!ok) break;
-          if (g >= 2) {
-            ok = BoundedWait(bar(&misc->s_empty[buf]), ((g >> 1) & 1) ^ 1, misc, p.status, 25);
-            if (!ok) break;
-          }
-          ptx::TcFenceAfterSync();
-          const uint32_t stage_addr = kv_addr + stage * kStageBytes;
+        const int n = __shfl_sync(0xffffffffu, t_hi - t_lo, 0);
+        int next_qk = 0, next_pv = 0;
+        int qk_part = 0;  // QK goes out in three groups of 12 k-steps so that a ready PV never waits long
+        uint32_t idle = 0;
+        uint64_t idle_start = 0;
+        while (next_pv < n) {
+          bool progressed = false;
+          // PV of the oldest tile whose P is ready: it frees a KV stage, so it goes first.
+          if (next_pv < next_qk) {
+            const int g = __shfl_sync(0xffffffffu, g0 + next_pv, 0);
+            const int stage = g % kStages;
+            const int first_pv = __shfl_sync(0xffffffffu, next_pv == 0 ? 1 : 0, 0);
+            if (__all_sync(0xffffffffu, ptx::MbarTestWait(bar(&misc->p_full[stage]), (g / kStages) & 1))) {
+              ptx::TcFenceAfterSync();
+              TRACE(g, 5);
+              const uint32_t stage_off = stage * kStageBytes;
+              const uint64_t pdesc = DescAt(k_desc0, stage_off + 8 * kSlabBytes);  // K-major: row = head, 32 B per k-step
+              const uint64_t vdesc = DescAt(v_desc0, stage_off);
 #pragma unroll
-          for (int ks = 0; ks < 36; ++ks) {
-            const int c = ks >> 2, kk = ks & 3;
-            const uint64_t a = ptx::SmemDescSw128(q_addr + c * kQSlabBytes + kk * 32, 16, 1024);
-            const uint64_t b = ptx::SmemDescSw128(stage_addr + c * kSlabBytes + kk * 32, 16, 1024);
-            ptx::MmaF16SS(tmem + kTmemColS + 32 * buf, a, b, kIdescQk, ks > 0 ? 1u : 0u);
+              for (int ks = 0; ks < kTile / 16; ++ks) {
+#pragma unroll
+                for (int tm = 0; tm < 4; ++tm) {
+                  const uint64_t a = DescAt(vdesc, 2 * tm * kSlabBytes + ks * 2048);
+                  const uint64_t b = DescAt(pdesc, ks * 32);
+                  const uint32_t acc = (first_pv != 0 && ks == 0) ? 0u : 1u;
+                  if (ptx::ElectOne()) ptx::MmaF16SS(tmem_u + 64 * tm, a, b, kIdescPv, acc);
+                }
+              }
+              if (ptx::ElectOne()) ptx::TcCommit(bar(&misc->kv_empty[stage]));
+              TRACE(g, 6);
+              ++next_pv;
+              progressed = true;
+            }
           }
-          ptx::TcCommit(bar(&misc->s_full[buf]));
-          if (i > 0) ok = issue_pv(g - 1, i - 1 == 0);
+          // QK of the next tile whose stage has landed and whose S buffer has been read out.
+          if (next_qk < n) {
+            const int g = __shfl_sync(0xffffffffu, g0 + next_qk, 0);
+            const int stage = g % kStages;
+            const int buf = g & 1;
+            bool ready = qk_part > 0;
+            if (!ready) {
+              ready = ptx::MbarTestWait(bar(&misc->kv_full[stage]), (g / kStages) & 1) &&
+                      (g < 2 || ptx::MbarTestWait(bar(&misc->s_empty[buf]), ((g >> 1) & 1) ^ 1));
+              ready = __all_sync(0xffffffffu, ready);
+              if (ready) {
+                ptx::TcFenceAfterSync();
+                TRACE(g, 1);
+              }
+            }
+            if (ready) {
+              const uint64_t kdesc = DescAt(k_desc0, stage * kStageBytes);
+              const uint32_t d = tmem_u + kTmemColS + kTile * buf;
+              // Three groups of 12 k-steps with compile-time offsets (a runtime offset here costs the
+              // uniform-datapath issue rate); a ready PV is looked for between groups.
+              if (qk_part == 0) {
+                IssueQkGroup<0>(q_desc, kdesc, d);
+              } else if (qk_part == 1) {
+                IssueQkGroup<3>(q_desc, kdesc, d);
+              } else {
+                IssueQkGroup<6>(q_desc, kdesc, d);
+              }
+              if (++qk_part == 3) {
+                if (ptx::ElectOne()) {
+                  ptx::TcCommit(bar(&misc->s_full[buf]));
+                  if (next_qk == n - 1) ptx::TcCommit(bar(&misc->q_empty));  // Q buffer free for the next segment
+                }
+                TRACE(g, 2);
+                qk_part = 0;
+                ++next_qk;
+              }
+              progressed = true;
+            }
+          }
+          if (progressed) {
+            idle = 0;
+            idle_start = 0;
+          } else if ((++idle & 1023u) == 0) {
+            bool give_up = Aborting(misc);
+            if (!give_up) {
+              const uint64_t now = ptx::GlobalTimerNs();
+              if (idle_start == 0) idle_start = now;
+              if (now - idle_start > 1000000000ull) {
+                if (lane == 0) RaiseTimeout(misc, p.status, 24, static_cast<uint32_t>(next_qk * 65536 + next_pv));
+                give_up = true;
+              }
+            }
+            if (__any_sync(0xffffffffu, give_up)) {
+              ok = false;
+              break;
+            }
+          }
         }
         if (!ok) break;
-        ok = issue_pv(g - 1, n == 1);
-        if (!ok) break;
-        ptx::TcCommit(bar(&misc->o_full));
+        if (ptx::ElectOne()) ptx::TcCommit(bar(&misc->o_full));
+        g0 += n;
         ++seg;
       }
-      // Nothing of this thread's tensor work may be in flight when TMEM is freed.
-      ptx::TcCommit(bar(&misc->drain));
-      {
+      // Nothing of this warp's tensor work may be in flight when TMEM is freed.
+      if (ptx::ElectOne()) {
+        ptx::TcCommit(bar(&misc->drain));
         const uint64_t t0 = ptx::GlobalTimerNs();
         while (!ptx::MbarTryWait(bar(&misc->drain), 0)) {
           if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
         }
       }
+      __syncwarp();
     }
   } else {
     // ======================= softmax + epilogue warps ============================================
@@ -393,43 +507,41 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool first_segment_of_cta = true;
 
     while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
-      // ---- stage Q (64 x 576 bf16) into the 128-byte swizzled K-major layout ----
-      {
-        const __nv_bfloat16* qb = p.q + static_cast<int64_t>(seq) * p.q_seq_stride;
-        for (int idx = tid; idx < kHeads * 72; idx += kSoftmaxThreads) {
-          const int h = idx / 72;
-          const int cc = idx - h * 72;
-          const int4 v = *reinterpret_cast<const int4*>(qb + h * p.q_head_stride + 8 * cc);
-          const int slab = cc >> 3, j = cc & 7;
-          unsigned char* dst = smem + kOffQ + slab * kQSlabBytes + h * 128 + ((j ^ (h & 7)) << 4);
-          *reinterpret_cast<int4*>(dst) = v;
-        }
-        ptx::FenceProxyAsyncShared();
-        ptx::MbarArrive(bar(&misc->q_full));
-      }
       float m_run = -INFINITY;  // reference maximum, log2 domain (s * scale * log2e)
       float l_run = 0.0f;
       const int n = t_hi - t_lo;
       for (int i = 0; i < n && ok; ++i, ++g) {
         const int buf = g & 1;
+        const int stage = g % kStages;
         const int tok0 = (t_lo + i) * kTile;
         const int valid = min(kTile, seq_len - tok0);
         ok = BoundedWait(bar(&misc->s_full[buf]), (g >> 1) & 1, misc, p.status, 30);
         if (!ok) break;
         ptx::TcFenceAfterSync();
-        uint32_t sr[32];
-        ptx::TmemLd32(tmem + lane_base + kTmemColS + 32 * buf, sr);
+        if (tid == 0) TRACE(g, 3);
+        uint32_t sr[kTile];
+#pragma unroll
+        for (int part = 0; part < kTile / 32; ++part) {
+          ptx::TmemLd32(tmem + lane_base + kTmemColS + kTile * buf + 32 * part,
+                        *reinterpret_cast<uint32_t(*)[32]>(&sr[32 * part]));
+        }
         ptx::TmemWaitLd();
         ptx::TcFenceBeforeSync();
         ptx::MbarArrive(bar(&misc->s_empty[buf]));
 
-        float tile_max = -INFINITY;
-        float sv[32];
+        // Raw maximum first (the scale is positive), then one FFMA + one EX2 per element.
+        float raw_max = -INFINITY;
+        if (valid == kTile) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          sv[j] = (j < valid) ? __uint_as_float(sr[j]) * p.scale_log2 : -INFINITY;
-          tile_max = fmaxf(tile_max, sv[j]);
+          for (int j = 0; j < kTile; ++j) raw_max = fmaxf(raw_max, __uint_as_float(sr[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < kTile; ++j) {
+            if (j >= valid) sr[j] = 0xff800000u;  // -inf: masked out of the maximum and of P
+            raw_max = fmaxf(raw_max, __uint_as_float(sr[j]));
+          }
         }
+        const float tile_max = raw_max * p.scale_log2;
         float factor = 1.0f;
         bool rescale = false;
         if (row_ok) {
@@ -442,27 +554,25 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           misc->factor[head] = factor;
         }
-        uint32_t packed[16];
+        const float neg_m = -m_run;
         float sum = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = exp2f(sv[2 * j] - m_run);
-          const float p1 = exp2f(sv[2 * j + 1] - m_run);
+        for (int j = 0; j < kTile / 2; ++j) {
+          const float p0 = ptx::Ex2Approx(fmaf(__uint_as_float(sr[2 * j]), p.scale_log2, neg_m));
+          const float p1 = ptx::Ex2Approx(fmaf(__uint_as_float(sr[2 * j + 1]), p.scale_log2, neg_m));
           const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          packed[j] = *reinterpret_cast<const uint32_t*>(&pb);
-          // The denominator sums the values the tensor core will actually multiply.
-          sum += __low2float(pb) + __high2float(pb);
+          sr[j] = *reinterpret_cast<const uint32_t*>(&pb);
+          sum += p0 + p1;  // the denominator (and lse) keep the unrounded fp32 weights
         }
         l_run = l_run * factor + sum;
 
-        // P may be overwritten once PV of the previous tile has drained (also orders the O rescale).
-        if (g >= 1) {
-          ok = BoundedWait(bar(&misc->p_empty), (g - 1) & 1, misc, p.status, 31);
-          if (!ok) break;
-        }
         const bool any_rescale = ptx::NamedBarrierOr(1, kSoftmaxThreads, rescale);
         if (any_rescale) {
-          // Rare path: scale the accumulated O^T columns (heads) by their factors.
+          // Rare path: scale the accumulated O^T columns (heads) by their factors. PV of the previous
+          // tile must have drained first; its commit is the arrival on that tile's kv_empty.
+          const int gp = g - 1;
+          ok = BoundedWait(bar(&misc->kv_empty[gp % kStages]), (gp / kStages) & 1, misc, p.status, 31);
+          if (!ok) break;
           ptx::TcFenceAfterSync();
 #pragma unroll 1
           for (int tm = 0; tm < 4; ++tm) {
@@ -480,18 +590,20 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::TmemWaitSt();
           ptx::TcFenceBeforeSync();
         }
+        unsigned char* stage_ptr = smem + kOffKv + stage * kStageBytes;
         if (row_ok) {
-          // Row `head` of P: 32 bf16 = logical 16-byte chunks 0..3 of a 128-byte swizzled row.
-          unsigned char* prow = smem + kOffP + head * 128;
+          // Row `head` of P (64 bf16 = 8 chunks of 16 bytes) over the stage's rope slab, which QK has
+          // finished with; chunks swizzled by the row index as the 128-byte pattern prescribes.
+          static_assert(kTile == 64, "P rows of 128 bytes fill the rope slab only for 64-token tiles");
+          unsigned char* prow = stage_ptr + 8 * kSlabBytes + head * 128;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 8; ++c) {
             *reinterpret_cast<int4*>(prow + ((c ^ (head & 7)) << 4)) =
-                make_int4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                make_int4(sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
           }
         }
         if (valid < kTile) {
           // Rows past the sequence end hold whatever the pool held; zero them so 0 * NaN cannot reach O.
-          unsigned char* stage_ptr = smem + kOffKv + (g % kStages) * kStageBytes;
           const int rows = kTile - valid;
           for (int idx = tid; idx < rows * 8 * 8; idx += kSoftmaxThreads) {
             const int chunk = idx & 7;
@@ -502,7 +614,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         ptx::FenceProxyAsyncShared();
         if (any_rescale) ptx::NamedBarrier(2, kSoftmaxThreads);  // factors are read before the next tile rewrites them
-        ptx::MbarArrive(bar(&misc->p_full));
+        if (tid == 0) TRACE(g, 4);
+        ptx::MbarArrive(bar(&misc->p_full[stage]));
       }
       if (!ok) break;
 
@@ -729,7 +842,53 @@ int32_t GetRowMap(const void* base, int64_t stride, int64_t rows, int32_t width,
   return B200KV_OK;
 }
 
+// Query view [batch][64 heads][576] bf16 with element strides (q_seq_stride, q_head_stride, 1);
+// box = 64 columns x 64 heads of one sequence, 128-byte swizzle.
+int32_t GetQMap(const void* base, int64_t head_stride, int64_t seq_stride, int32_t batch, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, head_stride * 131 + seq_stride, batch, -1};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return B200KV_OK;
+    }
+  }
+  EncodeTiledFn encode = ResolveEncodeTiled();
+  if (encode == nullptr) {
+    SetLastError("cuTensorMapEncodeTiled could not be resolved from the CUDA driver");
+    return B200KV_ERR_RUNTIME;
+  }
+  // A batch of one has no meaningful sequence stride; any multiple of 16 bytes that covers a sequence will do.
+  const int64_t seq_stride_eff = batch > 1 ? seq_stride : static_cast<int64_t>(kHeads) * head_stride;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kLatent + kRope), kHeads, static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_stride) * 2, static_cast<cuuint64_t>(seq_stride_eff) * 2};
+  const cuuint32_t box[3] = {64, kHeads, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  CUtensorMap map;
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    SetLastError("cuTensorMapEncodeTiled (query) failed with CUresult %d (base %p, strides %lld/%lld, batch %d)",
+                 static_cast<int>(rc), base, static_cast<long long>(head_stride), static_cast<long long>(seq_stride),
+                 batch);
+    return B200KV_ERR_RUNTIME;
+  }
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, map);
+  }
+  *out = map;
+  return B200KV_OK;
+}
+
 }  // namespace
+
+long long* g_trace = nullptr;  // set by the debug hook below; null in normal use
 
 size_t TcWorkspaceBytes(int32_t n_ctas) {
   return static_cast<size_t>(n_ctas) * 2 * kHeads * (kLatent + 2) * sizeof(float);
@@ -757,6 +916,9 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   if (int32_t rc = GetRowMap(a.pool.latent, a.pool.latent_row_stride, a.pool.pool_rows, kLatent, &latent_map)) return rc;
   if (int32_t rc = GetRowMap(a.pool.rope, a.pool.rope_row_stride, a.pool.pool_rows, kRope, &rope_map)) return rc;
 
+  CUtensorMap q_map;
+  if (int32_t rc = GetQMap(a.q, a.q_head_stride, a.q_seq_stride, a.batch, &q_map)) return rc;
+
   TcParams p{};
   p.q = static_cast<const __nv_bfloat16*>(a.q);
   p.q_seq_stride = a.q_seq_stride;
@@ -780,8 +942,9 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.ws_m = ws + slots * kHeads * kLatent;
   p.ws_l = p.ws_m + slots * kHeads;
   p.status = status;
+  p.trace = g_trace;
 
-  MlaDecodeTcKernel<<<n_ctas, kThreads, kSmemBytes, stream>>>(latent_map, rope_map, p);
+  MlaDecodeTcKernel<<<n_ctas, kThreads, kSmemBytes, stream>>>(latent_map, rope_map, q_map, p);
   if (int32_t rc = CheckCuda(cudaGetLastError(), "tcgen05 decode launch")) return rc;
   const int64_t rows = static_cast<int64_t>(a.batch) * kHeads;
   MlaFinalizeKernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(p, n_ctas);
@@ -789,3 +952,7 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
 }
 
 }  // namespace b200kv
+
+// Debug hook (not declared in the public header): device buffer of [ctas][64][8] clock64 stamps that a
+// library built with -DB200KV_TRACE fills per tile.
+extern "C" void b200kv_debug_set_trace(long long* device_buffer) { b200kv::g_trace = device_buffer; }

@@ -56,6 +56,21 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// Non-blocking probe of a phase.
+__device__ __forceinline__ bool MbarTestWait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // ---- fences ---------------------------------------------------------------------------------
 // Generic-proxy writes to shared memory (st.shared) become visible to the async proxy (TMA, MMA).
 __device__ __forceinline__ void FenceProxyAsyncShared() {
@@ -75,6 +90,15 @@ __device__ __forceinline__ void TmaLoad2D(uint32_t dst, const CUtensorMap* map, 
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void TmaLoad3D(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], "
+      "[%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
 
@@ -184,6 +208,12 @@ __device__ __forceinline__ bool NamedBarrierOr(uint32_t id, uint32_t threads, bo
       : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(threads)
       : "memory");
   return out != 0;
+}
+
+__device__ __forceinline__ float Ex2Approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ uint64_t GlobalTimerNs() {

@@ -1,0 +1,177 @@
+"""Decode attention on the device (both kernels) against the oracle and the golden vectors, within the
+path's tolerance: |err| <= 2e-3 + 1e-2*|ref| per element (2e-3 alone on benchmark-distributed inputs),
+lse within 1e-3. All calls go through the C ABI."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import b200kv
+import kvo
+import scenarios
+from gpu_util import run_decode
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import make_golden  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "attention_small.npz"))
+VARIANTS = [pytest.param(b200kv.DECODE_SIMT, id="simt"), pytest.param(b200kv.DECODE_TCGEN05, id="tcgen05")]
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("name", sorted(make_golden.CASES))
+def test_decode_matches_golden(name, variant):
+    q, pool, table, kv_len, bs, scale = make_golden.case_inputs(name)
+    out, lse = run_decode(q, pool, table, kv_len, bs, scale, variant)
+    scenarios.check_attention(out, lse, GOLDEN[name + "/out"].astype(np.float64),
+                              GOLDEN[name + "/lse"].astype(np.float64), what=name,
+                              strict_abs=not name.startswith("sharp"))
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_decode_matches_oracle_batched_permuted(variant):
+    """Four sequences of the B=32 x 4K configuration (context 4097 after the append), permuted tables."""
+    bs, B, n = 64, 4, 4097
+    blocks = B * scenarios.blocks_for(n, bs) + 7
+    kv_len = np.full(B, n, dtype=np.int32)
+    table = scenarios.build_tables(kv_len, bs, blocks)
+    pool = kvo.make_pool(blocks * bs)
+    q = kvo.make_q(B)
+    want, want_lse = kvo.mla_decode(q, pool, table, kv_len, bs, 1.0 / 24.0, use_double=True)
+    out, lse = run_decode(q, pool, table, kv_len, bs, 1.0 / 24.0, variant)
+    scenarios.check_attention(out, lse, kvo.bf16_to_f32(want).astype(np.float64), want_lse.astype(np.float64),
+                              abs_tol=2e-3, what="batched", strict_abs=True)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_decode_ragged_fragmented_with_empty_and_tiny_sequences(variant):
+    bs = 64
+    kv_len = np.array([0, 1, 31, 32, 33, 64, 65, 127, 128, 129, 1000, 2, 0, 517], dtype=np.int32)
+    blocks = int(sum(scenarios.blocks_for(int(n), bs) for n in kv_len)) + 9
+    table = scenarios.fragmented_tables(kv_len, bs, blocks)
+    pool = kvo.make_pool(blocks * bs)
+    # unowned blocks and the tails of last blocks hold NaN: they must never reach a result
+    owned = np.zeros(blocks * bs, dtype=bool)
+    for b, n in enumerate(kv_len):
+        j = np.arange(int(n))
+        owned[table[b, j // bs].astype(np.int64) * bs + j % bs] = True
+    pool[~owned] = 0x7FC1
+    q = kvo.make_q(len(kv_len), scale=4.0 / 24.0)
+    ref_out, ref_lse = scenarios.ref_attention_f64(q, pool, table, kv_len, bs, 1.0 / 24.0)
+    for max_ctas in (0, 3, 1):
+        out, lse = run_decode(q, pool, table, kv_len, bs, 1.0 / 24.0, variant, max_ctas=max_ctas)
+        scenarios.check_attention(out, lse, ref_out, ref_lse, what=f"ragged max_ctas={max_ctas}")
+        assert (out[kv_len == 0] == 0).all()
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_decode_online_softmax_stress(variant):
+    """A late dominant key (forces the running maximum to jump), large logits, and a one-token tail tile."""
+    bs, n = 64, 961  # 15 blocks + 1 token
+    blocks = 20
+    kv_len = np.array([n], dtype=np.int32)
+    table = scenarios.build_tables(kv_len, bs, blocks)
+    pool = kvo.make_pool(blocks * bs)
+    q = kvo.make_q(1, scale=16.0 / 24.0)
+    # make the last token nearly parallel to head 0's query, scaled up: its logit dwarfs the rest
+    qf = kvo.bf16_to_f32(q)[0, 0]
+    row = int(table[0, (n - 1) // bs]) * bs + (n - 1) % bs
+    pool[row] = kvo.f32_to_bf16((qf * 3.0).astype(np.float32))
+    mid = int(table[0, 5]) * bs + 17
+    pool[mid] = kvo.f32_to_bf16((kvo.bf16_to_f32(q)[0, 1] * 2.0).astype(np.float32))
+    ref_out, ref_lse = scenarios.ref_attention_f64(q, pool, table, kv_len, bs, 1.0 / 24.0)
+    out, lse = run_decode(q, pool, table, kv_len, bs, 1.0 / 24.0, variant)
+    scenarios.check_attention(out, lse, ref_out, ref_lse, what="stress")
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_decode_reference_layout_two_caches_bs128(variant):
+    """The reference's own geometry: separate latent [rows,512] and rope [rows,64] caches, block 128,
+    scale 1/sqrt(192)."""
+    bs, n, blocks = 128, 700, 8
+    kv_len = np.array([n, 129], dtype=np.int32)
+    table = scenarios.build_tables(kv_len, bs, blocks)
+    fused = kvo.make_pool(blocks * bs)
+    lat = np.ascontiguousarray(fused[:, :512])
+    rope = np.ascontiguousarray(fused[:, 512:])
+    q = kvo.make_q(2)
+    scale = float(1.0 / np.sqrt(192.0))
+    want, want_lse = kvo.mla_decode(q, lat, table, kv_len, bs, scale, use_double=True, rope_pool=rope)
+    out, lse = run_decode(q, lat, table, kv_len, bs, scale, variant, rope_pool_u16=rope)
+    scenarios.check_attention(out, lse, kvo.bf16_to_f32(want).astype(np.float64), want_lse.astype(np.float64),
+                              what="two caches", strict_abs=True)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_kv_range_shards_merge_to_whole(variant):
+    """KV-range split: each shard's un-normalised partial, merged by b200kv_lse_merge, equals the
+    single-device result (the multi-GPU long-context path run on one device)."""
+    bs, n, blocks = 64, 8192, 140
+    kv_len = np.array([n], dtype=np.int32)
+    table = scenarios.build_tables(kv_len, bs, blocks)
+    pool = kvo.make_pool(blocks * bs)
+    q = kvo.make_q(1, scale=6.0 / 24.0)
+    ref_out, ref_lse = scenarios.ref_attention_f64(q, pool, table, kv_len, bs, 1.0 / 24.0)
+    shards = 4
+    per = n // shards
+    parts = []
+    for r in range(shards):
+        po, pm, pl = run_decode(q, pool, table, np.array([per], np.int32), bs, 1.0 / 24.0, variant,
+                                kv_begin=np.array([r * per], np.int32), partial=True)
+        want_o, want_m, want_l = kvo.mla_decode(q, pool, table, np.array([per], np.int32), bs, 1.0 / 24.0,
+                                                kv_begin=np.array([r * per], np.int32), partial=True)
+        # partials may use different reference maxima: compare after normalising each
+        got_n = po / pl[..., None]
+        want_n = want_o / want_l[..., None]
+        assert np.abs(got_n - want_n).max() <= 2e-3 + 1e-2 * np.abs(want_n).max()
+        assert np.abs((pm + np.log(pl)) - (want_m + np.log(want_l))).max() <= 1e-3
+        parts.append((po, pm, pl))
+    po = torch.from_numpy(np.stack([p[0].reshape(-1, 512) for p in parts])).cuda()
+    pm = torch.from_numpy(np.stack([p[1].reshape(-1) for p in parts])).cuda()
+    pl = torch.from_numpy(np.stack([p[2].reshape(-1) for p in parts])).cuda()
+    out = torch.empty((64, 512), dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty(64, dtype=torch.float32, device="cuda")
+    b200kv.lse_merge(po, pm, pl, out, lse)
+    torch.cuda.synchronize()
+    from gpu_util import from_dev_bf16
+    scenarios.check_attention(from_dev_bf16(out).reshape(1, 64, 512), lse.cpu().numpy().reshape(1, 64), ref_out,
+                              ref_lse, what="merged shards")
+    # and the device merge equals the oracle's merge of the same partials
+    want_out, want_lse = kvo.lse_merge(po.cpu().numpy(), pm.cpu().numpy(), pl.cpu().numpy())
+    assert np.abs(kvo.bf16_to_f32(from_dev_bf16(out)) - kvo.bf16_to_f32(want_out)).max() <= 1e-3
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 1e-4
+
+
+def test_simt_handles_other_head_counts():
+    bs, blocks = 64, 8
+    kv_len = np.array([150, 64], dtype=np.int32)
+    table = scenarios.build_tables(kv_len, bs, blocks)
+    pool = kvo.make_pool(blocks * bs)
+    for heads in (8, 128):
+        q = kvo.make_q(2, heads=heads)
+        want, want_lse = kvo.mla_decode(q, pool, table, kv_len, bs, 1.0 / 24.0, use_double=True)
+        out, lse = run_decode(q, pool, table, kv_len, bs, 1.0 / 24.0, b200kv.DECODE_AUTO)
+        scenarios.check_attention(out, lse, kvo.bf16_to_f32(want).astype(np.float64), want_lse.astype(np.float64),
+                                  what=f"heads={heads}", strict_abs=True)
+
+
+def test_decode_reports_bad_block_without_faulting():
+    bs = 64
+    pool = kvo.make_pool(4 * bs)
+    table = np.array([[1, 99]], dtype=np.int32)
+    q = kvo.make_q(1)
+    from gpu_util import to_dev_bf16, to_dev_i32
+    for variant in (b200kv.DECODE_SIMT, b200kv.DECODE_TCGEN05):
+        qd, pd = to_dev_bf16(q), to_dev_bf16(pool)
+        out = torch.zeros((1, 64, 512), dtype=torch.bfloat16, device="cuda")
+        ws = torch.empty(b200kv.decode_workspace_bytes(1), dtype=torch.uint8, device="cuda")
+        status = b200kv.new_status()
+        b200kv.mla_decode(qd, b200kv.pool_view(pd), to_dev_i32(table), to_dev_i32([100]), bs, 1.0 / 24.0, out=out,
+                          workspace=ws, variant=variant, status=status)
+        torch.cuda.synchronize()
+        st = status.cpu().tolist()
+        assert st[0] == b200kv.DEV_BAD_BLOCK and st[1] == 0 and st[2] == 1 and st[3] == 99
