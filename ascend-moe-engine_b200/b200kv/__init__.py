@@ -319,6 +319,139 @@ class BlockPool:
         return out[:n].copy()
 
 
+class KvCache(Structure):
+    _fields_ = [
+        ("geometry", Reservation),
+        ("layers", c_int64),
+        ("block_size", c_int64),
+        ("max_seqs", c_int64),
+        ("block_table_handle", c_int64),
+        ("slot_mapping_handle", c_int64),
+        ("latent_handle", c_int64),
+        ("rope_handle", c_int64),
+    ]
+
+
+ARENA_DEVICE, ARENA_HOST_SIM = 0, 1
+
+
+class Arena:
+    """Three-phase static arena (reserve -> commit -> seal) behind the C ABI."""
+
+    def __init__(self, backend: int = ARENA_DEVICE):
+        lib.b200kv_arena_create.restype = c_void_p
+        lib.b200kv_arena_create.argtypes = [c_int32]
+        lib.b200kv_arena_destroy.argtypes = [c_void_p]
+        lib.b200kv_arena_destroy.restype = None
+        lib.b200kv_arena_reserve.restype = c_int64
+        lib.b200kv_arena_reserve.argtypes = [c_void_p, c_char_p, c_size_t, c_size_t]
+        lib.b200kv_arena_address.restype = c_void_p
+        lib.b200kv_arena_address.argtypes = [c_void_p, c_int64]
+        lib.b200kv_arena_offset.restype = c_int64
+        lib.b200kv_arena_offset.argtypes = [c_void_p, c_int64]
+        for name in ("reserved_bytes", "bytes"):
+            fn = getattr(lib, f"b200kv_arena_{name}")
+            fn.restype = c_size_t
+            fn.argtypes = [c_void_p]
+        for name in ("commit", "allocations", "commit_workspace", "seal", "sealed", "validate"):
+            fn = getattr(lib, f"b200kv_arena_{name}")
+            fn.restype = c_int32
+            fn.argtypes = [c_void_p]
+        lib.b200kv_arena_note_workspace.restype = c_int32
+        lib.b200kv_arena_note_workspace.argtypes = [c_void_p, c_uint64]
+        lib.b200kv_arena_workspace_fits.restype = c_int32
+        lib.b200kv_arena_workspace_fits.argtypes = [c_void_p, c_uint64]
+        lib.b200kv_arena_workspace.restype = c_void_p
+        lib.b200kv_arena_workspace.argtypes = [c_void_p]
+        lib.b200kv_arena_workspace_bytes.restype = c_uint64
+        lib.b200kv_arena_workspace_bytes.argtypes = [c_void_p]
+        lib.b200kv_kv_cache_reserve.restype = c_int32
+        lib.b200kv_kv_cache_reserve.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                                POINTER(KvCache)]
+        lib.b200kv_kv_cache_layer_view.restype = c_int32
+        lib.b200kv_kv_cache_layer_view.argtypes = [c_void_p, POINTER(KvCache), c_int64, POINTER(PoolView)]
+        self._h = lib.b200kv_arena_create(backend)
+        if not self._h:
+            raise B200KVError(ERR_INVALID, last_error())
+
+    def close(self):
+        if self._h:
+            lib.b200kv_arena_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def reserve(self, name: str, nbytes: int, align: int = 0) -> int:
+        handle = int(lib.b200kv_arena_reserve(self._h, name.encode(), nbytes, align))
+        if handle < 0:
+            raise B200KVError(-handle, last_error())
+        return handle
+
+    def commit(self):
+        check(lib.b200kv_arena_commit(self._h))
+
+    def address(self, handle: int) -> int:
+        addr = lib.b200kv_arena_address(self._h, handle)
+        if not addr:
+            raise B200KVError(ERR_INVALID, last_error())
+        return int(addr)
+
+    def offset(self, handle: int) -> int:
+        return int(lib.b200kv_arena_offset(self._h, handle))
+
+    @property
+    def reserved_bytes(self) -> int:
+        return int(lib.b200kv_arena_reserved_bytes(self._h))
+
+    @property
+    def nbytes(self) -> int:
+        return int(lib.b200kv_arena_bytes(self._h))
+
+    @property
+    def allocations(self) -> int:
+        return int(lib.b200kv_arena_allocations(self._h))
+
+    def note_workspace(self, nbytes: int):
+        check(lib.b200kv_arena_note_workspace(self._h, nbytes))
+
+    def commit_workspace(self):
+        check(lib.b200kv_arena_commit_workspace(self._h))
+
+    @property
+    def workspace(self) -> int:
+        return int(lib.b200kv_arena_workspace(self._h) or 0)
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(lib.b200kv_arena_workspace_bytes(self._h))
+
+    def workspace_fits(self, nbytes: int):
+        check(lib.b200kv_arena_workspace_fits(self._h, nbytes))
+
+    def seal(self):
+        check(lib.b200kv_arena_seal(self._h))
+
+    @property
+    def sealed(self) -> bool:
+        return bool(lib.b200kv_arena_sealed(self._h))
+
+    def validate(self):
+        check(lib.b200kv_arena_validate(self._h))
+
+    def reserve_kv_cache(self, max_context: int, block_size: int, layers: int = 43, max_seqs: int = 1,
+                         tokens_per_step: int = 1) -> KvCache:
+        cache = KvCache()
+        check(lib.b200kv_kv_cache_reserve(self._h, max_context, block_size, layers, max_seqs, tokens_per_step,
+                                          ctypes.byref(cache)))
+        return cache
+
+    def layer_view(self, cache: KvCache, layer: int) -> PoolView:
+        view = PoolView()
+        check(lib.b200kv_kv_cache_layer_view(self._h, ctypes.byref(cache), layer, ctypes.byref(view)))
+        return view
+
+
 def plan_reservation(max_context: int, block_size: int, layers: int = 43, max_seqs: int = 1,
                      tokens_per_step: int = 1) -> Reservation:
     out = Reservation()

@@ -198,6 +198,60 @@ int32_t b200kv_plan_reservation(int64_t max_context, int64_t block_size, int64_t
                                 int64_t tokens_per_step, b200kv_reservation* out);
 double b200kv_utilisation(int64_t active_tokens, int64_t blocks_per_layer, int64_t block_size);
 
+/* ------------------------------------------------------------------------------------------------
+ * Static arena and the KV cache carved from it.
+ * Replaces, for the KV spans, StaticMemoryArena::{Reserve, Commit, Address, NoteWorkspace,
+ * CommitWorkspace, AssertWorkspaceFits, Seal, ValidateAlignment}
+ * (src/memory/static_arena.cpp:88-124, 275-332) and the KV lines of StaticArenaManager
+ * (src/memory/static_arena_manager.cpp:298-300, 315-318). Same three phases and the same refusals:
+ * spans are 512-byte aligned by default, Commit performs ONE zero-filled device allocation, nothing
+ * can be reserved after Commit, and after Seal nothing can allocate at all. A refusal returns
+ * B200KV_ERR_INVALID (reserve: the negated code) with the reason in b200kv_last_error().
+ * backend B200KV_ARENA_HOST_SIM serves page-aligned host memory, like the reference's simulated
+ * device (src/core/device_ops.cpp:268-440), so that the latches can be tested without a GPU.
+ * ---------------------------------------------------------------------------------------------- */
+#define B200KV_ARENA_DEVICE 0
+#define B200KV_ARENA_HOST_SIM 1
+typedef struct b200kv_arena b200kv_arena;
+
+b200kv_arena* b200kv_arena_create(int32_t backend);
+void b200kv_arena_destroy(b200kv_arena* arena);
+/* Returns a handle >= 0, or the negated error code. align 0 = 512. */
+int64_t b200kv_arena_reserve(b200kv_arena* arena, const char* name, size_t bytes, size_t align);
+int32_t b200kv_arena_commit(b200kv_arena* arena);
+void* b200kv_arena_address(const b200kv_arena* arena, int64_t handle);
+int64_t b200kv_arena_offset(const b200kv_arena* arena, int64_t handle);
+size_t b200kv_arena_reserved_bytes(const b200kv_arena* arena);
+size_t b200kv_arena_bytes(const b200kv_arena* arena);
+int32_t b200kv_arena_allocations(const b200kv_arena* arena);
+int32_t b200kv_arena_note_workspace(b200kv_arena* arena, uint64_t bytes);
+int32_t b200kv_arena_commit_workspace(b200kv_arena* arena);
+void* b200kv_arena_workspace(const b200kv_arena* arena);
+uint64_t b200kv_arena_workspace_bytes(const b200kv_arena* arena);
+int32_t b200kv_arena_workspace_fits(const b200kv_arena* arena, uint64_t bytes);
+int32_t b200kv_arena_seal(b200kv_arena* arena);
+int32_t b200kv_arena_sealed(const b200kv_arena* arena);
+int32_t b200kv_arena_validate(const b200kv_arena* arena);
+
+typedef struct b200kv_kv_cache {
+  b200kv_reservation geometry;
+  int64_t layers;
+  int64_t block_size;
+  int64_t max_seqs;
+  int64_t block_table_handle; /* "kv.block_table": int32 [max_seqs][blocks_per_layer]     */
+  int64_t slot_mapping_handle; /* "kv.slot_mapping": int32 [tokens_per_step]              */
+  int64_t latent_handle;      /* "kv.latent_cache": bf16 [layers][blocks][block][512]      */
+  int64_t rope_handle;        /* "kv.rope_cache":   bf16 [layers][blocks][block][64]       */
+} b200kv_kv_cache;
+
+/* Reserves the four KV spans (RESERVE phase). */
+int32_t b200kv_kv_cache_reserve(b200kv_arena* arena, int64_t max_context, int64_t block_size, int64_t layers,
+                                int64_t max_seqs, int64_t tokens_per_step, b200kv_kv_cache* out);
+/* One layer's pool view after Commit: base + layer * blocks * block_size * width * 2
+ * (src/pipeline/pipeline.cpp:391-395). */
+int32_t b200kv_kv_cache_layer_view(const b200kv_arena* arena, const b200kv_kv_cache* cache, int64_t layer,
+                                   b200kv_pool_view* out);
+
 #ifdef __cplusplus
 }
 #endif
