@@ -1,0 +1,61 @@
+"""Multi-GPU plumbing for the two ways the path shards (one process per GPU, torch.distributed).
+
+Batched decode partitions whole sequences over ranks and needs no collective on the data path. A single
+long sequence is split by KV range: each rank attends over its block range, the per-rank partial
+(m, l, O) triples are all-gathered, and every rank merges them with the log-sum-exp reduction.
+The partition arithmetic is the C library's (b200kv_partition_sequences, b200kv_split_kv_range).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int32, c_int64, c_void_p
+
+import numpy as np
+
+from . import check, lib, lse_merge
+
+lib.b200kv_partition_sequences.restype = c_int32
+lib.b200kv_partition_sequences.argtypes = [c_void_p, c_int32, c_int32, c_void_p, c_void_p]
+lib.b200kv_split_kv_range.restype = c_int32
+lib.b200kv_split_kv_range.argtypes = [c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]
+
+
+def partition_sequences(kv_len, n_ranks: int):
+    """Returns (rank_of_seq int32 [n], tokens_per_rank int64 [n_ranks])."""
+    lens = np.ascontiguousarray(kv_len, dtype=np.int32)
+    ranks = np.empty(len(lens), dtype=np.int32)
+    loads = np.zeros(n_ranks, dtype=np.int64)
+    check(lib.b200kv_partition_sequences(lens.ctypes.data, len(lens), n_ranks, ranks.ctypes.data, loads.ctypes.data))
+    return ranks, loads
+
+
+def split_kv_range(kv_len: int, block_size: int, n_ranks: int, rank: int):
+    """Returns (begin, length) of `rank`'s contiguous block range of a kv_len-token sequence."""
+    begin, length = c_int32(), c_int32()
+    check(lib.b200kv_split_kv_range(kv_len, block_size, n_ranks, rank, ctypes.byref(begin), ctypes.byref(length)))
+    return int(begin.value), int(length.value)
+
+
+def all_gather_partials(partial_o, partial_m, partial_l, group=None):
+    """All-gathers one rank's partial (o [rows,512] fp32, m [rows], l [rows]) into stacked
+    ([world, rows, 512], [world, rows], [world, rows]) tensors on every rank. One collective moves all
+    three: they travel as a single [rows, 514] buffer per rank (131,584 bytes at 64 rows)."""
+    import torch
+    import torch.distributed as dist
+
+    rows = partial_m.numel()
+    packed = torch.cat([partial_o.reshape(rows, -1), partial_m.reshape(rows, 1), partial_l.reshape(rows, 1)], dim=1)
+    world = dist.get_world_size(group)
+    flat = torch.empty((world * rows, packed.shape[1]), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(flat, packed.contiguous(), group=group)
+    gathered = flat.view(world, rows, packed.shape[1])
+    width = partial_o.reshape(rows, -1).shape[1]
+    return gathered[:, :, :width].contiguous(), gathered[:, :, width].contiguous(), gathered[:, :, width + 1].contiguous()
+
+
+def merge_across_ranks(partial_o, partial_m, partial_l, out, lse=None, group=None, stream=None):
+    """KV-range split epilogue on the device: all-gather (NCCL) then the LSE merge kernel; every rank
+    ends with the full result in `out` (bf16 [rows, 512]) and `lse`."""
+    o, m, l = all_gather_partials(partial_o, partial_m, partial_l, group)
+    lse_merge(o, m, l, out, lse, stream=stream)
+    return out

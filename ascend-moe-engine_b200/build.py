@@ -25,6 +25,7 @@ SOURCES = [
     "mla_decode_tc.cu",
     "kv_block_pool.cpp",
     "kv_arena.cpp",
+    "kv_partition.cpp",
     "aclnn_shim.cpp",
     "no_alloc.cu",
 ]

@@ -680,8 +680,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // Merges the partial segments of every sequence that straddles CTAs, and writes the result of empty
-// sequences. One warp per (sequence, head). Recomputes the flat partition arithmetic of the decode
+// sequences. One warp per (sequence, head); grid-wide, so the partials (a few tens of MB, mostly still
+// in L2) are pulled by every SM at once. Recomputes the flat partition arithmetic of the decode
 // kernel: sequence b owns tiles [P_b, P_b + n_b) of T; CTA c owns [c*T/G, (c+1)*T/G).
+// Loads are arranged in three independent waves (lengths, then every part's (m, l) at once with one
+// part per lane, then every part's row with up to eight parts in flight) instead of a chain per part.
 __global__ void __launch_bounds__(256)
     MlaFinalizeKernel(TcParams p, int32_t n_ctas) {
   const int lane = threadIdx.x & 31;
@@ -713,28 +716,73 @@ __global__ void __launch_bounds__(256)
     const long long c_first = ((before + 1) * n_ctas - 1) / total;
     const long long c_last = ((before + mine) * n_ctas - 1) / total;
     if (c_first == c_last) return;  // written directly by the decode kernel
-    for (long long c = c_first; c <= c_last; ++c) {
-      const long long lo = total * c / n_ctas;
-      if (total * (c + 1) / n_ctas == lo) continue;  // a CTA with an empty range wrote nothing
-      const int slot = static_cast<int>(c * 2 + (lo >= before ? 0 : 1));
-      if (p.ws_l[slot * kHeads + h] > 0.0f) big = fmaxf(big, p.ws_m[slot * kHeads + h]);
-    }
-    for (long long c = c_first; c <= c_last; ++c) {
-      const long long lo = total * c / n_ctas;
-      if (total * (c + 1) / n_ctas == lo) continue;
-      const int slot = static_cast<int>(c * 2 + (lo >= before ? 0 : 1));
-      const float l = p.ws_l[slot * kHeads + h];
-      if (!(l > 0.0f)) continue;
-      const float w = expf(p.ws_m[slot * kHeads + h] - big);
-      sum_l += l * w;
-      const float4* src = reinterpret_cast<const float4*>(p.ws_o + (static_cast<int64_t>(slot) * kHeads + h) * kLatent);
+    for (long long c0 = c_first; c0 <= c_last; c0 += 32) {
+      // Wave 2: lane k takes CTA c0 + k: its slot, m and l (slot < 0: no part from that CTA).
+      const long long c = c0 + lane;
+      int slot = -1;
+      float m = -INFINITY, l = 0.0f;
+      if (c <= c_last) {
+        const long long lo = total * c / n_ctas;
+        if (total * (c + 1) / n_ctas != lo) {  // a CTA with an empty range wrote nothing
+          slot = static_cast<int>(c * 2 + (lo >= before ? 0 : 1));
+          l = p.ws_l[slot * kHeads + h];
+          m = p.ws_m[slot * kHeads + h];
+        }
+      }
+      if (!(l > 0.0f)) {
+        slot = -1;
+        m = -INFINITY;
+      }
+      float chunk_max = m;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, off));
+      const float new_big = fmaxf(big, chunk_max);
+      if (new_big == -INFINITY) continue;
+      // Rescale what earlier chunks of 32 parts accumulated (only sequences cut over more than 32 CTAs).
+      const float carry = big == -INFINITY ? 0.0f : expf(big - new_big);
+      big = new_big;
+      sum_l *= carry;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float4 v = src[lane + 32 * i];
-        acc[i].x = fmaf(v.x, w, acc[i].x);
-        acc[i].y = fmaf(v.y, w, acc[i].y);
-        acc[i].z = fmaf(v.z, w, acc[i].z);
-        acc[i].w = fmaf(v.w, w, acc[i].w);
+        acc[i].x *= carry;
+        acc[i].y *= carry;
+        acc[i].z *= carry;
+        acc[i].w *= carry;
+      }
+      const float w = slot >= 0 ? expf(m - big) : 0.0f;
+      float lw = l * w;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, off);
+      sum_l += lw;
+      // Wave 3: rows of the parts, eight parts (32 float4 per lane) in flight at a time.
+      const long long left = c_last - c0 + 1;
+      const int n_here = left < 32 ? static_cast<int>(left) : 32;
+      for (int k0 = 0; k0 < n_here; k0 += 8) {
+        float4 v[8][4];
+        float wk[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int src = (k0 + k) & 31;
+          const int slot_k = __shfl_sync(0xffffffffu, slot, src);
+          wk[k] = __shfl_sync(0xffffffffu, w, src);
+          if (k0 + k >= n_here || slot_k < 0) wk[k] = 0.0f;
+          const float4* rowp =
+              reinterpret_cast<const float4*>(p.ws_o + (static_cast<int64_t>(slot_k < 0 ? 0 : slot_k) * kHeads + h) * kLatent);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            v[k][i] = wk[k] != 0.0f ? rowp[lane + 32 * i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[i].x = fmaf(v[k][i].x, wk[k], acc[i].x);
+            acc[i].y = fmaf(v[k][i].y, wk[k], acc[i].y);
+            acc[i].z = fmaf(v[k][i].z, wk[k], acc[i].z);
+            acc[i].w = fmaf(v[k][i].w, wk[k], acc[i].w);
+          }
+        }
       }
     }
   }

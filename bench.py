@@ -25,7 +25,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "ascend-moe-engine_b200"))
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-LAYERS = 43
+LAYERS = 43           # overridden by --layers for profiling captures
 BATCH = 32
 CONTEXT = 4096          # tokens attended per sequence, including the one appended this step
 BLOCK = 64
@@ -266,7 +266,7 @@ def check_against_oracle(torch, b200kv, wl: Workload, variant) -> float:
 
     import kvo
 
-    layer, b = 7, 5
+    layer, b = min(7, LAYERS - 1), 5
     wl.step_resident(variant)
     torch.cuda.synchronize()
     rows = (wl.table_np[b].astype(np.int64)[:, None] * BLOCK + np.arange(BLOCK)[None, :]).reshape(-1)
@@ -385,12 +385,22 @@ def run_b200_arm(args):
         attention_only()
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    g_step = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g_step):
-        wl.step_resident(variant)
-    g_attn = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g_attn):
-        attention_only()
+    class Eager:
+        def __init__(self, fn):
+            self.fn = fn
+
+        def replay(self):
+            self.fn()
+
+    if args.no_graph:
+        g_step, g_attn = Eager(lambda: wl.step_resident(variant)), Eager(attention_only)
+    else:
+        g_step = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_step):
+            wl.step_resident(variant)
+        g_attn = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_attn):
+            attention_only()
     launches_per_step = LAYERS * 3  # append, decode, finalize/merge per layer
 
     # ---- device-resident timing (value) ----
@@ -423,81 +433,85 @@ def run_b200_arm(args):
     if st[0] != 0:
         raise RuntimeError(f"device status word reports {st}")
 
-    # ---- end-to-end timing through the C ABI with host buffers (e2e) ----
-    h_q = torch.empty((LAYERS, BATCH, HEADS, ROW), dtype=torch.bfloat16).pin_memory()
-    h_new = torch.empty((LAYERS, BATCH, ROW), dtype=torch.bfloat16).pin_memory()
-    h_slots = torch.from_numpy(wl.slots_np).pin_memory()
-    h_out = torch.empty((LAYERS, BATCH, HEADS, LATENT), dtype=torch.bfloat16).pin_memory()
-    h_q.copy_(wl.q.cpu())
-    h_new.copy_(wl.new_rows.cpu())
-    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-    d_q = [torch.empty_like(wl.q[0]) for _ in range(2)]
-    d_new = [torch.empty_like(wl.new_rows[0]) for _ in range(2)]
-    d_out = [torch.empty_like(wl.out[0]) for _ in range(2)]
-    d_slots = torch.empty_like(wl.slots)
+    def measure_e2e():
+        # ---- end-to-end timing through the C ABI with host buffers (e2e) ----
+        h_q = torch.empty((LAYERS, BATCH, HEADS, ROW), dtype=torch.bfloat16).pin_memory()
+        h_new = torch.empty((LAYERS, BATCH, ROW), dtype=torch.bfloat16).pin_memory()
+        h_slots = torch.from_numpy(wl.slots_np).pin_memory()
+        h_out = torch.empty((LAYERS, BATCH, HEADS, LATENT), dtype=torch.bfloat16).pin_memory()
+        h_q.copy_(wl.q.cpu())
+        h_new.copy_(wl.new_rows.cpu())
+        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+        d_q = [torch.empty_like(wl.q[0]) for _ in range(2)]
+        d_new = [torch.empty_like(wl.new_rows[0]) for _ in range(2)]
+        d_out = [torch.empty_like(wl.out[0]) for _ in range(2)]
+        d_slots = torch.empty_like(wl.slots)
 
-    def step_e2e():
-        # Layer l's inputs are uploaded on one stream while layer l-1 computes and layer l-2's result is
-        # read back on a third; two buffers per direction. Every byte the step consumes starts in pinned
-        # host memory and every result ends there.
-        compute = torch.cuda.current_stream()
-        in_ready = [None, None]
-        in_free = [None, None]
-        out_ready = [None, None]
-        out_free = [None, None]
-        copy_in.wait_stream(compute)
-        copy_out.wait_stream(compute)
-        with torch.cuda.stream(copy_in):
-            d_slots.copy_(h_slots, non_blocking=True)
-        for layer in range(LAYERS):
-            s = layer & 1
+        def step_e2e():
+            # Layer l's inputs are uploaded on one stream while layer l-1 computes and layer l-2's result is
+            # read back on a third; two buffers per direction. Every byte the step consumes starts in pinned
+            # host memory and every result ends there.
+            compute = torch.cuda.current_stream()
+            in_ready = [None, None]
+            in_free = [None, None]
+            out_ready = [None, None]
+            out_free = [None, None]
+            copy_in.wait_stream(compute)
+            copy_out.wait_stream(compute)
             with torch.cuda.stream(copy_in):
-                if in_free[s] is not None:
-                    copy_in.wait_event(in_free[s])
-                d_q[s].copy_(h_q[layer], non_blocking=True)
-                d_new[s].copy_(h_new[layer], non_blocking=True)
-                in_ready[s] = torch.cuda.Event()
-                in_ready[s].record(copy_in)
-            compute.wait_event(in_ready[s])
-            if out_free[s] is not None:
-                compute.wait_event(out_free[s])
-            wl.kv.append(wl.views[layer], d_new[s][:, :LATENT], d_new[s][:, LATENT:], d_slots, status=wl.status)
-            wl.kv.mla_decode(d_q[s], wl.views[layer], wl.table, wl.kv_len, BLOCK, SCALE, out=d_out[s],
-                             workspace=wl.ws, variant=variant, status=wl.status)
-            in_free[s] = torch.cuda.Event()
-            in_free[s].record(compute)
-            out_ready[s] = torch.cuda.Event()
-            out_ready[s].record(compute)
-            with torch.cuda.stream(copy_out):
-                copy_out.wait_event(out_ready[s])
-                h_out[layer].copy_(d_out[s], non_blocking=True)
-                out_free[s] = torch.cuda.Event()
-                out_free[s].record(copy_out)
-        compute.wait_stream(copy_in)
-        compute.wait_stream(copy_out)
+                d_slots.copy_(h_slots, non_blocking=True)
+            for layer in range(LAYERS):
+                s = layer & 1
+                with torch.cuda.stream(copy_in):
+                    if in_free[s] is not None:
+                        copy_in.wait_event(in_free[s])
+                    d_q[s].copy_(h_q[layer], non_blocking=True)
+                    d_new[s].copy_(h_new[layer], non_blocking=True)
+                    in_ready[s] = torch.cuda.Event()
+                    in_ready[s].record(copy_in)
+                compute.wait_event(in_ready[s])
+                if out_free[s] is not None:
+                    compute.wait_event(out_free[s])
+                wl.kv.append(wl.views[layer], d_new[s][:, :LATENT], d_new[s][:, LATENT:], d_slots, status=wl.status)
+                wl.kv.mla_decode(d_q[s], wl.views[layer], wl.table, wl.kv_len, BLOCK, SCALE, out=d_out[s],
+                                 workspace=wl.ws, variant=variant, status=wl.status)
+                in_free[s] = torch.cuda.Event()
+                in_free[s].record(compute)
+                out_ready[s] = torch.cuda.Event()
+                out_ready[s].record(compute)
+                with torch.cuda.stream(copy_out):
+                    copy_out.wait_event(out_ready[s])
+                    h_out[layer].copy_(d_out[s], non_blocking=True)
+                    out_free[s] = torch.cuda.Event()
+                    out_free[s].record(copy_out)
+            compute.wait_stream(copy_in)
+            compute.wait_stream(copy_out)
 
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        step_e2e()
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    g_e2e = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g_e2e):
-        step_e2e()
-    for _ in range(max(1, args.warmup // 2)):
-        g_e2e.replay()
-    barrier()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        g_e2e.replay()
-    e1.record()
-    barrier()
-    e2e_ms_total = e0.elapsed_time(e1)
-    # the read-back result is the device result, bit for bit
-    if not torch.equal(h_out[LAYERS - 1].view(torch.int16), wl.out[LAYERS - 1].cpu().view(torch.int16)):
-        raise RuntimeError("bench self-check failed: end-to-end output differs from the resident run")
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step_e2e()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g_e2e = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_e2e):
+            step_e2e()
+        for _ in range(max(1, args.warmup // 2)):
+            g_e2e.replay()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            g_e2e.replay()
+        e1.record()
+        barrier()
+        e2e_ms_total = e0.elapsed_time(e1)
+        # the read-back result is the device result, bit for bit
+        if not torch.equal(h_out[LAYERS - 1].view(torch.int16), wl.out[LAYERS - 1].cpu().view(torch.int16)):
+            raise RuntimeError("bench self-check failed: end-to-end output differs from the resident run")
+        return e2e_ms_total
+
+    e2e_ms_total = float('nan') if args.skip_e2e else measure_e2e()
     h2d = LAYERS * (BATCH * HEADS * ROW * 2 + BATCH * ROW * 2) + BATCH * 4
     d2h = LAYERS * BATCH * HEADS * LATENT * 2
 
@@ -506,9 +520,10 @@ def run_b200_arm(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms_total, attn_ms = (float(x) for x in times.cpu())
 
-    move = measure_move_kernels(torch, b200kv, wl, hbm_peak) if rank == 0 else None
+    move = measure_move_kernels(torch, b200kv, wl, hbm_peak) if (rank == 0 and not args.skip_move) else None
     if rank == 0:
-        cpu_value, cpu_sample_desc, cpu_threads = cpu_sample() if world == 1 else (None, "rank 0 at N=1 only", 0)
+        cpu_value, cpu_sample_desc, cpu_threads = (cpu_sample() if (world == 1 and not args.skip_cpu)
+                                                    else (None, "skipped (rank 0 at N=1 only)", 0))
         ms_per_step = ms_total / args.steps
         value = world * BATCH / (ms_per_step * 1e-3)
         achieved = ATTN_BYTES_PER_LAUNCH / (attn_ms * 1e-3) * 1e-9
@@ -532,9 +547,9 @@ def run_b200_arm(args):
             "move_kernels": move,
             "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": cpu_threads, "kind": "port",
                              "sample": cpu_sample_desc},
-            "e2e": {"value": world * BATCH / (e2e_ms_total / args.steps * 1e-3), "unit": "tokens/s",
+            "e2e": {"value": None if args.skip_e2e else world * BATCH / (e2e_ms_total / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms_total / args.steps},
+                    "ms_per_step": None if args.skip_e2e else e2e_ms_total / args.steps},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
@@ -550,7 +565,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--variant", default="auto", choices=["auto", "simt", "tcgen05"])
+    ap.add_argument("--layers", type=int, default=43, help="fewer layers give a small case for profiler captures")
+    ap.add_argument("--no-graph", action="store_true", help="launch step by step instead of replaying CUDA graphs")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-move", action="store_true")
     args = ap.parse_args()
+    global LAYERS
+    LAYERS = args.layers
     if args.impl == "reference":
         run_reference_arm(args)
     else:

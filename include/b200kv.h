@@ -252,6 +252,19 @@ int32_t b200kv_kv_cache_reserve(b200kv_arena* arena, int64_t max_context, int64_
 int32_t b200kv_kv_cache_layer_view(const b200kv_arena* arena, const b200kv_kv_cache* cache, int64_t layer,
                                    b200kv_pool_view* out);
 
+/* ------------------------------------------------------------------------------------------------
+ * Multi-GPU work partition (host). No counterpart in the reference, which runs on one device
+ * (include/moe/core/config.hpp:280).
+ * ---------------------------------------------------------------------------------------------- */
+/* Batched decode: whole sequences to ranks by longest-processing-time greedy on context length.
+ * rank_of_seq [n_seqs] receives each sequence's rank; tokens_per_rank [n_ranks] (or null) the loads. */
+int32_t b200kv_partition_sequences(const int32_t* kv_len, int32_t n_seqs, int32_t n_ranks, int32_t* rank_of_seq,
+                                   int64_t* tokens_per_rank);
+/* One long sequence: shard `rank` is a contiguous block range; *begin is a multiple of block_size and
+ * feeds b200kv_decode_args.kv_begin, *len feeds kv_len. The shard partials merge with b200kv_lse_merge. */
+int32_t b200kv_split_kv_range(int32_t kv_len, int32_t block_size, int32_t n_ranks, int32_t rank, int32_t* begin,
+                              int32_t* len);
+
 #ifdef __cplusplus
 }
 #endif
