@@ -236,6 +236,33 @@ def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: f
     check(lib.b200kv_mla_decode(ctypes.byref(args), _stream_handle(stream), _ptr(status)))
 
 
+def mla_decode_static(q, view: PoolView, block_table, kv_len, block_size: int, scale: float, out=None, lse=None,
+                      kv_begin=None, partial=None, max_ctas: int = 0, status=None, stream=None) -> None:
+    """b200kv_mla_decode_static: the same attention, with the library's built-in scratch instead of a
+    workspace tensor; nothing is allocated on the device by the call."""
+    lib.b200kv_mla_decode_static.restype = c_int32
+    lib.b200kv_mla_decode_static.argtypes = [POINTER(DecodeArgs), c_void_p, c_void_p]
+    args = DecodeArgs()
+    args.q = _ptr(q)
+    args.q_seq_stride = q.stride(0)
+    args.q_head_stride = q.stride(1)
+    args.pool = view
+    args.block_table = _ptr(block_table)
+    args.max_blocks = block_table.stride(0)
+    args.kv_len = _ptr(kv_len)
+    args.kv_begin = _ptr(kv_begin)
+    args.batch = q.shape[0]
+    args.heads = q.shape[1]
+    args.block_size = block_size
+    args.scale = scale
+    args.out = _ptr(out)
+    args.lse = _ptr(lse)
+    if partial is not None:
+        args.partial_o, args.partial_m, args.partial_l = (_ptr(t) for t in partial)
+    args.max_ctas = max_ctas
+    check(lib.b200kv_mla_decode_static(ctypes.byref(args), _stream_handle(stream), _ptr(status)))
+
+
 def lse_merge(partial_o, partial_m, partial_l, out, lse=None, stream=None) -> None:
     """partial_o fp32 [P, rows, 512], partial_m / partial_l fp32 [P, rows] -> out bf16 [rows, 512]."""
     n_parts, rows = int(partial_m.shape[0]), int(partial_m.shape[1])

@@ -134,6 +134,22 @@ size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t m
 int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* stream, b200kv_status_word* status);
 
 /*
+ * Decode attention without a caller workspace and without any device allocation. No counterpart in
+ * the reference. Same arguments and results as b200kv_mla_decode (args->workspace, workspace_bytes and
+ * variant are ignored; the tensor-core kernel runs, so the geometry it needs applies: 64 heads,
+ * block_size % 64 == 0, 16-byte aligned q). The partial-result scratch is a fixed array inside the
+ * library's device image, b200kv_mla_decode_static_scratch_bytes() bytes (8,421,376) on every GPU that
+ * loads the library, held until the process exits. It covers grids of up to B200KV_STATIC_MAX_CTAS
+ * CTAs: args->max_ctas = 0 means that many; a larger max_ctas is refused with B200KV_ERR_INVALID.
+ * The first call on a device looks up the array's address (cudaGetSymbolAddress): make that first
+ * call outside any stream capture. All calls share the one array, so two calls that overlap on the
+ * GPU (different streams, no ordering between them) race; calls on one stream are safe.
+ */
+#define B200KV_STATIC_MAX_CTAS 32
+size_t b200kv_mla_decode_static_scratch_bytes(void);
+int32_t b200kv_mla_decode_static(const b200kv_decode_args* args, void* stream, b200kv_status_word* status);
+
+/*
  * LSE merge of n_parts shard partials (the reduction that follows the KV-range split):
  *   M = max_r m_r, L = sum_r l_r e^{m_r-M}, out = sum_r O_r e^{m_r-M} / L, lse = M + log L.
  * partial_o: fp32 [n_parts][rows][512]; partial_m, partial_l: fp32 [n_parts][rows]; rows = batch*heads.
