@@ -27,6 +27,7 @@
 // word, raises a CTA-wide abort flag, waits (bounded) for its own TMA loads, frees TMEM and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -47,7 +48,7 @@ constexpr int kStageBytes = 9 * kSlabBytes;             // 73,728
 constexpr int kQSlabBytes = kHeads * 128;               // 8,192
 constexpr int kQBytes = 9 * kQSlabBytes;                // 73,728
 constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemColS = 256;                     // S buffers at columns 256 and 256 + kTile
 constexpr float kRescaleThreshold = 8.0f;               // log2 units: rescale O only when max grows by > 2^8
@@ -61,7 +62,7 @@ constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + slack for the man
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 
 struct Misc {
-  uint64_t kv_full[kStages];
+  uint64_t kv_full[kStages][3];  // one per group of three slabs, so QK can start on a tile's first third
   uint64_t kv_empty[kStages];
   uint64_t s_full[2];
   uint64_t s_empty[2];
@@ -70,7 +71,7 @@ struct Misc {
   uint64_t q_empty;
   uint64_t o_full;
   uint64_t o_empty;
-  uint64_t drain;
+  uint64_t drain[2];
   uint32_t tmem_base;
   int32_t abort_flag;
   int32_t start_seq;
@@ -213,25 +214,72 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto bar = [&](const uint64_t* b) { return ptx::SmemAddr(b); };
 
   // ---- setup ----------------------------------------------------------------------------------
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      ptx::MbarInit(bar(&misc->kv_full[s]), 1);
-      ptx::MbarInit(bar(&misc->kv_empty[s]), 1);
-      ptx::MbarInit(bar(&misc->p_full[s]), kSoftmaxThreads);
+  if (threadIdx.x == 0) TRACE(63, 0);
+
+  // One tile's nine TMA loads (eight latent slabs, one rope slab) into stage g % kStages.
+  auto issue_tile = [&](int seq, int begin, int t, int g) {
+    const int stage = g % kStages;
+    const int tok = begin + t * kTile;
+    const int64_t table_col = tok / p.block_size;
+    const int64_t block =
+        table_col < p.max_blocks ? p.block_table[static_cast<int64_t>(seq) * p.max_blocks + table_col] : -1;
+    int64_t row = block * p.block_size + tok % p.block_size;
+    if (block < 0 || row + kTile > p.pool_rows) {
+      RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, tok / p.block_size, static_cast<int32_t>(block));
+      row = 0;  // keep the pipeline moving on addressable memory; the status word tells the host
     }
-    for (int s = 0; s < 2; ++s) {
-      ptx::MbarInit(bar(&misc->s_full[s]), 1);
-      ptx::MbarInit(bar(&misc->s_empty[s]), kSoftmaxThreads);
+    const uint32_t dst = kv_addr + stage * kStageBytes;
+    TRACE(g, 0);
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      const uint32_t full = bar(&misc->kv_full[stage][k]);
+      ptx::MbarArriveExpectTx(full, 3 * kSlabBytes);
+#pragma unroll
+      for (int c = 3 * k; c < 3 * k + 3; ++c) {
+        if (c < 8) {
+          ptx::TmaLoad2D(dst + c * kSlabBytes, &latent_map, 64 * c, static_cast<int32_t>(row), full);
+        } else {
+          ptx::TmaLoad2D(dst + 8 * kSlabBytes, &rope_map, 0, static_cast<int32_t>(row), full);
+        }
+      }
     }
-    ptx::MbarInit(bar(&misc->q_full), 1);
-    ptx::MbarInit(bar(&misc->q_empty), 1);
-    ptx::MbarInit(bar(&misc->o_full), 1);
-    ptx::MbarInit(bar(&misc->o_empty), kSoftmaxThreads);
-    ptx::MbarInit(bar(&misc->drain), 1);
-    misc->abort_flag = 0;
-    ptx::FenceBarrierInit();
-  }
-  if (warp == 0) {
+  };
+  // Q of one sequence: nine 64-column slabs of 64 head rows.
+  auto issue_q = [&](int seq) {
+    const uint32_t qbar = bar(&misc->q_full);
+    ptx::MbarArriveExpectTx(qbar, kQBytes);
+#pragma unroll
+    for (int c = 0; c < 9; ++c) ptx::TmaLoad3D(q_addr + c * kQSlabBytes, &q_map, 64 * c, 0, seq, qbar);
+  };
+
+  int pre_issued = 0;  // tiles the producer put in flight before the CTA-wide setup barrier
+  if (warp == 4) {
+    // The producer warp initialises the barriers, finds this CTA's slice of the flat tile list and
+    // puts Q and the first tiles in flight at once: the other warps' setup (TMEM allocation, the
+    // barrier below) then overlaps the first loads' latency instead of preceding it.
+    if (lane == 0) {
+      for (int s = 0; s < kStages; ++s) {
+        for (int k = 0; k < 3; ++k) ptx::MbarInit(bar(&misc->kv_full[s][k]), 1);
+        ptx::MbarInit(bar(&misc->kv_empty[s]), 1);
+        ptx::MbarInit(bar(&misc->p_full[s]), kSoftmaxThreads);
+      }
+      for (int s = 0; s < 2; ++s) {
+        ptx::MbarInit(bar(&misc->s_full[s]), 1);
+        ptx::MbarInit(bar(&misc->s_empty[s]), kSoftmaxThreads);
+      }
+      ptx::MbarInit(bar(&misc->q_full), 1);
+      ptx::MbarInit(bar(&misc->q_empty), 1);
+      ptx::MbarInit(bar(&misc->o_full), 1);
+      ptx::MbarInit(bar(&misc->o_empty), kSoftmaxThreads);
+      ptx::MbarInit(bar(&misc->drain[0]), 1);
+      ptx::MbarInit(bar(&misc->drain[1]), 1);
+      misc->abort_flag = 0;
+      ptx::FenceBarrierInit();
+      ptx::PrefetchTensorMap(&latent_map);
+      ptx::PrefetchTensorMap(&rope_map);
+      ptx::PrefetchTensorMap(&q_map);
+    }
+    __syncwarp();
     // This CTA's slice of the flat tile list: total, then the sequence holding the first tile.
     long long total = 0;
     for (int b = lane; b < p.batch; b += 32) total += TilesOf(p.kv_len[b]);
@@ -239,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
     const long long lo = total * cta / n_ctas;
     const long long hi = total * (cta + 1) / n_ctas;
-    int start_seq = p.batch, start_tile = 0;
+    int start_seq = p.batch, start_tile = 0, start_seq_tiles = 0;
     long long before = 0;
     for (int b0 = 0; b0 < p.batch && start_seq == p.batch; b0 += 32) {
       const int b = b0 + lane;
@@ -258,6 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const long long mine_src = __shfl_sync(0xffffffffu, mine, src);
         start_seq = b0 + src;
         start_tile = static_cast<int>(lo - (before + incl_src - mine_src));
+        start_seq_tiles = static_cast<int>(mine_src);
       }
       before += __shfl_sync(0xffffffffu, incl, 31);
     }
@@ -265,21 +314,26 @@ __global__ void __launch_bounds__(kThreads, 1)
       misc->start_seq = start_seq;
       misc->start_tile = start_tile;
       misc->n_tiles = static_cast<int>(hi - lo);
+      if (hi > lo && start_seq < p.batch) {
+        issue_q(start_seq);
+        const int begin = p.kv_begin ? p.kv_begin[start_seq] : 0;
+        const int t_end = min(start_seq_tiles, start_tile + static_cast<int>(hi - lo));
+        for (int t = start_tile; t < t_end && pre_issued < kStages; ++t, ++pre_issued) {
+          issue_tile(start_seq, begin, t, pre_issued);
+        }
+      }
     }
+    __syncwarp();
   }
   if (warp == 5) {
     ptx::TmemAlloc(ptx::SmemAddr(&misc->tmem_base), kTmemCols);
     ptx::TmemRelinquish();
   }
-  if (warp == 4 && lane == 0) {
-    ptx::PrefetchTensorMap(&latent_map);
-    ptx::PrefetchTensorMap(&rope_map);
-    ptx::PrefetchTensorMap(&q_map);
-  }
   ptx::TcFenceBeforeSync();
   __syncthreads();
   ptx::TcFenceAfterSync();
 
+  if (threadIdx.x == 0) TRACE(63, 1);
   const uint32_t tmem = misc->tmem_base;
   const int start_seq = misc->start_seq;
   const int start_tile = misc->start_tile;
@@ -294,44 +348,22 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       int seg = 0;
       while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
-        // Q of this segment's sequence: nine 64-column slabs of 64 head rows, once the previous
-        // segment's last QK has finished reading the buffer.
+        // Q of this segment's sequence, once the previous segment's last QK has finished reading the
+        // buffer (the first segment's Q went out before the setup barrier).
         if (seg > 0) {
           ok = BoundedWait(bar(&misc->q_empty), (seg - 1) & 1, misc, p.status, 11);
           if (!ok) break;
-        }
-        {
-          const uint32_t qbar = bar(&misc->q_full);
-          ptx::MbarArriveExpectTx(qbar, kQBytes);
-#pragma unroll
-          for (int c = 0; c < 9; ++c) ptx::TmaLoad3D(q_addr + c * kQSlabBytes, &q_map, 64 * c, 0, seq, qbar);
+          issue_q(seq);
         }
         ++seg;
         const int begin = p.kv_begin ? p.kv_begin[seq] : 0;
         for (int t = t_lo; t < t_hi; ++t, ++g) {
-          const int stage = g % kStages;
+          if (g < pre_issued) continue;
           if (g >= kStages) {
-            ok = BoundedWait(bar(&misc->kv_empty[stage]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
+            ok = BoundedWait(bar(&misc->kv_empty[g % kStages]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
             if (!ok) break;
           }
-          const int tok = begin + t * kTile;
-          const int64_t table_col = tok / p.block_size;
-          const int64_t block =
-              table_col < p.max_blocks ? p.block_table[static_cast<int64_t>(seq) * p.max_blocks + table_col] : -1;
-          int64_t row = block * p.block_size + tok % p.block_size;
-          if (block < 0 || row + kTile > p.pool_rows) {
-            RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, tok / p.block_size, static_cast<int32_t>(block));
-            row = 0;  // keep the pipeline moving on addressable memory; the status word tells the host
-          }
-          const uint32_t full = bar(&misc->kv_full[stage]);
-          const uint32_t dst = kv_addr + stage * kStageBytes;
-          TRACE(g, 0);
-          ptx::MbarArriveExpectTx(full, kStageBytes);
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            ptx::TmaLoad2D(dst + c * kSlabBytes, &latent_map, 64 * c, static_cast<int32_t>(row), full);
-          }
-          ptx::TmaLoad2D(dst + 8 * kSlabBytes, &rope_map, 0, static_cast<int32_t>(row), full);
+          issue_tile(seq, begin, t, g);
         }
       }
       if (!ok) {
@@ -346,23 +378,27 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
           if (last < 0) continue;
-          const uint32_t full = bar(&misc->kv_full[s]);
           const uint32_t parity = (last / kStages) & 1;
           const uint64_t t0 = ptx::GlobalTimerNs();
-          while (!ptx::MbarTryWait(full, parity)) {
-            if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
+          for (int k = 0; k < 3; ++k) {
+            while (!ptx::MbarTryWait(bar(&misc->kv_full[s][k]), parity)) {
+              if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
+            }
           }
         }
       }
     }
-  } else if (warp == 5) {
-    // ======================= MMA issuer ==========================================================
-    // The whole warp runs this loop in lockstep and each tcgen05 instruction sits under elect.sync:
-    // measured on B200, that form issues an M=64 N=64 MMA every 34 cycles (the tensor pipe's own
-    // rate), against 46-58 for a single-thread loop or a lane-predicated one. elect.sync picks the
-    // same lane every time, so the commits track the MMAs they follow.
+  } else if (warp == 5 || warp == 6) {
+    // ======================= MMA issuers =========================================================
+    // Warp 5 issues every QK, warp 6 every PV: two independent instruction streams into the tensor
+    // pipe, so a PV whose P has just become ready never queues behind a 36-instruction QK burst, and
+    // each warp waits with plain blocking waits. A whole warp runs its loop in lockstep and each
+    // tcgen05 instruction sits under elect.sync: measured on B200, that form issues an M=64 N=64 MMA
+    // every 34 cycles against 46-58 for a single-thread or lane-predicated loop. elect.sync picks the
+    // same lane every time, so a warp's commits track the MMAs that warp issued.
     {
       constexpr uint32_t kIdescPv = ptx::InstrDescBf16(128, kHeads, 1, 0);
+      const bool is_qk = warp == 5;
       // Descriptor templates; the start address is advanced by adding to the low word.
       const uint64_t q_desc = ptx::SmemDescSw128(q_addr, 16, 1024);            // K-major, 8-row groups 1024 B apart
       const uint64_t k_desc0 = ptx::SmemDescSw128(kv_addr, 16, 1024);          // K-major B (tile rows = N)
@@ -379,112 +415,82 @@ __global__ void __launch_bounds__(kThreads, 1)
       while (ok) {
         const int have = walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len) ? 1 : 0;
         if (__shfl_sync(0xffffffffu, have, 0) == 0) break;
-        ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_full), seg & 1, misc, p.status, 22));
-        if (!ok) break;
-        if (seg > 0) {
-          // The previous segment's accumulators must have been drained by the epilogue.
-          ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->o_empty), (seg - 1) & 1, misc, p.status, 23));
-          if (!ok) break;
-        }
         const int n = __shfl_sync(0xffffffffu, t_hi - t_lo, 0);
-        int next_qk = 0, next_pv = 0;
-        int qk_part = 0;
-        uint32_t idle = 0;
-        uint64_t idle_start = 0;
-        while (next_pv < n) {
-          bool progressed = false;
-          // PV of the oldest tile whose P is ready: it frees a KV stage, so it goes first.
-          if (next_pv < next_qk) {
-            const int g = __shfl_sync(0xffffffffu, g0 + next_pv, 0);
-            const int stage = g % kStages;
-            const int first_pv = __shfl_sync(0xffffffffu, next_pv == 0 ? 1 : 0, 0);
-            if (__all_sync(0xffffffffu, ptx::MbarTestWait(bar(&misc->p_full[stage]), (g / kStages) & 1))) {
-              ptx::TcFenceAfterSync();
-              TRACE(g, 5);
-              const uint32_t stage_off = stage * kStageBytes;
-              const uint64_t pdesc = DescAt(k_desc0, stage_off + 8 * kSlabBytes);  // K-major: row = head, 32 B per k-step
-              const uint64_t vdesc = DescAt(v_desc0, stage_off);
-#pragma unroll
-              for (int ks = 0; ks < kTile / 16; ++ks) {
-#pragma unroll
-                for (int tm = 0; tm < 4; ++tm) {
-                  const uint64_t a = DescAt(vdesc, 2 * tm * kSlabBytes + ks * 2048);
-                  const uint64_t b = DescAt(pdesc, ks * 32);
-                  const uint32_t acc = (first_pv != 0 && ks == 0) ? 0u : 1u;
-                  if (ptx::ElectOne()) ptx::MmaF16SS(tmem_u + 64 * tm, a, b, kIdescPv, acc);
-                }
-              }
-              if (ptx::ElectOne()) ptx::TcCommit(bar(&misc->kv_empty[stage]));
-              TRACE(g, 6);
-              ++next_pv;
-              progressed = true;
-            }
-          }
-          // QK of the next tile whose stage has landed and whose S buffer has been read out.
-          if (next_qk < n) {
-            const int g = __shfl_sync(0xffffffffu, g0 + next_qk, 0);
+        if (is_qk) {
+          ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_full), seg & 1, misc, p.status, 22));
+          for (int i = 0; i < n && ok; ++i) {
+            const int g = __shfl_sync(0xffffffffu, g0 + i, 0);
             const int stage = g % kStages;
             const int buf = g & 1;
-            bool ready = qk_part > 0;
-            if (!ready) {
-              ready = ptx::MbarTestWait(bar(&misc->kv_full[stage]), (g / kStages) & 1) &&
-                      (g < 2 || ptx::MbarTestWait(bar(&misc->s_empty[buf]), ((g >> 1) & 1) ^ 1));
-              ready = __all_sync(0xffffffffu, ready);
-              if (ready) {
-                ptx::TcFenceAfterSync();
-                TRACE(g, 1);
-              }
+            const uint32_t kv_parity = (g / kStages) & 1;
+            ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][0]), kv_parity, misc, p.status, 24));
+            if (ok && g >= 2) {
+              ok = __all_sync(0xffffffffu,
+                              BoundedWait(bar(&misc->s_empty[buf]), ((g >> 1) & 1) ^ 1, misc, p.status, 25));
             }
-            if (ready) {
-              const uint64_t kdesc = DescAt(k_desc0, stage * kStageBytes);
-              const uint32_t d = tmem_u + kTmemColS + kTile * buf;
-              // All 36 k-steps go out back to back: measured, the straight run issues one MMA per 35
-              // cycles, while returning to the polling loop between groups costs more than it gains.
-              IssueQkGroup<0>(q_desc, kdesc, d);
-              IssueQkGroup<3>(q_desc, kdesc, d);
-              IssueQkGroup<6>(q_desc, kdesc, d);
-              qk_part = 2;
-              if (++qk_part == 3) {
-                if (ptx::ElectOne()) {
-                  ptx::TcCommit(bar(&misc->s_full[buf]));
-                  if (next_qk == n - 1) ptx::TcCommit(bar(&misc->q_empty));  // Q buffer free for the next segment
-                }
-                TRACE(g, 2);
-                qk_part = 0;
-                ++next_qk;
-              }
-              progressed = true;
+            if (!ok) break;
+            ptx::TcFenceAfterSync();
+            TRACE(g, 1);
+            const uint64_t kdesc = DescAt(k_desc0, stage * kStageBytes);
+            const uint32_t d = tmem_u + kTmemColS + kTile * buf;
+            // Twelve k-steps per slab group, each group as soon as its slabs have landed (compile-time
+            // offsets; a runtime offset costs the uniform-datapath issue rate).
+            IssueQkGroup<0>(q_desc, kdesc, d);
+            ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][1]), kv_parity, misc, p.status, 26));
+            if (!ok) break;
+            ptx::TcFenceAfterSync();
+            IssueQkGroup<3>(q_desc, kdesc, d);
+            ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][2]), kv_parity, misc, p.status, 27));
+            if (!ok) break;
+            ptx::TcFenceAfterSync();
+            IssueQkGroup<6>(q_desc, kdesc, d);
+            if (ptx::ElectOne()) {
+              ptx::TcCommit(bar(&misc->s_full[buf]));
+              if (i == n - 1) ptx::TcCommit(bar(&misc->q_empty));  // Q buffer free for the next segment
             }
+            TRACE(g, 2);
           }
-          if (progressed) {
-            idle = 0;
-            idle_start = 0;
-          } else if ((++idle & 1023u) == 0) {
-            bool give_up = Aborting(misc);
-            if (!give_up) {
-              const uint64_t now = ptx::GlobalTimerNs();
-              if (idle_start == 0) idle_start = now;
-              if (now - idle_start > 1000000000ull) {
-                if (lane == 0) RaiseTimeout(misc, p.status, 24, static_cast<uint32_t>(next_qk * 65536 + next_pv));
-                give_up = true;
+        } else {
+          if (seg > 0) {
+            // The previous segment's accumulators must have been drained by the epilogue.
+            ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->o_empty), (seg - 1) & 1, misc, p.status, 23));
+          }
+          for (int i = 0; i < n && ok; ++i) {
+            const int g = __shfl_sync(0xffffffffu, g0 + i, 0);
+            const int stage = g % kStages;
+            ok = __all_sync(0xffffffffu,
+                            BoundedWait(bar(&misc->p_full[stage]), (g / kStages) & 1, misc, p.status, 21));
+            if (!ok) break;
+            ptx::TcFenceAfterSync();
+            TRACE(g, 5);
+            const uint32_t stage_off = stage * kStageBytes;
+            const uint64_t pdesc = DescAt(k_desc0, stage_off + 8 * kSlabBytes);  // K-major: row = head, 32 B per k-step
+            const uint64_t vdesc = DescAt(v_desc0, stage_off);
+            const int first_pv = __shfl_sync(0xffffffffu, i == 0 ? 1 : 0, 0);
+#pragma unroll
+            for (int ks = 0; ks < kTile / 16; ++ks) {
+#pragma unroll
+              for (int tm = 0; tm < 4; ++tm) {
+                const uint64_t a = DescAt(vdesc, 2 * tm * kSlabBytes + ks * 2048);
+                const uint64_t b = DescAt(pdesc, ks * 32);
+                const uint32_t acc = (first_pv != 0 && ks == 0) ? 0u : 1u;
+                if (ptx::ElectOne()) ptx::MmaF16SS(tmem_u + 64 * tm, a, b, kIdescPv, acc);
               }
             }
-            if (__any_sync(0xffffffffu, give_up)) {
-              ok = false;
-              break;
-            }
+            if (ptx::ElectOne()) ptx::TcCommit(bar(&misc->kv_empty[stage]));
+            TRACE(g, 6);
           }
+          if (ok && ptx::ElectOne()) ptx::TcCommit(bar(&misc->o_full));
         }
-        if (!ok) break;
-        if (ptx::ElectOne()) ptx::TcCommit(bar(&misc->o_full));
         g0 += n;
         ++seg;
       }
       // Nothing of this warp's tensor work may be in flight when TMEM is freed.
       if (ptx::ElectOne()) {
-        ptx::TcCommit(bar(&misc->drain));
+        const uint32_t drain = bar(&misc->drain[is_qk ? 0 : 1]);
+        ptx::TcCommit(drain);
         const uint64_t t0 = ptx::GlobalTimerNs();
-        while (!ptx::MbarTryWait(bar(&misc->drain), 0)) {
+        while (!ptx::MbarTryWait(drain, 0)) {
           if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
         }
       }
@@ -494,6 +500,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ======================= softmax + epilogue warps ============================================
     const int tid = threadIdx.x;                 // 0..127
     const bool row_ok = lane < 16;               // M=64 accumulators use lanes 0..15 of each 32-lane quarter
+    const bool upper = lane >= 16;               // takes tokens 32..63 of row (lane - 16) in the softmax
     const int head = warp * 16 + (lane & 15);
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     SegmentWalker walk(p.kv_len, p.batch, start_seq, start_tile, my_tiles);
@@ -526,41 +533,53 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::TcFenceBeforeSync();
         ptx::MbarArrive(bar(&misc->s_empty[buf]));
 
+        // Lanes 0-15 of a warp hold the 64 scores of their row (an M=64 accumulator occupies lanes 0-15
+        // of each 32-lane quarter). Lane t+16 takes over tokens 32-63 of lane t's row, so all 128 threads
+        // work: x[j] is token tok_base + j of row `head`.
+        static_assert(kTile == 64, "the lane split below assumes 64-token tiles");
+        const int tok_base = upper ? 32 : 0;
+        float x[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const uint32_t from_pair = __shfl_sync(0xffffffffu, sr[32 + j], lane & 15);
+          x[j] = __uint_as_float(upper ? from_pair : sr[j]);
+        }
         // Raw maximum first (the scale is positive), then one FFMA + one EX2 per element.
         float raw_max = -INFINITY;
         if (valid == kTile) {
 #pragma unroll
-          for (int j = 0; j < kTile; ++j) raw_max = fmaxf(raw_max, __uint_as_float(sr[j]));
+          for (int j = 0; j < 32; ++j) raw_max = fmaxf(raw_max, x[j]);
         } else {
 #pragma unroll
-          for (int j = 0; j < kTile; ++j) {
-            if (j >= valid) sr[j] = 0xff800000u;  // -inf: masked out of the maximum and of P
-            raw_max = fmaxf(raw_max, __uint_as_float(sr[j]));
+          for (int j = 0; j < 32; ++j) {
+            if (tok_base + j >= valid) x[j] = -INFINITY;  // masked out of the maximum and of P
+            raw_max = fmaxf(raw_max, x[j]);
           }
         }
+        raw_max = fmaxf(raw_max, __shfl_xor_sync(0xffffffffu, raw_max, 16));
         const float tile_max = raw_max * p.scale_log2;
         float factor = 1.0f;
         bool rescale = false;
-        if (row_ok) {
-          if (m_run == -INFINITY) {
-            m_run = tile_max;  // first tile of the segment: nothing accumulated yet
-          } else if (tile_max > m_run + kRescaleThreshold) {
-            factor = exp2f(m_run - tile_max);
-            m_run = tile_max;
-            rescale = true;
-          }
-          misc->factor[head] = factor;
+        if (m_run == -INFINITY) {
+          m_run = tile_max;  // first tile of the segment: nothing accumulated yet
+        } else if (tile_max > m_run + kRescaleThreshold) {
+          factor = exp2f(m_run - tile_max);
+          m_run = tile_max;
+          rescale = true;
         }
+        if (!upper) misc->factor[head] = factor;
         const float neg_m = -m_run;
         float sum = 0.0f;
+        uint32_t packed[16];
 #pragma unroll
-        for (int j = 0; j < kTile / 2; ++j) {
-          const float p0 = ptx::Ex2Approx(fmaf(__uint_as_float(sr[2 * j]), p.scale_log2, neg_m));
-          const float p1 = ptx::Ex2Approx(fmaf(__uint_as_float(sr[2 * j + 1]), p.scale_log2, neg_m));
+        for (int j = 0; j < 16; ++j) {
+          const float p0 = ptx::Ex2Approx(fmaf(x[2 * j], p.scale_log2, neg_m));
+          const float p1 = ptx::Ex2Approx(fmaf(x[2 * j + 1], p.scale_log2, neg_m));
           const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          sr[j] = *reinterpret_cast<const uint32_t*>(&pb);
+          packed[j] = *reinterpret_cast<const uint32_t*>(&pb);
           sum += p0 + p1;  // the denominator (and lse) keep the unrounded fp32 weights
         }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
         l_run = l_run * factor + sum;
 
         const bool any_rescale = ptx::NamedBarrierOr(1, kSoftmaxThreads, rescale);
@@ -588,15 +607,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::TcFenceBeforeSync();
         }
         unsigned char* stage_ptr = smem + kOffKv + stage * kStageBytes;
-        if (row_ok) {
-          // Row `head` of P (64 bf16 = 8 chunks of 16 bytes) over the stage's rope slab, which QK has
-          // finished with; chunks swizzled by the row index as the 128-byte pattern prescribes.
-          static_assert(kTile == 64, "P rows of 128 bytes fill the rope slab only for 64-token tiles");
+        {
+          // Row `head` of P (64 bf16 = 8 chunks of 16 bytes, this thread's half = 4 chunks) over the
+          // stage's rope slab, which QK has finished with; chunks swizzled by the row index as the
+          // 128-byte pattern prescribes.
           unsigned char* prow = stage_ptr + 8 * kSlabBytes + head * 128;
+          const int c0 = upper ? 4 : 0;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            *reinterpret_cast<int4*>(prow + ((c ^ (head & 7)) << 4)) =
-                make_int4(sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
+          for (int c = 0; c < 4; ++c) {
+            *reinterpret_cast<int4*>(prow + (((c0 + c) ^ (head & 7)) << 4)) =
+                make_int4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
           }
         }
         if (valid < kTile) {
@@ -620,6 +640,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = BoundedWait(bar(&misc->o_full), seg & 1, misc, p.status, 32);
       if (!ok) break;
       ptx::TcFenceAfterSync();
+      if (tid == 0) TRACE(63, 2 + 2 * (seg & 1));
       const bool whole = (t_lo == 0 && t_hi == seq_tiles);
       const bool to_user_partial = whole && p.user_o != nullptr;
       const bool to_ws = !whole;
@@ -665,6 +686,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ptx::TcFenceBeforeSync();
       ptx::MbarArrive(bar(&misc->o_empty));
+      if (tid == 0) TRACE(63, 3 + 2 * (seg & 1));
       first_segment_of_cta = false;
       ++seg;
     }
@@ -673,6 +695,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ---- teardown ---------------------------------------------------------------------------------
   ptx::TcFenceBeforeSync();
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(63, 6);
   if (warp == 5) {
     ptx::TcFenceAfterSync();
     ptx::TmemDealloc(tmem, kTmemCols);
@@ -991,6 +1014,9 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
 
   MlaDecodeTcKernel<<<n_ctas, kThreads, kSmemBytes, stream>>>(latent_map, rope_map, q_map, p);
   if (int32_t rc = CheckCuda(cudaGetLastError(), "tcgen05 decode launch")) return rc;
+#ifdef B200KV_TRACE
+  if (getenv("B200KV_SKIP_FINALIZE") != nullptr) return B200KV_OK;  // instrumented builds only: timing breakdown
+#endif
   const int64_t rows = static_cast<int64_t>(a.batch) * kHeads;
   MlaFinalizeKernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(p, n_ctas);
   return CheckCuda(cudaGetLastError(), "decode finalize launch");
