@@ -558,6 +558,143 @@ def run_b200_arm(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------
+# The two multi-GPU configurations (not the driver's default workload; run with --workload)
+# ---------------------------------------------------------------------------------------------------
+def run_extra_workload(args):
+    """--workload ragged : configs[2], 256 ragged sequences partitioned over the ranks by length
+                           (no collective), fragmented tables, 16 decode steps per timed run.
+       --workload longctx: configs[3], one 262,144-token sequence split by KV range over the ranks; every
+                           layer ends with an all-gather of the partials (NCCL) and the LSE merge."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import b200kv
+    import kvo
+    import scenarios
+    from b200kv import dist as kvdist
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+    hbm_peak, _, peak_kind = measured_peaks()
+    layers = args.layers
+    status = b200kv.new_status()
+
+    if args.workload == "ragged":
+        lens_all = scenarios.ragged_lengths(256, 512, 32768)
+        ranks, loads = kvdist.partition_sequences(lens_all, world)
+        kv_len_np = lens_all[ranks == rank].astype(np.int32)
+        nseq = len(kv_len_np)
+        blocks = int(sum(scenarios.blocks_for(int(n) + 16, BLOCK) for n in kv_len_np)) + 8
+        table_np = scenarios.fragmented_tables(kv_len_np + 16, BLOCK, blocks)
+        pool = torch.empty((layers, blocks * BLOCK, ROW), dtype=torch.bfloat16, device="cuda")
+        b200kv.fill_normal_bf16(pool, SEED + rank, kvo.STREAM_KV)
+        q = torch.empty((nseq, HEADS, ROW), dtype=torch.bfloat16, device="cuda")
+        b200kv.fill_normal_bf16(q, SEED + rank, kvo.STREAM_Q, 0, SCALE)
+        new = torch.empty((nseq, ROW), dtype=torch.bfloat16, device="cuda")
+        b200kv.fill_normal_bf16(new, SEED + rank, kvo.STREAM_NEW)
+        out = torch.empty((nseq, HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
+        table = torch.from_numpy(table_np).cuda()
+        views = [b200kv.pool_view(pool[l]) for l in range(layers)]
+        ws = torch.empty(b200kv.decode_workspace_bytes(nseq), dtype=torch.uint8, device="cuda")
+        decode_steps = 16
+        # lengths and slots of each of the 16 consecutive decode steps, precomputed on the device
+        lens_steps = [torch.from_numpy(kv_len_np + i + 1).cuda() for i in range(decode_steps)]
+        slots_steps = []
+        for i in range(decode_steps):
+            pos = kv_len_np.astype(np.int64) + i
+            slots_steps.append(torch.from_numpy(
+                (table_np[np.arange(nseq), pos // BLOCK].astype(np.int64) * BLOCK + pos % BLOCK).astype(np.int32)).cuda())
+
+        def step():
+            for i in range(decode_steps):
+                for l in range(layers):
+                    b200kv.append(views[l], new[:, :LATENT], new[:, LATENT:], slots_steps[i], status=status)
+                    b200kv.mla_decode(q, views[l], table, lens_steps[i], BLOCK, SCALE, out=out, workspace=ws,
+                                      status=status)
+        tokens_per_step = 256 * decode_steps
+        bytes_per_step = float(sum(int((kv_len_np + i + 1).sum()) for i in range(decode_steps))) * ROW * 2 * layers
+        desc = (f"configs[2]: 256 sequences, lengths 512..32768 (seeded), LPT partition over {world} rank(s) "
+                f"(rank 0 holds {nseq} sequences, load imbalance {loads.max() / loads.mean():.4f}), fragmented tables, "
+                f"{decode_steps} decode steps per run, {layers} of 43 layers resident")
+    else:
+        n = 262144
+        begin, length = kvdist.split_kv_range(n, BLOCK, world, rank)
+        my_blocks = scenarios.blocks_for(length, BLOCK)
+        total_blocks = n // BLOCK
+        # this rank's pool holds only its block range; its table column j maps block begin/BLOCK + j
+        table_np = np.zeros((1, total_blocks), dtype=np.int32)
+        table_np[0, begin // BLOCK: begin // BLOCK + my_blocks] = kvo.permutation(my_blocks, seed=SEED + rank)
+        pool = torch.empty((layers, my_blocks * BLOCK, ROW), dtype=torch.bfloat16, device="cuda")
+        b200kv.fill_normal_bf16(pool, SEED + rank, kvo.STREAM_KV)
+        q = torch.empty((1, HEADS, ROW), dtype=torch.bfloat16, device="cuda")
+        b200kv.fill_normal_bf16(q, SEED, kvo.STREAM_Q, 0, SCALE)
+        table = torch.from_numpy(table_np).cuda()
+        lens = torch.tensor([length], dtype=torch.int32, device="cuda")
+        begins = torch.tensor([begin], dtype=torch.int32, device="cuda")
+        views = [b200kv.pool_view(pool[l]) for l in range(layers)]
+        ws = torch.empty(b200kv.decode_workspace_bytes(1), dtype=torch.uint8, device="cuda")
+        po = torch.empty((HEADS, LATENT), dtype=torch.float32, device="cuda")
+        pm = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
+        pl = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
+        out = torch.empty((HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
+        lse = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
+
+        def step():
+            for l in range(layers):
+                b200kv.mla_decode(q, views[l], table, lens, BLOCK, SCALE, kv_begin=begins,
+                                  partial=(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS)),
+                                  workspace=ws, status=status)
+                if world > 1:
+                    kvdist.merge_across_ranks(po, pm, pl, out, lse)
+                else:
+                    b200kv.lse_merge(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS), out, lse)
+        tokens_per_step = 1
+        bytes_per_step = float(n) * ROW * 2 * layers
+        desc = (f"configs[3]: one sequence of {n} tokens split by KV range over {world} rank(s) "
+                f"({length} tokens on rank 0), all-gather of 131,584-byte partials + LSE merge per layer, "
+                f"{layers} of 43 layers")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(1, args.warmup)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    st = status.cpu().tolist()
+    if st[0] != 0:
+        raise RuntimeError(f"device status word reports {st}")
+    if rank == 0:
+        scale43 = 43.0 / layers
+        gbs = bytes_per_step / (ms * 1e-3) * 1e-9
+        print(json.dumps({
+            "metric": f"decode tokens/s ({args.workload})", "value": tokens_per_step / (ms * scale43 * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms * scale43, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": {"workload": desc},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": gbs / hbm_peak, "peak_kind": peak_kind,
+                         "note": "rank 0's KV bytes per step over the step time, launch overhead included"},
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -570,11 +707,15 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-move", action="store_true")
+    ap.add_argument("--workload", default="batched", choices=["batched", "ragged", "longctx"],
+                    help="batched = configs[1] (the driver's workload); ragged / longctx = the multi-GPU configurations")
     args = ap.parse_args()
     global LAYERS
     LAYERS = args.layers
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload != "batched":
+        run_extra_workload(args)
     else:
         run_b200_arm(args)
 
