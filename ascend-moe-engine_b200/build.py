@@ -26,7 +26,7 @@ SOURCES = [
     "kv_block_pool.cpp",
     "kv_arena.cpp",
     "kv_partition.cpp",
-    "aclnn_shim.cpp",
+    "aclnn_shim.cu",
     "no_alloc.cu",
 ]
 
