@@ -38,6 +38,29 @@ __device__ __forceinline__ void StoreStream16(void* p, int4 v) {
                : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with LaunchOverlapped may be scheduled while its
+// predecessor in the stream is still draining; it must call GridDependencyWait() before it reads anything
+// the predecessor wrote. A kernel lets its successor start early with GridDependencyTrigger(). Both are
+// no-ops for ordinary launches.
+__device__ __forceinline__ void GridDependencyWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void GridDependencyTrigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t LaunchOverlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 inline int32_t CurrentDeviceSmCount() {
   static thread_local int cached_device = -1;
   static thread_local int cached_sms = 0;

@@ -93,6 +93,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
     AppendKernel(b200kv_pool_view pool, const char* latent_src, int64_t src_latent_stride_b, const char* rope_src,
                  int64_t src_rope_stride_b, const int32_t* __restrict__ slot_mapping, int64_t n_tokens,
                  int latent_chunks, int rope_chunks, int32_t* status) {
+  GridDependencyTrigger();
+  GridDependencyWait();
   const int lane = threadIdx.x & 31;
   const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
@@ -215,11 +217,12 @@ extern "C" int32_t b200kv_append(const b200kv_pool_view* pool, const void* laten
                  static_cast<long long>(src_rope_stride));
     return B200KV_ERR_INVALID;
   }
-  AppendKernel<B200KV_LATENT_DIM / 8, B200KV_ROPE_DIM / 8>
-      <<<GridFor(n_tokens), kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-          *pool, static_cast<const char*>(latent_src), src_latent_stride * 2, static_cast<const char*>(rope_src),
-          src_rope_stride * 2, slot_mapping, n_tokens, B200KV_LATENT_DIM / 8, B200KV_ROPE_DIM / 8, status);
-  return CheckCuda(cudaGetLastError(), "append launch");
+  return CheckCuda(
+      LaunchOverlapped(AppendKernel<B200KV_LATENT_DIM / 8, B200KV_ROPE_DIM / 8>, dim3(GridFor(n_tokens)),
+                       dim3(kWarpsPerCta * 32), 0, static_cast<cudaStream_t>(stream), *pool,
+                       static_cast<const char*>(latent_src), src_latent_stride * 2, static_cast<const char*>(rope_src),
+                       src_rope_stride * 2, slot_mapping, n_tokens, B200KV_LATENT_DIM / 8, B200KV_ROPE_DIM / 8, status),
+      "append launch");
 }
 
 extern "C" int32_t b200kv_gather(const b200kv_pool_view* pool, const int32_t* block_table, int64_t max_blocks,

@@ -214,6 +214,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto bar = [&](const uint64_t* b) { return ptx::SmemAddr(b); };
 
   // ---- setup ----------------------------------------------------------------------------------
+  GridDependencyTrigger();  // the finalize kernel may be scheduled as SMs free up
+  GridDependencyWait();     // everything below reads what earlier kernels in the stream wrote
   if (threadIdx.x == 0) TRACE(63, 0);
 
   // One tile's nine TMA loads (eight latent slabs, one rope slab) into stage g % kStages.
@@ -728,6 +730,10 @@ __global__ void __launch_bounds__(256)
   }
   const long long mine = TilesOf(p.kv_len[b]);
   const bool want_partial = p.user_o != nullptr;
+  // The lengths above were already stable when the decode kernel read them; the partials below are
+  // what that kernel wrote, so they wait for its completion.
+  GridDependencyTrigger();
+  GridDependencyWait();
 
   float big = -INFINITY, sum_l = 0.0f;
   float4 acc[4];
@@ -1012,14 +1018,18 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.status = status;
   p.trace = g_trace;
 
-  MlaDecodeTcKernel<<<n_ctas, kThreads, kSmemBytes, stream>>>(latent_map, rope_map, q_map, p);
-  if (int32_t rc = CheckCuda(cudaGetLastError(), "tcgen05 decode launch")) return rc;
+  if (int32_t rc = CheckCuda(LaunchOverlapped(MlaDecodeTcKernel, dim3(n_ctas), dim3(kThreads), kSmemBytes, stream,
+                                              latent_map, rope_map, q_map, p),
+                             "tcgen05 decode launch")) {
+    return rc;
+  }
 #ifdef B200KV_TRACE
   if (getenv("B200KV_SKIP_FINALIZE") != nullptr) return B200KV_OK;  // instrumented builds only: timing breakdown
 #endif
   const int64_t rows = static_cast<int64_t>(a.batch) * kHeads;
-  MlaFinalizeKernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(p, n_ctas);
-  return CheckCuda(cudaGetLastError(), "decode finalize launch");
+  return CheckCuda(LaunchOverlapped(MlaFinalizeKernel, dim3(static_cast<unsigned>((rows + 7) / 8)), dim3(256), 0, stream,
+                                    p, n_ctas),
+                   "decode finalize launch");
 }
 
 }  // namespace b200kv
