@@ -141,6 +141,26 @@ __device__ __noinline__ bool BoundedWait(uint32_t bar, uint32_t parity, Misc* mi
   }
 }
 
+// ---- work partition -----------------------------------------------------------------------------------
+// The tiles of all sequences form one flat list (sequence after sequence, empty ones contribute nothing).
+// Cutting that list into G equal runs of tiles leaves the CTAs uneven: a CTA whose run crosses from one
+// sequence into the next reloads Q and drains its accumulators in mid-run, which costs it about as much
+// as one and a half tiles. So the list is cut by cost instead: a tile costs 2, entering a new sequence
+// costs 3 more. Tile x of the sequence with ordinal s (among the non-empty ones) sits at cost position
+// 2x + 3s; with C = 2T + 3(S - 1) the total, CTA c takes the tiles whose position lies in
+// [ceil(c*C/G), ceil((c+1)*C/G)). Both kernels derive everything from these two functions.
+struct CostCut {
+  long long cost_total;  // C, at least 2 when there is any tile
+  long long n_ctas;      // G
+  __device__ long long CtaOf(long long x, long long s) const { return (2 * x + 3 * s) * n_ctas / cost_total; }
+  __device__ long long FirstPos(long long c) const { return (c * cost_total + n_ctas - 1) / n_ctas; }
+  // First tile of a sequence (first tile `first`, ordinal s) at or after cost position k.
+  __device__ long long FirstTileAt(long long k, long long first, long long s) const {
+    const long long x = (k - 3 * s + 1) >> 1;  // ceil((k - 3s) / 2), also right for negative values
+    return x > first ? x : first;
+  }
+};
+
 // Walks the segments of this CTA's tile range. All roles run the same iterator.
 struct SegmentWalker {
   const int32_t* kv_len;
@@ -215,7 +235,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // ---- setup ----------------------------------------------------------------------------------
   GridDependencyTrigger();  // the finalize kernel may be scheduled as SMs free up
-  GridDependencyWait();     // everything below reads what earlier kernels in the stream wrote
   if (threadIdx.x == 0) TRACE(63, 0);
 
   // One tile's nine TMA loads (eight latent slabs, one rope slab) into stage g % kStages.
@@ -282,36 +301,70 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::PrefetchTensorMap(&q_map);
     }
     __syncwarp();
-    // This CTA's slice of the flat tile list: total, then the sequence holding the first tile.
-    long long total = 0;
-    for (int b = lane; b < p.batch; b += 32) total += TilesOf(p.kv_len[b]);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
-    const long long lo = total * cta / n_ctas;
-    const long long hi = total * (cta + 1) / n_ctas;
-    int start_seq = p.batch, start_tile = 0, start_seq_tiles = 0;
-    long long before = 0;
-    for (int b0 = 0; b0 < p.batch && start_seq == p.batch; b0 += 32) {
-      const int b = b0 + lane;
-      const long long mine = b < p.batch ? TilesOf(p.kv_len[b]) : 0;
-      long long incl = mine;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const long long up = __shfl_up_sync(0xffffffffu, incl, off);
-        if (lane >= off) incl += up;
-      }
-      const bool hit = (before + incl > lo) && mine > 0;
-      const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-      if (ballot != 0 && hi > lo) {
-        const int src = __ffs(ballot) - 1;
-        const long long incl_src = __shfl_sync(0xffffffffu, incl, src);
-        const long long mine_src = __shfl_sync(0xffffffffu, mine, src);
-        start_seq = b0 + src;
-        start_tile = static_cast<int>(lo - (before + incl_src - mine_src));
-        start_seq_tiles = static_cast<int>(mine_src);
-      }
-      before += __shfl_sync(0xffffffffu, incl, 31);
+    // Up to here nothing read memory that an earlier kernel in the stream may still be writing, so under
+    // a programmatic dependent launch the lines above overlap that kernel's tail. From here on the
+    // lengths, the block table, Q and the pool are read.
+    GridDependencyWait();
+    // This CTA's run of the flat tile list (see CostCut): totals first, then the tile at which the run
+    // starts and the tile at which the next CTA's run starts.
+    long long total = 0, nonempty = 0;
+    for (int b = lane; b < p.batch; b += 32) {
+      const int t = TilesOf(p.kv_len[b]);
+      total += t;
+      nonempty += t > 0 ? 1 : 0;
     }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      total += __shfl_xor_sync(0xffffffffu, total, off);
+      nonempty += __shfl_xor_sync(0xffffffffu, nonempty, off);
+    }
+    const CostCut cut{2 * total + 3 * (nonempty > 0 ? nonempty - 1 : 0), n_ctas};
+    // One pass over the sequences finds both the first tile at or after this CTA's first cost position
+    // (flat index `lo`, its sequence, that sequence's first flat index and tile count) and the first tile
+    // at or after the next CTA's (`hi`); either is `total` when no tile is left.
+    int start_seq = p.batch, start_seq_tiles = 0;
+    long long start_first = 0;
+    long long lo = total, hi = total;
+    if (total > 0) {
+      const long long k_lo = cut.FirstPos(cta), k_hi = cut.FirstPos(cta + 1);
+      bool have_lo = false, have_hi = false;
+      long long before = 0, before_s = 0;
+      for (int b0 = 0; b0 < p.batch && !have_hi; b0 += 32) {
+        const int b = b0 + lane;
+        const long long mine = b < p.batch ? TilesOf(p.kv_len[b]) : 0;
+        long long incl = mine, incl_s = mine > 0 ? 1 : 0;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const long long up = __shfl_up_sync(0xffffffffu, incl, off);
+          const long long up_s = __shfl_up_sync(0xffffffffu, incl_s, off);
+          if (lane >= off) {
+            incl += up;
+            incl_s += up_s;
+          }
+        }
+        const long long s = before_s + incl_s - 1;                      // ordinal of this lane's sequence, if not empty
+        const long long last_pos = 2 * (before + incl - 1) + 3 * s;     // cost position of its last tile
+        const unsigned hit_lo = __ballot_sync(0xffffffffu, mine > 0 && last_pos >= k_lo);
+        const unsigned hit_hi = __ballot_sync(0xffffffffu, mine > 0 && last_pos >= k_hi);
+        if (!have_lo && hit_lo != 0) {
+          const int src = __ffs(hit_lo) - 1;
+          start_first = before + __shfl_sync(0xffffffffu, incl - mine, src);
+          start_seq = b0 + src;
+          start_seq_tiles = static_cast<int>(__shfl_sync(0xffffffffu, mine, src));
+          lo = cut.FirstTileAt(k_lo, start_first, __shfl_sync(0xffffffffu, s, src));
+          have_lo = true;
+        }
+        if (hit_hi != 0) {
+          const int src = __ffs(hit_hi) - 1;
+          const long long first = before + __shfl_sync(0xffffffffu, incl - mine, src);
+          hi = cut.FirstTileAt(k_hi, first, __shfl_sync(0xffffffffu, s, src));
+          have_hi = true;
+        }
+        before += __shfl_sync(0xffffffffu, incl, 31);
+        before_s += __shfl_sync(0xffffffffu, incl_s, 31);
+      }
+    }
+    const int start_tile = static_cast<int>(lo - start_first);
     if (lane == 0) {
       misc->start_seq = start_seq;
       misc->start_tile = start_tile;
@@ -331,6 +384,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::TmemAlloc(ptx::SmemAddr(&misc->tmem_base), kTmemCols);
     ptx::TmemRelinquish();
   }
+  GridDependencyWait();  // every thread, before it reads anything of the caller's
   ptx::TcFenceBeforeSync();
   __syncthreads();
   ptx::TcFenceAfterSync();
@@ -717,16 +771,22 @@ __global__ void __launch_bounds__(256)
   if (row >= static_cast<int64_t>(p.batch) * kHeads) return;
   const int b = static_cast<int>(row / kHeads);
   const int h = static_cast<int>(row % kHeads);
-  long long before = 0, total = 0;
-  for (int s = lane; s < p.batch; s += 32) {
-    const long long t = TilesOf(p.kv_len[s]);
+  long long before = 0, total = 0, before_s = 0, nonempty = 0;
+  for (int i = lane; i < p.batch; i += 32) {
+    const long long t = TilesOf(p.kv_len[i]);
     total += t;
-    if (s < b) before += t;
+    nonempty += t > 0 ? 1 : 0;
+    if (i < b) {
+      before += t;
+      before_s += t > 0 ? 1 : 0;
+    }
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
     total += __shfl_xor_sync(0xffffffffu, total, off);
+    nonempty += __shfl_xor_sync(0xffffffffu, nonempty, off);
     before += __shfl_xor_sync(0xffffffffu, before, off);
+    before_s += __shfl_xor_sync(0xffffffffu, before_s, off);
   }
   const long long mine = TilesOf(p.kv_len[b]);
   const bool want_partial = p.user_o != nullptr;
@@ -741,19 +801,25 @@ __global__ void __launch_bounds__(256)
   for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 
   if (mine > 0) {
-    // CTA owning tile x: the largest c with floor(c*T/G) <= x.
-    const long long c_first = ((before + 1) * n_ctas - 1) / total;
-    const long long c_last = ((before + mine) * n_ctas - 1) / total;
+    // The decode kernel's cut of the tile list (CostCut): this sequence has ordinal before_s and owns
+    // tiles [before, before + mine).
+    const CostCut cut{2 * total + 3 * (nonempty - 1), n_ctas};
+    const long long c_first = cut.CtaOf(before, before_s);
+    const long long c_last = cut.CtaOf(before + mine - 1, before_s);
     if (c_first == c_last) return;  // written directly by the decode kernel
+    // The CTA that took the tile before this sequence: if it is c_first, this sequence is not that CTA's
+    // first segment and its part sits in the CTA's second slot.
+    const long long c_prev = before > 0 ? cut.CtaOf(before - 1, before_s - 1) : -1;
     for (long long c0 = c_first; c0 <= c_last; c0 += 32) {
       // Wave 2: lane k takes CTA c0 + k: its slot, m and l (slot < 0: no part from that CTA).
       const long long c = c0 + lane;
       int slot = -1;
       float m = -INFINITY, l = 0.0f;
       if (c <= c_last) {
-        const long long lo = total * c / n_ctas;
-        if (total * (c + 1) / n_ctas != lo) {  // a CTA with an empty range wrote nothing
-          slot = static_cast<int>(c * 2 + (lo >= before ? 0 : 1));
+        // The CTA holds a part if its first tile inside this sequence lies before the next CTA's run.
+        const long long x = cut.FirstTileAt(cut.FirstPos(c), before, before_s);
+        if (x < before + mine && 2 * x + 3 * before_s < cut.FirstPos(c + 1)) {
+          slot = static_cast<int>(c * 2 + (c > c_prev ? 0 : 1));
           l = p.ws_l[slot * kHeads + h];
           m = p.ws_m[slot * kHeads + h];
         }
