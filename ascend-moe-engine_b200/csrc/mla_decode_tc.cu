@@ -762,8 +762,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 // sequences. One warp per (sequence, head); grid-wide, so the partials (a few tens of MB, mostly still
 // in L2) are pulled by every SM at once. Recomputes the flat partition arithmetic of the decode
 // kernel: sequence b owns tiles [P_b, P_b + n_b) of T; CTA c owns [c*T/G, (c+1)*T/G).
-// Loads are arranged in three independent waves (lengths, then every part's (m, l) at once with one
-// part per lane, then every part's row with up to eight parts in flight) instead of a chain per part.
+// Loads are arranged in two independent waves instead of a chain per part: the lengths (before the
+// decode kernel has finished), then every part's (m, l), one part per lane, together with the parts' rows,
+// up to eight parts in flight.
 __global__ void __launch_bounds__(256)
     MlaFinalizeKernel(TcParams p, int32_t n_ctas) {
   const int lane = threadIdx.x & 31;
@@ -790,8 +791,24 @@ __global__ void __launch_bounds__(256)
   }
   const long long mine = TilesOf(p.kv_len[b]);
   const bool want_partial = p.user_o != nullptr;
-  // The lengths above were already stable when the decode kernel read them; the partials below are
-  // what that kernel wrote, so they wait for its completion.
+  // The decode kernel's cut of the tile list (CostCut): this sequence has ordinal before_s and owns tiles
+  // [before, before + mine). c_prev is the CTA that took the tile before this sequence: if it is c_first,
+  // this sequence is not that CTA's first segment and its part sits in the CTA's second slot.
+  const CostCut cut{2 * total + 3 * (nonempty > 0 ? nonempty - 1 : 0), n_ctas};
+  const long long c_first = mine > 0 ? cut.CtaOf(before, before_s) : 0;
+  const long long c_last = mine > 0 ? cut.CtaOf(before + mine - 1, before_s) : -1;
+  const long long c_prev = before > 0 && mine > 0 ? cut.CtaOf(before - 1, before_s - 1) : -1;
+  // Slot of CTA c's part of this sequence, or -1: the CTA holds a part if its first tile inside the
+  // sequence lies before the next CTA's run.
+  auto slot_of = [&](long long c) {
+    if (c > c_last) return -1;
+    const long long x = cut.FirstTileAt(cut.FirstPos(c), before, before_s);
+    if (x >= before + mine || 2 * x + 3 * before_s >= cut.FirstPos(c + 1)) return -1;
+    return static_cast<int>(c * 2 + (c > c_prev ? 0 : 1));
+  };
+  int slot = slot_of(c_first + lane);
+  // All of the above came from the lengths, which were stable before the decode kernel ran; the partials
+  // below are what that kernel wrote, so they wait for its completion.
   GridDependencyTrigger();
   GridDependencyWait();
 
@@ -800,83 +817,68 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
   for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 
-  if (mine > 0) {
-    // The decode kernel's cut of the tile list (CostCut): this sequence has ordinal before_s and owns
-    // tiles [before, before + mine).
-    const CostCut cut{2 * total + 3 * (nonempty - 1), n_ctas};
-    const long long c_first = cut.CtaOf(before, before_s);
-    const long long c_last = cut.CtaOf(before + mine - 1, before_s);
-    if (c_first == c_last) return;  // written directly by the decode kernel
-    // The CTA that took the tile before this sequence: if it is c_first, this sequence is not that CTA's
-    // first segment and its part sits in the CTA's second slot.
-    const long long c_prev = before > 0 ? cut.CtaOf(before - 1, before_s - 1) : -1;
-    for (long long c0 = c_first; c0 <= c_last; c0 += 32) {
-      // Wave 2: lane k takes CTA c0 + k: its slot, m and l (slot < 0: no part from that CTA).
-      const long long c = c0 + lane;
-      int slot = -1;
-      float m = -INFINITY, l = 0.0f;
-      if (c <= c_last) {
-        // The CTA holds a part if its first tile inside this sequence lies before the next CTA's run.
-        const long long x = cut.FirstTileAt(cut.FirstPos(c), before, before_s);
-        if (x < before + mine && 2 * x + 3 * before_s < cut.FirstPos(c + 1)) {
-          slot = static_cast<int>(c * 2 + (c > c_prev ? 0 : 1));
-          l = p.ws_l[slot * kHeads + h];
-          m = p.ws_m[slot * kHeads + h];
+  if (mine > 0 && c_first == c_last) return;  // written directly by the decode kernel
+  for (long long c0 = c_first; c0 <= c_last; c0 += 32) {
+    // One wave of loads per chunk of 32 parts: lane k asks for the (m, l) of CTA c0 + k's part while the
+    // rows of the chunk's first eight parts are requested as well; where a part lies follows from
+    // arithmetic, so nothing here waits for an earlier load.
+    if (c0 != c_first) slot = slot_of(c0 + lane);
+    float m = -INFINITY, l = 0.0f;
+    if (slot >= 0) {
+      l = p.ws_l[slot * kHeads + h];
+      m = p.ws_m[slot * kHeads + h];
+    }
+    const long long left = c_last - c0 + 1;
+    const int n_here = left < 32 ? static_cast<int>(left) : 32;
+    float w = 0.0f;
+    for (int k0 = 0; k0 < n_here; k0 += 8) {
+      float4 v[8][4];
+      int slot_k[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        slot_k[k] = __shfl_sync(0xffffffffu, slot, (k0 + k) & 31);
+        if (k0 + k >= n_here) slot_k[k] = -1;
+        const float4* rowp = reinterpret_cast<const float4*>(
+            p.ws_o + (static_cast<int64_t>(slot_k[k] < 0 ? 0 : slot_k[k]) * kHeads + h) * kLatent);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v[k][i] = slot_k[k] >= 0 ? rowp[lane + 32 * i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
       }
-      if (!(l > 0.0f)) {
-        slot = -1;
-        m = -INFINITY;
-      }
-      float chunk_max = m;
+      if (k0 == 0) {
+        // The chunk's weights (this is where m and l are first needed).
+        if (!(l > 0.0f)) m = -INFINITY;
+        float chunk_max = m;
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, off));
-      const float new_big = fmaxf(big, chunk_max);
-      if (new_big == -INFINITY) continue;
-      // Rescale what earlier chunks of 32 parts accumulated (only sequences cut over more than 32 CTAs).
-      const float carry = big == -INFINITY ? 0.0f : expf(big - new_big);
-      big = new_big;
-      sum_l *= carry;
+        for (int off = 16; off > 0; off >>= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, off));
+        const float new_big = fmaxf(big, chunk_max);
+        // Rescale what earlier chunks accumulated (only sequences cut over more than 32 CTAs).
+        const float carry = (big == -INFINITY || new_big == -INFINITY) ? 0.0f : expf(big - new_big);
+        big = new_big;
+        sum_l *= carry;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc[i].x *= carry;
-        acc[i].y *= carry;
-        acc[i].z *= carry;
-        acc[i].w *= carry;
-      }
-      const float w = slot >= 0 ? expf(m - big) : 0.0f;
-      float lw = l * w;
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, off);
-      sum_l += lw;
-      // Wave 3: rows of the parts, eight parts (32 float4 per lane) in flight at a time.
-      const long long left = c_last - c0 + 1;
-      const int n_here = left < 32 ? static_cast<int>(left) : 32;
-      for (int k0 = 0; k0 < n_here; k0 += 8) {
-        float4 v[8][4];
-        float wk[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int src = (k0 + k) & 31;
-          const int slot_k = __shfl_sync(0xffffffffu, slot, src);
-          wk[k] = __shfl_sync(0xffffffffu, w, src);
-          if (k0 + k >= n_here || slot_k < 0) wk[k] = 0.0f;
-          const float4* rowp =
-              reinterpret_cast<const float4*>(p.ws_o + (static_cast<int64_t>(slot_k < 0 ? 0 : slot_k) * kHeads + h) * kLatent);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            v[k][i] = wk[k] != 0.0f ? rowp[lane + 32 * i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          }
+        for (int i = 0; i < 4; ++i) {
+          acc[i].x *= carry;
+          acc[i].y *= carry;
+          acc[i].z *= carry;
+          acc[i].w *= carry;
         }
+        w = (l > 0.0f && big != -INFINITY) ? expf(m - big) : 0.0f;
+        float lw = l * w;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int off = 16; off > 0; off >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, off);
+        sum_l += lw;
+      }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            acc[i].x = fmaf(v[k][i].x, wk[k], acc[i].x);
-            acc[i].y = fmaf(v[k][i].y, wk[k], acc[i].y);
-            acc[i].z = fmaf(v[k][i].z, wk[k], acc[i].z);
-            acc[i].w = fmaf(v[k][i].w, wk[k], acc[i].w);
-          }
+      for (int k = 0; k < 8; ++k) {
+        const float wk = __shfl_sync(0xffffffffu, w, (k0 + k) & 31);
+        if (slot_k[k] < 0 || wk == 0.0f) continue;  // an empty part's row may hold anything
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[i].x = fmaf(v[k][i].x, wk, acc[i].x);
+          acc[i].y = fmaf(v[k][i].y, wk, acc[i].y);
+          acc[i].z = fmaf(v[k][i].z, wk, acc[i].z);
+          acc[i].w = fmaf(v[k][i].w, wk, acc[i].w);
         }
       }
     }
