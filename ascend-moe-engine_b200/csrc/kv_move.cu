@@ -99,30 +99,77 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
   const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t groups = (n_tokens + kRowsPerWarp - 1) / kRowsPerWarp;
+  const int lc = kLatentChunks > 0 ? kLatentChunks : latent_chunks;
+  const int rc = kRopeChunks > 0 ? kRopeChunks : rope_chunks;
+  const int per_row = lc + rc;
+  const int total = per_row * kRowsPerWarp;
+  constexpr int kMaxItems = (kLatentChunks > 0) ? ((kLatentChunks + kRopeChunks) * kRowsPerWarp + 31) / 32 : 12;
   for (int64_t g = warp; g < groups; g += n_warps) {
-    RowPair mine{};
-    bool valid = false;
-    if (lane < kRowsPerWarp) {
-      const int64_t t = g * kRowsPerWarp + lane;
-      if (t < n_tokens) {
-        const int64_t slot = slot_mapping[t];
+    const int64_t t0 = g * kRowsPerWarp;
+    // Where a row comes from depends on its token index only, where it goes on its slot: the slot loads
+    // (lanes 0..3) and all the row loads leave together, one round trip to memory instead of two.
+    int64_t slot = -1;
+    if (lane < kRowsPerWarp && t0 + lane < n_tokens) slot = slot_mapping[t0 + lane];
+    int4 regs[kMaxItems];
+    for (int base = 0; base < total; base += 32 * kMaxItems) {
+#pragma unroll
+      for (int i = 0; i < kMaxItems; ++i) {
+        const int idx = base + lane + 32 * i;
+        const int r = idx / per_row;
+        const int c = idx - r * per_row;
+        if (idx < total && t0 + r < n_tokens) {
+          const char* src = c < lc ? latent_src + (t0 + r) * src_latent_stride_b + 16 * c
+                                   : rope_src + (t0 + r) * src_rope_stride_b + 16 * (c - lc);
+          regs[i] = LoadStream16(src);
+        }
+      }
+      // Destinations: a negative slot is padding, one past the pool is recorded and skipped.
+      bool valid = false;
+      char* my_latent = nullptr;
+      char* my_rope = nullptr;
+      if (lane < kRowsPerWarp && t0 + lane < n_tokens) {
         if (slot >= pool.pool_rows) {
-          RecordError(status, B200KV_DEV_BAD_SLOT, static_cast<int32_t>(t), static_cast<int32_t>(slot));
+          if (base == 0) RecordError(status, B200KV_DEV_BAD_SLOT, static_cast<int32_t>(t0 + lane), static_cast<int32_t>(slot));
         } else if (slot >= 0) {
           valid = true;
-          mine.src_latent = latent_src + t * src_latent_stride_b;
-          mine.src_rope = rope_src + t * src_rope_stride_b;
-          mine.dst_latent = static_cast<char*>(pool.latent) + slot * pool.latent_row_stride * 2;
-          mine.dst_rope = static_cast<char*>(pool.rope) + slot * pool.rope_row_stride * 2;
+          my_latent = static_cast<char*>(pool.latent) + slot * pool.latent_row_stride * 2;
+          my_rope = static_cast<char*>(pool.rope) + slot * pool.rope_row_stride * 2;
+        }
+      }
+      const unsigned ok_mask = __ballot_sync(0xffffffffu, valid);
+      unsigned long long dl[kRowsPerWarp], dr[kRowsPerWarp];
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) {
+        dl[r] = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_latent), r);
+        dr[r] = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_rope), r);
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxItems; ++i) {
+        const int idx = base + lane + 32 * i;
+        const int r = idx / per_row;
+        const int c = idx - r * per_row;
+        if (idx < total && ((ok_mask >> r) & 1u)) {
+          // Selecting by comparison keeps the pointer arrays in registers.
+          unsigned long long dl_r = dl[0], dr_r = dr[0];
+#pragma unroll
+          for (int q = 1; q < kRowsPerWarp; ++q) {
+            if (r == q) {
+              dl_r = dl[q];
+              dr_r = dr[q];
+            }
+          }
+          char* dst = c < lc ? reinterpret_cast<char*>(dl_r) + 16 * c : reinterpret_cast<char*>(dr_r) + 16 * (c - lc);
+          StoreStream16(dst, regs[i]);
         }
       }
     }
-    CopyFourRows<kLatentChunks, kRopeChunks>(mine, valid, latent_chunks, rope_chunks);
   }
 }
 
+// 64 registers (four CTAs per SM) cost the gather nothing and double its resident warps; the append
+// spills at that bound and is faster left alone.
 template <int kLatentChunks, int kRopeChunks>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 4)
     GatherKernel(b200kv_pool_view pool, const int32_t* __restrict__ block_table, int64_t max_blocks,
                  const int32_t* __restrict__ kv_len, int32_t batch, int32_t block_size, char* out_latent,
                  int64_t out_latent_stride_b, char* out_rope, int64_t out_rope_stride_b,

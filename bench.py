@@ -286,7 +286,7 @@ def check_against_oracle(torch, b200kv, wl: Workload, variant) -> float:
     return err
 
 
-def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float):
+def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph: bool = True):
     """Bandwidth of the two pure-movement kernels on inputs larger than L2: a prefill-sized append
     (64 sequences x 256 rows, the churn configuration's chunk) and a gather of one full layer."""
     import numpy as np
@@ -307,6 +307,14 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float):
                 fn(i)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        if not use_graph:  # profiling captures: a few plain launches (their timing includes Python)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(4):
+                fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / 4 * 1e-3
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             for i in range(iters):
@@ -346,6 +354,17 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float):
     bytes_gather = total * ROW * 2 * 2 + wl.blocks * 4
     res["gather"] = {"rows_per_launch": total, "algorithmic_bytes": bytes_gather, "us_per_launch": t * 1e6,
                      "achieved_gbs": bytes_gather / t * 1e-9, "frac_of_measured_hbm": bytes_gather / t * 1e-9 / hbm_peak}
+    # Append of a whole layer's rows (a 32 x 4096-token prefill written in one call, 151 MB read + 151 MB
+    # written): the same kernel where its fixed costs (first loads, write drain, about 3 us) are amortised.
+    full_slots = perm.to(torch.int32).contiguous()
+
+    def do_append_layer(i):
+        b200kv.append(wl.views[i % LAYERS], out_l[i % 2], out_r[i % 2], full_slots, status=wl.status)
+    t = timeit(do_append_layer, 43)
+    bytes_layer = total * (ROW * 2 * 2 + 4)
+    res["append_layer"] = {"rows_per_launch": total, "algorithmic_bytes": bytes_layer, "us_per_launch": t * 1e6,
+                           "achieved_gbs": bytes_layer / t * 1e-9,
+                           "frac_of_measured_hbm": bytes_layer / t * 1e-9 / hbm_peak}
     del src, out_l, out_r
     return res
 
@@ -520,7 +539,8 @@ def run_b200_arm(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms_total, attn_ms = (float(x) for x in times.cpu())
 
-    move = measure_move_kernels(torch, b200kv, wl, hbm_peak) if (rank == 0 and not args.skip_move) else None
+    move = (measure_move_kernels(torch, b200kv, wl, hbm_peak, use_graph=not args.no_graph)
+            if (rank == 0 and not args.skip_move) else None)
     if rank == 0:
         cpu_value, cpu_sample_desc, cpu_threads = (cpu_sample() if (world == 1 and not args.skip_cpu)
                                                     else (None, "skipped (rank 0 at N=1 only)", 0))
