@@ -14,72 +14,11 @@
 #include <thread>
 #include <vector>
 
+#include "aclnn_types.h"
 #include "b200kv_aclnn.h"
 #include "common.cuh"
 
 using namespace b200kv;
-
-namespace {
-constexpr aclnnStatus kErrNull = 161001;     // ACLNN_ERR_PARAM_NULLPTR (include/moe/core/op_table.hpp:142-147)
-constexpr aclnnStatus kErrInvalid = 161002;  // ACLNN_ERR_PARAM_INVALID
-constexpr aclnnStatus kErrRuntime = 361001;  // ACLNN_ERR_RUNTIME_ERROR
-
-int64_t ElementBytes(aclDataType t) {
-  switch (t) {
-    case ACL_FLOAT32: case ACL_INT32: return 4;
-    case ACL_FLOAT16: case ACL_BF16: case ACL_INT16: case ACL_UINT16: return 2;
-    case ACL_INT64: case ACL_UINT64: case ACL_FLOAT64: return 8;
-    default: return 1;
-  }
-}
-}  // namespace
-
-struct aclTensor {
-  std::vector<int64_t> dims, strides, storage_dims;
-  int64_t offset = 0;
-  aclDataType dtype = ACL_DT_UNDEFINED;
-  aclFormat format = ACL_FORMAT_ND;
-  void* data = nullptr;
-  int64_t Elements() const {
-    int64_t n = 1;
-    for (int64_t d : dims) n *= d;
-    return n;
-  }
-  void* Address() const { return static_cast<char*>(data) + offset * ElementBytes(dtype); }
-};
-struct aclTensorList {
-  std::vector<aclTensor*> items;
-};
-struct aclIntArray {
-  std::vector<int64_t> values;
-};
-struct aclScalar {
-  unsigned char bytes[8] = {};
-  aclDataType dtype = ACL_DT_UNDEFINED;
-};
-struct aclOpExecutor {
-  enum Kind { kScatter, kAttention } kind = kScatter;
-  bool repeatable = false;
-  // scatter
-  const aclTensor* key = nullptr;
-  const aclTensor* value = nullptr;
-  const aclTensor* slots = nullptr;
-  aclTensor* key_cache = nullptr;
-  aclTensor* value_cache = nullptr;
-  // attention
-  const aclTensor* query = nullptr;
-  const aclTensor* query_rope = nullptr;
-  const aclTensor* latent_cache = nullptr;
-  const aclTensor* rope_cache = nullptr;
-  const aclTensor* block_table = nullptr;
-  const aclTensor* out = nullptr;
-  const aclTensor* lse = nullptr;
-  std::vector<int32_t> kv_len;
-  int32_t batch = 0, heads = 0, block_size = 0;
-  float scale = 0.0f;
-  bool q_is_fused = false;  // query_rope directly follows query inside one 576-wide row
-  uint64_t decode_ws = 0, q_pack_bytes = 0;
-};
 
 // ---- descriptors --------------------------------------------------------------------------------------
 extern "C" aclTensor* aclCreateTensor(const int64_t* view_dims, uint64_t view_dims_num, aclDataType dtype,
