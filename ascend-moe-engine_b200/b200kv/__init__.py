@@ -71,6 +71,23 @@ class DecodeArgs(Structure):
     ]
 
 
+class ProducerArgs(Structure):
+    """b200kv_producer_args (include/b200kv.h)."""
+
+    _fields_ = [
+        ("pool", PoolView),
+        ("kv_a", c_void_p), ("kv_a_stride", c_int64),
+        ("gamma", c_void_p), ("eps", ctypes.c_float),
+        ("cos", c_void_p), ("cos_stride", c_int64),
+        ("sin", c_void_p), ("sin_stride", c_int64),
+        ("slot_mapping", c_void_p), ("n_tokens", c_int64),
+        ("q_rope", c_void_p), ("q_token_stride", c_int64), ("q_head_stride", c_int64), ("heads", c_int32),
+        ("latent_out", c_void_p), ("latent_out_stride", c_int64),
+        ("rope_out", c_void_p), ("rope_out_stride", c_int64),
+        ("rstd_out", c_void_p),
+    ]
+
+
 class Reservation(Structure):
     _fields_ = [
         ("blocks_per_layer", c_int64),
@@ -101,6 +118,11 @@ def _load() -> ctypes.CDLL:
     lib.b200kv_mla_decode_workspace_bytes.argtypes = [c_int32, c_int32, c_int32]
     lib.b200kv_mla_decode.restype = c_int32
     lib.b200kv_mla_decode.argtypes = [POINTER(DecodeArgs), c_void_p, c_void_p]
+    lib.b200kv_append_fused.restype = c_int32
+    lib.b200kv_append_fused.argtypes = [POINTER(ProducerArgs), c_void_p, c_void_p]
+    lib.b200kv_mx_quant_e4m3.restype = c_int32
+    lib.b200kv_mx_quant_e4m3.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                         c_void_p]
     lib.b200kv_lse_merge.restype = c_int32
     lib.b200kv_lse_merge.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p]
     lib.b200kv_fill_normal_bf16.restype = c_int32
@@ -192,6 +214,38 @@ def append(view: PoolView, latent_src, rope_src, slot_mapping, status=None, stre
     check(lib.b200kv_append(ctypes.byref(view), _ptr(latent_src), latent_src.stride(0) if n else LATENT_DIM,
                             _ptr(rope_src), rope_src.stride(0) if n else ROPE_DIM, _ptr(slot_mapping), n,
                             _stream_handle(stream), _ptr(status)))
+
+
+def append_fused(view: PoolView, kv_a, gamma, cos, sin, slot_mapping, eps: float = 1e-6, q_rope=None,
+                 latent_out=None, rope_out=None, rstd_out=None, status=None, stream=None) -> None:
+    """The producer of the appended rows in one launch: kv_a bf16 [T, >=576] ([latent | rope] per token),
+    gamma bf16 [512], cos / sin bf16 [T, 64] (or [64] shared by all tokens), slot_mapping int32 [T].
+    q_rope bf16 [T, heads, 64] is rotated in place; latent_out [T, 512], rope_out [T, 64] and rstd_out fp32
+    [T] receive copies of what was computed."""
+    n = int(slot_mapping.shape[0])
+    a = ProducerArgs()
+    a.pool = view
+    a.kv_a, a.kv_a_stride = _ptr(kv_a), kv_a.stride(0) if n else LATENT_DIM + ROPE_DIM
+    a.gamma, a.eps = _ptr(gamma), eps
+    a.cos, a.cos_stride = _ptr(cos), (cos.stride(0) if cos.dim() == 2 else 0)
+    a.sin, a.sin_stride = _ptr(sin), (sin.stride(0) if sin.dim() == 2 else 0)
+    a.slot_mapping, a.n_tokens = _ptr(slot_mapping), n
+    if q_rope is not None:
+        a.q_rope, a.q_token_stride, a.q_head_stride, a.heads = _ptr(q_rope), q_rope.stride(0), q_rope.stride(1), \
+            int(q_rope.shape[1])
+    if latent_out is not None:
+        a.latent_out, a.latent_out_stride = _ptr(latent_out), latent_out.stride(0)
+    if rope_out is not None:
+        a.rope_out, a.rope_out_stride = _ptr(rope_out), rope_out.stride(0)
+    a.rstd_out = _ptr(rstd_out)
+    check(lib.b200kv_append_fused(ctypes.byref(a), _stream_handle(stream), _ptr(status)))
+
+
+def mx_quant_e4m3(x, q, scales, stream=None) -> None:
+    """x bf16 [rows, cols] -> q uint8 [rows, cols] (FP8 E4M3 codes), scales uint8 [rows, cols / 32] (E8M0)."""
+    rows, cols = int(x.shape[0]), int(x.shape[1])
+    check(lib.b200kv_mx_quant_e4m3(_ptr(x), x.stride(0), rows, cols, _ptr(q), q.stride(0), _ptr(scales),
+                                   scales.stride(0), _stream_handle(stream)))
 
 
 def gather(view: PoolView, block_table, kv_len, block_size: int, out_latent, out_rope, out_row_offsets,

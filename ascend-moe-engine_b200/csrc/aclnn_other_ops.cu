@@ -6,6 +6,7 @@
 // operator it belongs to; the launch checks that pairing and enqueues nothing, so the tensors such an
 // operator should have written keep whatever they held. Signatures follow the plan-function types of
 // include/moe/core/op_table.hpp (line given in include/b200kv_aclnn.h beside each declaration).
+#include <cstring>
 #include <new>
 
 #include "aclnn_types.h"
@@ -55,13 +56,10 @@ aclnnStatus LaunchNothing(const char* op, void* workspace, uint64_t workspace_si
   return 0;
 }
 
-constexpr char kNameRmsNorm[] = "aclnnRmsNorm";
 constexpr char kNameRmsNormDynamicMxQuant[] = "aclnnRmsNormDynamicMxQuant";
-constexpr char kNameDynamicMxQuant[] = "aclnnDynamicMxQuant";
 constexpr char kNameCast[] = "aclnnCast";
 constexpr char kNameMatmul[] = "aclnnMatmul";
 constexpr char kNameQuantMatmulV5[] = "aclnnQuantMatmulV5";
-constexpr char kNameApplyRotaryPosEmbV2[] = "aclnnApplyRotaryPosEmbV2";
 constexpr char kNameSigmoid[] = "aclnnSigmoid";
 constexpr char kNameSqrt[] = "aclnnSqrt";
 constexpr char kNameMul[] = "aclnnMul";
@@ -83,14 +81,175 @@ constexpr char kNameQuantLightningIndexer[] = "aclnnQuantLightningIndexer";
 
 }  // namespace
 
+// ---- the three stages beside the KV path: working for the shapes the path produces and consumes -----------
+// aclnnRmsNorm on a 512-wide bf16 row (stage 6, kv_a_norm), aclnnApplyRotaryPosEmbV2 in mode "half" on 64-wide
+// bf16 slices (stage 7, rope) and aclnnDynamicMxQuant to FP8 E4M3 with E8M0 block-32 scales on the last axis
+// (stage 10, attn_quant) run the kernels of kv_stages.cu. The engine also uses these operators elsewhere with
+// other shapes (a 4096-wide norm, for instance): those plans succeed as stand-ins like the operators below.
+namespace {
+
+constexpr char kNameRmsNorm[] = "aclnnRmsNorm";
+constexpr char kNameApplyRotaryPosEmbV2[] = "aclnnApplyRotaryPosEmbV2";
+constexpr char kNameDynamicMxQuant[] = "aclnnDynamicMxQuant";
+
+bool Contiguous(const aclTensor* t) {
+  int64_t expect = 1;
+  for (int64_t i = static_cast<int64_t>(t->dims.size()) - 1; i >= 0; --i) {
+    if (t->dims[i] != 1 && t->strides[i] != expect) return false;
+    expect *= t->dims[i];
+  }
+  return true;
+}
+
+aclnnStatus NewStageExecutor(aclOpExecutor::Kind kind, const char* op, uint64_t* workspace_size, aclOpExecutor** executor,
+                             aclOpExecutor** out) {
+  auto* exec = new (std::nothrow) aclOpExecutor();
+  if (exec == nullptr) return kErrRuntime;
+  exec->kind = kind;
+  exec->op = op;
+  *workspace_size = 0;
+  *executor = exec;
+  *out = exec;
+  return 0;
+}
+
+// Checks the executor of a stage launch; `*plan_only` tells the caller that the plan was a stand-in.
+aclnnStatus CheckStageLaunch(const char* op, aclOpExecutor::Kind kind, aclOpExecutor* executor, bool* plan_only) {
+  if (executor == nullptr) {
+    SetLastError("%s: executor is null", op);
+    return kErrNull;
+  }
+  *plan_only = executor->kind == aclOpExecutor::kPlanOnly;
+  if ((executor->kind != kind && !*plan_only) || executor->op != op) {
+    SetLastError("%s: the executor was planned for %s", op, executor->op != nullptr ? executor->op : "a KV-path operator");
+    return kErrInvalid;
+  }
+  return 0;
+}
+
+aclnnStatus Finish(aclOpExecutor* executor, int32_t rc) {
+  if (!executor->repeatable) delete executor;
+  return rc == B200KV_OK ? 0 : (rc == B200KV_ERR_NULLPTR ? kErrNull : (rc == B200KV_ERR_INVALID ? kErrInvalid : kErrRuntime));
+}
+
+}  // namespace
+
 extern "C" aclnnStatus aclnnRmsNormGetWorkspaceSize(const aclTensor* x, const aclTensor* gamma, double epsilon,
-    const aclTensor* y_out, const aclTensor* rstd_out, uint64_t* workspace_size, aclOpExecutor** executor) {
+                                                    const aclTensor* y_out, const aclTensor* rstd_out,
+                                                    uint64_t* workspace_size, aclOpExecutor** executor) {
   const void* required[] = {x, gamma, y_out};
-  return PlanOnly(kNameRmsNorm, required, sizeof(required) / sizeof(required[0]), workspace_size, executor);
+  const bool ours = x != nullptr && gamma != nullptr && y_out != nullptr && workspace_size != nullptr &&
+                    executor != nullptr && x->dtype == ACL_BF16 && gamma->dtype == ACL_BF16 && y_out->dtype == ACL_BF16 &&
+                    !x->dims.empty() && x->dims.back() == B200KV_LATENT_DIM && gamma->Elements() == B200KV_LATENT_DIM &&
+                    y_out->Elements() == x->Elements() && Contiguous(x) && Contiguous(y_out) && Contiguous(gamma) &&
+                    (rstd_out == nullptr || (rstd_out->dtype == ACL_FLOAT32 && Contiguous(rstd_out) &&
+                                             rstd_out->Elements() == x->Elements() / B200KV_LATENT_DIM)) &&
+                    epsilon >= 0.0;
+  if (!ours) return PlanOnly(kNameRmsNorm, required, 3, workspace_size, executor);
+  aclOpExecutor* exec = nullptr;
+  if (aclnnStatus rc = NewStageExecutor(aclOpExecutor::kRmsNorm, kNameRmsNorm, workspace_size, executor, &exec)) return rc;
+  exec->stage_tensor[0] = x;
+  exec->stage_tensor[1] = gamma;
+  exec->stage_tensor[2] = y_out;
+  exec->stage_tensor[3] = rstd_out;
+  exec->stage_scalar = epsilon;
+  return 0;
 }
+
 extern "C" aclnnStatus aclnnRmsNorm(void* workspace, uint64_t workspace_size, aclOpExecutor* executor, aclrtStream stream) {
-  return LaunchNothing(kNameRmsNorm, workspace, workspace_size, executor, stream);
+  bool plan_only = false;
+  if (aclnnStatus rc = CheckStageLaunch(kNameRmsNorm, aclOpExecutor::kRmsNorm, executor, &plan_only)) return rc;
+  if (plan_only) return LaunchNothing(kNameRmsNorm, workspace, workspace_size, executor, stream);
+  const aclTensor* x = executor->stage_tensor[0];
+  const aclTensor* rstd = executor->stage_tensor[3];
+  const int32_t rc = b200kv_rmsnorm512(x->Address(), B200KV_LATENT_DIM, executor->stage_tensor[1]->Address(),
+                                       static_cast<float>(executor->stage_scalar), x->Elements() / B200KV_LATENT_DIM,
+                                       executor->stage_tensor[2]->Address(), B200KV_LATENT_DIM,
+                                       rstd != nullptr ? static_cast<float*>(rstd->Address()) : nullptr, stream);
+  return Finish(executor, rc);
 }
+
+extern "C" aclnnStatus aclnnApplyRotaryPosEmbV2GetWorkspaceSize(aclTensor* query_ref, aclTensor* key_ref,
+                                                                const aclTensor* cos, const aclTensor* sin, int64_t layout,
+                                                                char* rotary_mode, uint64_t* workspace_size,
+                                                                aclOpExecutor** executor) {
+  (void)layout;
+  const void* required[] = {query_ref, cos, sin};
+  auto slices = [](const aclTensor* t) {  // [T, vectors, 64] bf16, contiguous
+    return t->dtype == ACL_BF16 && t->dims.size() == 3 && t->dims[2] == B200KV_ROPE_DIM && Contiguous(t);
+  };
+  const bool ours = query_ref != nullptr && cos != nullptr && sin != nullptr && workspace_size != nullptr &&
+                    executor != nullptr && rotary_mode != nullptr && std::strcmp(rotary_mode, "half") == 0 &&
+                    slices(query_ref) && (key_ref == nullptr || (slices(key_ref) && key_ref->dims[0] == query_ref->dims[0])) &&
+                    cos->dtype == ACL_BF16 && sin->dtype == ACL_BF16 && Contiguous(cos) && Contiguous(sin) &&
+                    cos->Elements() == query_ref->dims[0] * B200KV_ROPE_DIM && sin->Elements() == cos->Elements();
+  if (!ours) return PlanOnly(kNameApplyRotaryPosEmbV2, required, 3, workspace_size, executor);
+  aclOpExecutor* exec = nullptr;
+  if (aclnnStatus rc = NewStageExecutor(aclOpExecutor::kRope, kNameApplyRotaryPosEmbV2, workspace_size, executor, &exec)) {
+    return rc;
+  }
+  exec->stage_tensor[0] = query_ref;
+  exec->stage_tensor[1] = key_ref;
+  exec->stage_tensor[2] = cos;
+  exec->stage_tensor[3] = sin;
+  return 0;
+}
+
+extern "C" aclnnStatus aclnnApplyRotaryPosEmbV2(void* workspace, uint64_t workspace_size, aclOpExecutor* executor,
+                                                aclrtStream stream) {
+  bool plan_only = false;
+  if (aclnnStatus rc = CheckStageLaunch(kNameApplyRotaryPosEmbV2, aclOpExecutor::kRope, executor, &plan_only)) return rc;
+  if (plan_only) return LaunchNothing(kNameApplyRotaryPosEmbV2, workspace, workspace_size, executor, stream);
+  const aclTensor* q = executor->stage_tensor[0];
+  const aclTensor* k = executor->stage_tensor[1];
+  const void* cos = executor->stage_tensor[2]->Address();
+  const void* sin = executor->stage_tensor[3]->Address();
+  int32_t rc = b200kv_rope_half64(q->Address(), q->dims[1] * B200KV_ROPE_DIM, B200KV_ROPE_DIM, cos, B200KV_ROPE_DIM, sin,
+                                  B200KV_ROPE_DIM, q->dims[0], static_cast<int32_t>(q->dims[1]), stream);
+  if (rc == B200KV_OK && k != nullptr) {
+    rc = b200kv_rope_half64(k->Address(), k->dims[1] * B200KV_ROPE_DIM, B200KV_ROPE_DIM, cos, B200KV_ROPE_DIM, sin,
+                            B200KV_ROPE_DIM, k->dims[0], static_cast<int32_t>(k->dims[1]), stream);
+  }
+  return Finish(executor, rc);
+}
+
+extern "C" aclnnStatus aclnnDynamicMxQuantGetWorkspaceSize(const aclTensor* x, int64_t axis, char* round_mode_optional,
+                                                           int64_t dst_type, int64_t blocksize, int64_t scale_alg,
+                                                           const aclTensor* y_out, const aclTensor* mxscale_out,
+                                                           uint64_t* workspace_size, aclOpExecutor** executor) {
+  (void)scale_alg;
+  const void* required[] = {x, y_out, mxscale_out};
+  const bool ours = x != nullptr && y_out != nullptr && mxscale_out != nullptr && workspace_size != nullptr &&
+                    executor != nullptr && x->dtype == ACL_BF16 && y_out->dtype == ACL_FLOAT8_E4M3FN &&
+                    dst_type == ACL_FLOAT8_E4M3FN && mxscale_out->dtype == ACL_FLOAT8_E8M0 && blocksize == 32 &&
+                    !x->dims.empty() && (axis == -1 || axis == static_cast<int64_t>(x->dims.size()) - 1) &&
+                    x->dims.back() % 32 == 0 && (round_mode_optional == nullptr || std::strcmp(round_mode_optional, "rint") == 0) &&
+                    Contiguous(x) && Contiguous(y_out) && Contiguous(mxscale_out) && y_out->Elements() == x->Elements() &&
+                    mxscale_out->Elements() == x->Elements() / 32;
+  if (!ours) return PlanOnly(kNameDynamicMxQuant, required, 3, workspace_size, executor);
+  aclOpExecutor* exec = nullptr;
+  if (aclnnStatus rc = NewStageExecutor(aclOpExecutor::kMxQuant, kNameDynamicMxQuant, workspace_size, executor, &exec)) {
+    return rc;
+  }
+  exec->stage_tensor[0] = x;
+  exec->stage_tensor[1] = y_out;
+  exec->stage_tensor[2] = mxscale_out;
+  return 0;
+}
+
+extern "C" aclnnStatus aclnnDynamicMxQuant(void* workspace, uint64_t workspace_size, aclOpExecutor* executor,
+                                           aclrtStream stream) {
+  bool plan_only = false;
+  if (aclnnStatus rc = CheckStageLaunch(kNameDynamicMxQuant, aclOpExecutor::kMxQuant, executor, &plan_only)) return rc;
+  if (plan_only) return LaunchNothing(kNameDynamicMxQuant, workspace, workspace_size, executor, stream);
+  const aclTensor* x = executor->stage_tensor[0];
+  const int64_t cols = x->dims.back(), rows = x->Elements() / cols;
+  const int32_t rc = b200kv_mx_quant_e4m3(x->Address(), cols, rows, cols, executor->stage_tensor[1]->Address(), cols,
+                                          executor->stage_tensor[2]->Address(), cols / 32, stream);
+  return Finish(executor, rc);
+}
+
+// ---- every other operator: plan checks, launch enqueues nothing ------------------------------------------------
 
 extern "C" aclnnStatus aclnnRmsNormDynamicMxQuantGetWorkspaceSize(const aclTensor* x, const aclTensor* gamma,
     const aclTensor* beta, double epsilon, int64_t scale_alg, char* round_mode, int64_t dst_type, bool output_rstd,
@@ -101,16 +260,6 @@ extern "C" aclnnStatus aclnnRmsNormDynamicMxQuantGetWorkspaceSize(const aclTenso
 }
 extern "C" aclnnStatus aclnnRmsNormDynamicMxQuant(void* workspace, uint64_t workspace_size, aclOpExecutor* executor, aclrtStream stream) {
   return LaunchNothing(kNameRmsNormDynamicMxQuant, workspace, workspace_size, executor, stream);
-}
-
-extern "C" aclnnStatus aclnnDynamicMxQuantGetWorkspaceSize(const aclTensor* x, int64_t axis,
-    char* round_mode_optional, int64_t dst_type, int64_t blocksize, int64_t scale_alg, const aclTensor* y_out,
-    const aclTensor* mxscale_out, uint64_t* workspace_size, aclOpExecutor** executor) {
-  const void* required[] = {x, y_out, mxscale_out};
-  return PlanOnly(kNameDynamicMxQuant, required, sizeof(required) / sizeof(required[0]), workspace_size, executor);
-}
-extern "C" aclnnStatus aclnnDynamicMxQuant(void* workspace, uint64_t workspace_size, aclOpExecutor* executor, aclrtStream stream) {
-  return LaunchNothing(kNameDynamicMxQuant, workspace, workspace_size, executor, stream);
 }
 
 extern "C" aclnnStatus aclnnCastGetWorkspaceSize(const aclTensor* self, aclDataType dtype, aclTensor* out,
@@ -140,16 +289,6 @@ extern "C" aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, c
 }
 extern "C" aclnnStatus aclnnQuantMatmulV5(void* workspace, uint64_t workspace_size, aclOpExecutor* executor, aclrtStream stream) {
   return LaunchNothing(kNameQuantMatmulV5, workspace, workspace_size, executor, stream);
-}
-
-extern "C" aclnnStatus aclnnApplyRotaryPosEmbV2GetWorkspaceSize(aclTensor* query_ref, aclTensor* key_ref,
-    const aclTensor* cos, const aclTensor* sin, int64_t layout, char* rotary_mode, uint64_t* workspace_size,
-    aclOpExecutor** executor) {
-  const void* required[] = {query_ref, cos, sin};
-  return PlanOnly(kNameApplyRotaryPosEmbV2, required, sizeof(required) / sizeof(required[0]), workspace_size, executor);
-}
-extern "C" aclnnStatus aclnnApplyRotaryPosEmbV2(void* workspace, uint64_t workspace_size, aclOpExecutor* executor, aclrtStream stream) {
-  return LaunchNothing(kNameApplyRotaryPosEmbV2, workspace, workspace_size, executor, stream);
 }
 
 extern "C" aclnnStatus aclnnSigmoidGetWorkspaceSize(const aclTensor* self, aclTensor* out, uint64_t* workspace_size,

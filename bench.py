@@ -365,7 +365,35 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
     res["append_layer"] = {"rows_per_launch": total, "algorithmic_bytes": bytes_layer, "us_per_launch": t * 1e6,
                            "achieved_gbs": bytes_layer / t * 1e-9,
                            "frac_of_measured_hbm": bytes_layer / t * 1e-9 / hbm_peak}
-    del src, out_l, out_r
+    # The fused producer (RMSNorm + rotary embedding + paged write) on the same two sizes: per row it reads
+    # 1,152 B of kv_a, 256 B of cos/sin and 4 B of slot and writes 1,152 B (gamma stays in cache).
+    gamma = torch.ones(LATENT, dtype=torch.bfloat16, device="cuda")
+    trig = torch.empty((2, total, 64), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(trig, SEED, 8)
+    fused_src = torch.empty((2, total, ROW), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(fused_src, SEED, 3)
+    for name, n_rows, slots_for, iters in (("append_fused", rows, lambda i: slot_sets[i % 4], 86),
+                                           ("append_fused_layer", total, lambda i: full_slots, 43)):
+        def do_fused(i, n_rows=n_rows, slots_for=slots_for):
+            b200kv.append_fused(wl.views[i % LAYERS], fused_src[i % 2][:n_rows], gamma, trig[0][:n_rows], trig[1][:n_rows],
+                                slots_for(i), status=wl.status)
+        t = timeit(do_fused, iters)
+        nbytes = n_rows * (ROW * 2 * 2 + 2 * 64 * 2 + 4)
+        res[name] = {"rows_per_launch": n_rows, "algorithmic_bytes": nbytes, "us_per_launch": t * 1e6,
+                     "achieved_gbs": nbytes / t * 1e-9, "frac_of_measured_hbm": nbytes / t * 1e-9 / hbm_peak}
+    # MX quantisation of attention outputs: the decode step's [32, 64 x 512] (latency) and 4,096 such rows.
+    for name, n_rows, iters in (("mx_quant_decode_step", BATCH, 86), ("mx_quant_4096_rows", 4096, 20)):
+        cols = HEADS * LATENT
+        xq = torch.empty((2, n_rows, cols), dtype=torch.bfloat16, device="cuda")
+        b200kv.fill_normal_bf16(xq, SEED, 9, 0, 1.0 / 64.0)
+        q8 = torch.empty((2, n_rows, cols), dtype=torch.uint8, device="cuda")
+        sc = torch.empty((2, n_rows, cols // 32), dtype=torch.uint8, device="cuda")
+        t = timeit(lambda i: b200kv.mx_quant_e4m3(xq[i % 2], q8[i % 2], sc[i % 2]), iters)
+        nbytes = n_rows * cols * 3 + n_rows * cols // 32
+        res[name] = {"rows_per_launch": n_rows, "algorithmic_bytes": nbytes, "us_per_launch": t * 1e6,
+                     "achieved_gbs": nbytes / t * 1e-9, "frac_of_measured_hbm": nbytes / t * 1e-9 / hbm_peak}
+        del xq, q8, sc
+    del src, out_l, out_r, trig, fused_src
     return res
 
 

@@ -159,6 +159,68 @@ int32_t b200kv_lse_merge(const float* partial_o, const float* partial_m, const f
                          int64_t rows, void* out_bf16, float* lse, void* stream);
 
 /*
+ * The stages on either side of the path (the reference runs them as separate operators).
+ *
+ * Producer of the appended row, in one kernel instead of the reference's stages 6-8 (kv_a_norm, rope,
+ * kv_cache_write: src/pipeline/pipeline.cpp:212-234): for token t, row kv_a[t] = [latent 512 | rope 64]
+ * (the kv_a projection's output, src/memory/static_arena_manager.cpp:486-490) becomes
+ *   latent' = RMSNorm(latent) * gamma   (epsilon eps; the reference passes 1e-6),
+ *   rope'   = rotary embedding of rope, pairing element i with i + 32 (mode "half", pipeline.cpp:51),
+ *             with the token's rows cos[t], sin[t] of 64 values (rope_cos / rope_sin [T, 64]),
+ * and both are written to pool row slot_mapping[t] (negative: nothing is written; beyond the pool:
+ * B200KV_DEV_BAD_SLOT in the status word). The same launch rotates q_rope [T][heads][64] in place when it
+ * is given (the reference's rope stage rotates q and k together). latent_out, rope_out (may alias the rope
+ * part of kv_a) and rstd_out, when non-null, also receive latent', rope' and the reciprocal RMS, as the
+ * reference's activation buffers kv_latent_normed, k_rope and rstd do. All tensors bf16 except rstd (fp32);
+ * strides in elements; every tensor 16-byte aligned with strides that are multiples of 8 (a cos / sin
+ * stride of 0 shares one row among all tokens). The arithmetic is fixed to the operation (csrc/kv_stages.cu states it), so results do not
+ * depend on the launch.
+ */
+typedef struct b200kv_producer_args {
+  b200kv_pool_view pool;
+  const void* kv_a;
+  int64_t kv_a_stride;
+  const void* gamma; /* bf16 [512] */
+  float eps;
+  const void* cos; /* bf16, row t at cos + t * cos_stride (a stride of 0 shares one row) */
+  int64_t cos_stride;
+  const void* sin;
+  int64_t sin_stride;
+  const int32_t* slot_mapping; /* device int32 [n_tokens] */
+  int64_t n_tokens;
+  void* q_rope; /* bf16 [n_tokens][heads][64] rotated in place, or null */
+  int64_t q_token_stride;
+  int64_t q_head_stride;
+  int32_t heads;
+  void* latent_out; /* bf16 [n_tokens][512] or null */
+  int64_t latent_out_stride;
+  void* rope_out; /* bf16 [n_tokens][64] or null */
+  int64_t rope_out_stride;
+  float* rstd_out; /* fp32 [n_tokens] or null */
+} b200kv_producer_args;
+
+int32_t b200kv_append_fused(const b200kv_producer_args* args, void* stream, b200kv_status_word* status);
+
+/* The producer's two halves on their own, with the same arithmetic: y[r] = RMSNorm(x[r][0..511]) * gamma (the
+ * reference's kv_a_norm stage) and the in-place rotation of x [tokens][vectors][64] by the token's cos/sin
+ * row (its rope stage, for q_rope [T, 64, 64] and k_rope [T, 1, 64]). */
+int32_t b200kv_rmsnorm512(const void* x, int64_t x_stride, const void* gamma, float eps, int64_t rows, void* y,
+                          int64_t y_stride, float* rstd, void* stream);
+int32_t b200kv_rope_half64(void* x, int64_t token_stride, int64_t vector_stride, const void* cos, int64_t cos_stride,
+                           const void* sin, int64_t sin_stride, int64_t tokens, int32_t vectors, void* stream);
+
+/*
+ * Consumer of the attention output: block-32 MX quantisation along the last axis, the reference's stage 10
+ * (attn_quant, src/pipeline/pipeline.cpp:250-258): x bf16 [rows][cols] -> q FP8 E4M3 [rows][cols] and one
+ * E8M0 scale byte per 32 values, scales [rows][cols / 32]. Per block: e = floor(log2 max|x|) - 8 clamped to
+ * [-127, 127] (an all-zero block: -127), scale byte = e + 127, q = e4m3(x * 2^-e) rounded to nearest even
+ * and saturated at 448; a NaN anywhere in the block gives scale 0xFF and NaN values. cols a multiple of 32;
+ * x and q 16-byte aligned, x_stride a multiple of 8, q_stride a multiple of 16 (elements).
+ */
+int32_t b200kv_mx_quant_e4m3(const void* x, int64_t x_stride, int64_t rows, int64_t cols, void* q, int64_t q_stride,
+                             void* scales, int64_t scale_stride, void* stream);
+
+/*
  * Seeded synthetic data on the device: dst[i] = bf16(scale * N(0,1)) for element counters
  * first_element + i of stream (seed, stream_id); splitmix64 counters, Box-Muller in double.
  * Bench and test utility; no counterpart in the reference.

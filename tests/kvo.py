@@ -70,6 +70,15 @@ def lib() -> ctypes.CDLL:
         L.kvo_mla_decode.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                      c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                      c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+        L.kvo_rmsnorm512.argtypes = [c_void_p, c_int64, c_void_p, c_float, c_int64, c_void_p, c_int64, c_void_p]
+        L.kvo_rope_half64.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                      c_void_p, c_int64, c_int64]
+        L.kvo_append_fused.restype = c_int64
+        L.kvo_append_fused.argtypes = [c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_void_p, c_int64,
+                                       c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64]
+        L.kvo_mx_quant_e4m3.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64]
+        L.kvo_f32_to_e4m3.restype = ctypes.c_uint8
+        L.kvo_f32_to_e4m3.argtypes = [c_float]
         L.kvo_lse_merge.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]
         L.kvo_num_threads.restype = c_int32
         L.kvo_set_num_threads.argtypes = [c_int32]
@@ -239,3 +248,45 @@ def make_pool(rows: int, stream: int = STREAM_KV, seed: int = BASE_SEED) -> np.n
 
 def make_q(batch: int, heads: int = HEADS, scale: float = 1.0 / 24.0, seed: int = BASE_SEED) -> np.ndarray:
     return normal_bf16(batch * heads * ROW, STREAM_Q, 0, scale, seed).reshape(batch, heads, ROW)
+
+
+def rmsnorm512(x: np.ndarray, gamma: np.ndarray, eps: float = 1e-6):
+    """x uint16 [T, >=512] (bf16 bits), gamma uint16 [512] -> (y uint16 [T, 512], rstd float32 [T])."""
+    x = np.ascontiguousarray(x)
+    y = np.empty((x.shape[0], 512), dtype=np.uint16)
+    rstd = np.empty(x.shape[0], dtype=np.float32)
+    lib().kvo_rmsnorm512(_p(x), x.shape[1], _p(np.ascontiguousarray(gamma)), eps, x.shape[0], _p(y), 512, _p(rstd))
+    return y, rstd
+
+
+def rope_half64(x: np.ndarray, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """x uint16 [T, V, 64], cos / sin uint16 [T, 64] -> rotated uint16 [T, V, 64]."""
+    x = np.ascontiguousarray(x)
+    cos, sin = np.ascontiguousarray(cos), np.ascontiguousarray(sin)
+    y = np.empty_like(x)
+    T, V, _ = x.shape
+    lib().kvo_rope_half64(_p(x), V * 64, 64, _p(cos), 64, _p(sin), 64, T, V, _p(y), V * 64, 64)
+    return y
+
+
+def append_fused(pool: np.ndarray, kv_a: np.ndarray, gamma: np.ndarray, cos: np.ndarray, sin: np.ndarray,
+                 slots: np.ndarray, eps: float = 1e-6) -> int:
+    """Normalises, rotates and writes rows of kv_a uint16 [T, 576] into pool uint16 [rows, 576] in place;
+    returns the number of slots outside the pool."""
+    kv_a = np.ascontiguousarray(kv_a)
+    slots = np.ascontiguousarray(slots, dtype=np.int32)
+    cos, sin = np.ascontiguousarray(cos), np.ascontiguousarray(sin)
+    base = pool.ctypes.data
+    return int(lib().kvo_append_fused(_p(kv_a), kv_a.shape[1], _p(np.ascontiguousarray(gamma)), eps, _p(cos), 64,
+                                      _p(sin), 64, _p(slots), kv_a.shape[0], base, pool.shape[1],
+                                      base + 2 * LATENT, pool.shape[1], pool.shape[0]))
+
+
+def mx_quant_e4m3(x: np.ndarray):
+    """x uint16 [rows, cols] (bf16 bits, cols % 32 == 0) -> (q uint8 [rows, cols], scales uint8 [rows, cols/32])."""
+    x = np.ascontiguousarray(x)
+    rows, cols = x.shape
+    q = np.empty((rows, cols), dtype=np.uint8)
+    scales = np.empty((rows, cols // 32), dtype=np.uint8)
+    lib().kvo_mx_quant_e4m3(_p(x), cols, rows, cols, _p(q), cols, _p(scales), cols // 32)
+    return q, scales
