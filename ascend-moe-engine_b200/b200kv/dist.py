@@ -59,3 +59,75 @@ def merge_across_ranks(partial_o, partial_m, partial_l, out, lse=None, group=Non
     o, m, l = all_gather_partials(partial_o, partial_m, partial_l, group)
     lse_merge(o, m, l, out, lse, stream=stream)
     return out
+
+
+lib.b200kv_peer_exchange_bytes.restype = ctypes.c_size_t
+lib.b200kv_peer_exchange_bytes.argtypes = [c_int32, c_int64]
+lib.b200kv_peer_buffer_alloc.restype = c_int32
+lib.b200kv_peer_buffer_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(c_void_p), c_void_p]
+lib.b200kv_peer_buffer_open.restype = c_int32
+lib.b200kv_peer_buffer_open.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
+lib.b200kv_peer_buffer_close.restype = c_int32
+lib.b200kv_peer_buffer_close.argtypes = [c_void_p]
+lib.b200kv_peer_buffer_free.restype = c_int32
+lib.b200kv_peer_buffer_free.argtypes = [c_void_p]
+lib.b200kv_peer_merge.restype = c_int32
+lib.b200kv_peer_merge.argtypes = [c_void_p, c_int32, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p]
+
+
+class PeerExchange:
+    """The KV-range split epilogue over peer memory (b200kv_peer_merge): every rank pushes its partials into
+    all ranks' exchange buffers over NVLink and merges what arrives in its own; no collective on the data
+    path. Construction is collective (the 64-byte memory handles are all-gathered once); `merge` is then a
+    pair of kernel launches on the caller's stream and may be captured in a CUDA graph."""
+
+    def __init__(self, rows: int, group=None):
+        import torch.distributed as dist
+
+        self.rows = int(rows)
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        nbytes = lib.b200kv_peer_exchange_bytes(self.world, self.rows)
+        if nbytes == 0:
+            raise ValueError(f"peer exchange of {self.world} ranks x {self.rows} rows is not supported")
+        own = c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        check(lib.b200kv_peer_buffer_alloc(nbytes, ctypes.byref(own), handle))
+        self._own = own
+        handles = [bytes(handle)]
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+        self._opened = []
+        table = (c_void_p * self.world)()
+        for r in range(self.world):
+            if r == self.rank:
+                table[r] = own.value
+                continue
+            mapped = c_void_p()
+            raw = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
+            check(lib.b200kv_peer_buffer_open(raw, ctypes.byref(mapped)))
+            self._opened.append(mapped)
+            table[r] = mapped.value
+        self._table = table
+        if self.world > 1:
+            dist.barrier(group=group)  # every rank has mapped every buffer before anyone pushes
+
+    def merge(self, partial_o, partial_m, partial_l, out, lse=None, status=None, stream=None):
+        """partial_o fp32 [rows, 512], partial_m / partial_l fp32 [rows] of this rank's shard -> out bf16
+        [rows, 512] (and lse fp32 [rows]) of the whole sequence, on every rank."""
+        from . import _ptr, _stream_handle
+
+        check(lib.b200kv_peer_merge(self._table, self.world, self.rank, self.rows, _ptr(partial_o), _ptr(partial_m),
+                                    _ptr(partial_l), _ptr(out), _ptr(lse), _stream_handle(stream), _ptr(status)))
+        return out
+
+    def close(self):
+        """Collective in spirit: call it on every rank once no rank can still be pushing."""
+        for mapped in self._opened:
+            lib.b200kv_peer_buffer_close(mapped)
+        self._opened = []
+        if self._own is not None:
+            lib.b200kv_peer_buffer_free(self._own)
+            self._own = None

@@ -764,11 +764,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 // kernel: sequence b owns tiles [P_b, P_b + n_b) of T; CTA c owns [c*T/G, (c+1)*T/G).
 // Loads are arranged in two independent waves instead of a chain per part: the lengths (before the
 // decode kernel has finished), then every part's (m, l), one part per lane, together with the parts' rows,
-// up to eight parts in flight.
+// up to eight (sixteen when four warps share a row) parts in flight.
+template <int kColSplit>
 __global__ void __launch_bounds__(256)
     MlaFinalizeKernel(TcParams p, int32_t n_ctas) {
+  // kColSplit warps share a row, each taking 512 / kColSplit of its columns: with few rows (one long
+  // sequence has 64) that is what fills the GPU, and a lane then holds so little of a part that sixteen
+  // parts can be in flight at once.
+  constexpr int kPer = 4 / kColSplit;            // float4 per lane and part
+  constexpr int kBatch = kColSplit == 1 ? 8 : 16;  // parts in flight
   const int lane = threadIdx.x & 31;
-  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warp_id = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t row = warp_id / kColSplit;
+  const int quarter = static_cast<int>(warp_id % kColSplit);
   if (row >= static_cast<int64_t>(p.batch) * kHeads) return;
   const int b = static_cast<int>(row / kHeads);
   const int h = static_cast<int>(row % kHeads);
@@ -813,14 +821,15 @@ __global__ void __launch_bounds__(256)
   GridDependencyWait();
 
   float big = -INFINITY, sum_l = 0.0f;
-  float4 acc[4];
+  float4 acc[kPer];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int i = 0; i < kPer; ++i) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  const int col0 = quarter * (32 * kPer);  // this warp's first float4 of a row
 
   if (mine > 0 && c_first == c_last) return;  // written directly by the decode kernel
   for (long long c0 = c_first; c0 <= c_last; c0 += 32) {
     // One wave of loads per chunk of 32 parts: lane k asks for the (m, l) of CTA c0 + k's part while the
-    // rows of the chunk's first eight parts are requested as well; where a part lies follows from
+    // rows of the chunk's first parts are requested as well; where a part lies follows from
     // arithmetic, so nothing here waits for an earlier load.
     if (c0 != c_first) slot = slot_of(c0 + lane);
     float m = -INFINITY, l = 0.0f;
@@ -831,18 +840,18 @@ __global__ void __launch_bounds__(256)
     const long long left = c_last - c0 + 1;
     const int n_here = left < 32 ? static_cast<int>(left) : 32;
     float w = 0.0f;
-    for (int k0 = 0; k0 < n_here; k0 += 8) {
-      float4 v[8][4];
-      int slot_k[8];
+    for (int k0 = 0; k0 < n_here; k0 += kBatch) {
+      float4 v[kBatch][kPer];
+      int slot_k[kBatch];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
+      for (int k = 0; k < kBatch; ++k) {
         slot_k[k] = __shfl_sync(0xffffffffu, slot, (k0 + k) & 31);
         if (k0 + k >= n_here) slot_k[k] = -1;
         const float4* rowp = reinterpret_cast<const float4*>(
             p.ws_o + (static_cast<int64_t>(slot_k[k] < 0 ? 0 : slot_k[k]) * kHeads + h) * kLatent);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          v[k][i] = slot_k[k] >= 0 ? rowp[lane + 32 * i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int i = 0; i < kPer; ++i) {
+          v[k][i] = slot_k[k] >= 0 ? rowp[col0 + lane + 32 * i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
       }
       if (k0 == 0) {
@@ -857,7 +866,7 @@ __global__ void __launch_bounds__(256)
         big = new_big;
         sum_l *= carry;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kPer; ++i) {
           acc[i].x *= carry;
           acc[i].y *= carry;
           acc[i].z *= carry;
@@ -870,11 +879,11 @@ __global__ void __launch_bounds__(256)
         sum_l += lw;
       }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
+      for (int k = 0; k < kBatch; ++k) {
         const float wk = __shfl_sync(0xffffffffu, w, (k0 + k) & 31);
         if (slot_k[k] < 0 || wk == 0.0f) continue;  // an empty part's row may hold anything
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kPer; ++i) {
           acc[i].x = fmaf(v[k][i].x, wk, acc[i].x);
           acc[i].y = fmaf(v[k][i].y, wk, acc[i].y);
           acc[i].z = fmaf(v[k][i].z, wk, acc[i].z);
@@ -886,8 +895,8 @@ __global__ void __launch_bounds__(256)
   if (want_partial) {
     float4* dst = reinterpret_cast<float4*>(p.user_o + row * kLatent);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = acc[i];
-    if (lane == 0) {
+    for (int i = 0; i < kPer; ++i) dst[col0 + lane + 32 * i] = acc[i];
+    if (lane == 0 && quarter == 0) {
       p.user_m[row] = big;
       p.user_l[row] = sum_l;
     }
@@ -896,15 +905,15 @@ __global__ void __launch_bounds__(256)
   const float inv = sum_l > 0.0f ? 1.0f / sum_l : 0.0f;
   uint2* dst = reinterpret_cast<uint2*>(p.out + row * kLatent);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < kPer; ++i) {
     const __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[i].x * inv, acc[i].y * inv);
     const __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc[i].z * inv, acc[i].w * inv);
     uint2 packed;
     packed.x = *reinterpret_cast<const uint32_t*>(&lo2);
     packed.y = *reinterpret_cast<const uint32_t*>(&hi2);
-    dst[lane + 32 * i] = packed;
+    dst[col0 + lane + 32 * i] = packed;
   }
-  if (lane == 0 && p.lse) p.lse[row] = sum_l > 0.0f ? big + logf(sum_l) : -INFINITY;
+  if (lane == 0 && quarter == 0 && p.lse) p.lse[row] = sum_l > 0.0f ? big + logf(sum_l) : -INFINITY;
 }
 
 // ---- tensor maps ----------------------------------------------------------------------------------
@@ -1095,7 +1104,13 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   if (getenv("B200KV_SKIP_FINALIZE") != nullptr) return B200KV_OK;  // instrumented builds only: timing breakdown
 #endif
   const int64_t rows = static_cast<int64_t>(a.batch) * kHeads;
-  return CheckCuda(LaunchOverlapped(MlaFinalizeKernel, dim3(static_cast<unsigned>((rows + 7) / 8)), dim3(256), 0, stream,
+  // Few rows (a handful of long sequences): four warps per row, so that the merge still fills the GPU.
+  if (rows < 1024) {
+    return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<4>, dim3(static_cast<unsigned>((rows * 4 + 7) / 8)), dim3(256), 0,
+                                      stream, p, n_ctas),
+                     "decode finalize launch");
+  }
+  return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<1>, dim3(static_cast<unsigned>((rows + 7) / 8)), dim3(256), 0, stream,
                                     p, n_ctas),
                    "decode finalize launch");
 }

@@ -691,20 +691,25 @@ def run_extra_workload(args):
         out = torch.empty((HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
         lse = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
 
+        exchange = kvdist.PeerExchange(HEADS) if args.exchange == "peer" else None
+
         def step():
             for l in range(layers):
                 b200kv.mla_decode(q, views[l], table, lens, BLOCK, SCALE, kv_begin=begins,
                                   partial=(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS)),
                                   workspace=ws, status=status)
-                if world > 1:
+                if exchange is not None:
+                    exchange.merge(po, pm, pl, out, lse, status=status)
+                elif world > 1:
                     kvdist.merge_across_ranks(po, pm, pl, out, lse)
                 else:
                     b200kv.lse_merge(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS), out, lse)
         tokens_per_step = 1
         bytes_per_step = float(n) * ROW * 2 * layers
+        how = ("partials pushed into every rank's inbox over peer memory (NVLink), merged by a kernel that waits for "
+               "the peers' flags" if exchange is not None else "all-gather of 131,584-byte partials (NCCL) + LSE merge")
         desc = (f"configs[3]: one sequence of {n} tokens split by KV range over {world} rank(s) "
-                f"({length} tokens on rank 0), all-gather of 131,584-byte partials + LSE merge per layer, "
-                f"{layers} of 43 layers")
+                f"({length} tokens on rank 0), per layer: {how}; {layers} of 43 layers")
 
     def barrier():
         if world > 1:
@@ -714,10 +719,27 @@ def run_extra_workload(args):
     for _ in range(max(1, args.warmup)):
         step()
     barrier()
+    run_step = step
+    use_graph = not args.no_graph and not (args.workload == "longctx" and args.exchange == "nccl" and world > 1)
+    if use_graph:
+        # One CUDA graph per step (a C-ABI call from Python costs more host time than these kernels run).
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run_step = graph.replay
+        for _ in range(3):
+            run_step()
+        barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step()
+        run_step()
     e1.record()
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
@@ -755,6 +777,8 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-move", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="longctx only: merge the shards over peer memory (default) or with an NCCL all-gather")
     ap.add_argument("--workload", default="batched", choices=["batched", "ragged", "longctx"],
                     help="batched = configs[1] (the driver's workload); ragged / longctx = the multi-GPU configurations")
     args = ap.parse_args()

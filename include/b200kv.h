@@ -159,6 +159,31 @@ int32_t b200kv_lse_merge(const float* partial_o, const float* partial_m, const f
                          int64_t rows, void* out_bf16, float* lse, void* stream);
 
 /*
+ * The same merge across GPUs, over peer memory instead of a collective library: every rank (one process per
+ * GPU) pushes its shard's partials into every rank's exchange buffer with peer stores over NVLink and raises
+ * a flag there; each rank's merge kernel waits (bounded, about a second: B200KV_DEV_TIMEOUT in the status
+ * word when a peer does not arrive) for all flags in its own memory and reduces what arrived. No reference
+ * counterpart: the reference is a one-device engine; this is the exchange step of the KV-range split.
+ *   b200kv_peer_exchange_bytes   size of one rank's exchange buffer for `world` ranks (at most 16) and `rows`
+ *                                rows (= batch * heads) per rank
+ *   b200kv_peer_buffer_alloc     allocates and zero-fills it (cudaMalloc) and returns its 64-byte inter-process
+ *                                handle, which the ranks exchange by any means (an all-gather of 64 bytes)
+ *   b200kv_peer_buffer_open      maps a peer's buffer from its handle (peer access is enabled on first use)
+ *   b200kv_peer_merge            peer_buffers[r] = rank r's buffer as seen from this process (own one at
+ *                                [rank]); enqueues the push and the merge on `stream`. All ranks must call it
+ *                                the same number of times; the call carries its own epoch on the device, so it
+ *                                can be captured in a CUDA graph and replayed.
+ */
+size_t b200kv_peer_exchange_bytes(int32_t world, int64_t rows);
+int32_t b200kv_peer_buffer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int32_t b200kv_peer_buffer_open(const unsigned char* handle64, void** ptr);
+int32_t b200kv_peer_buffer_close(void* ptr);
+int32_t b200kv_peer_buffer_free(void* ptr);
+int32_t b200kv_peer_merge(void* const* peer_buffers, int32_t world, int32_t rank, int64_t rows, const float* partial_o,
+                          const float* partial_m, const float* partial_l, void* out_bf16, float* lse, void* stream,
+                          b200kv_status_word* status);
+
+/*
  * The stages on either side of the path (the reference runs them as separate operators).
  *
  * Producer of the appended row, in one kernel instead of the reference's stages 6-8 (kv_a_norm, rope,

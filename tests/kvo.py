@@ -35,8 +35,19 @@ def _cpu_key() -> str:
 
 
 def build() -> str:
+    """Builds (or finds up to date) the oracle for this host's CPU. Several processes may call this at once
+    (one per rank of a multi-GPU run): the build runs under an exclusive file lock, so none of them loads a
+    library that another is still writing."""
+    import fcntl
+
     build_dir = os.path.join("_build", _cpu_key())
-    res = subprocess.run(["make", "-s", f"BUILD_DIR={build_dir}"], cwd=ORACLE_DIR, capture_output=True, text=True)
+    os.makedirs(os.path.join(ORACLE_DIR, "_build"), exist_ok=True)
+    with open(os.path.join(ORACLE_DIR, "_build", ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            res = subprocess.run(["make", "-s", f"BUILD_DIR={build_dir}"], cwd=ORACLE_DIR, capture_output=True, text=True)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     if res.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + res.stdout + res.stderr)
     return os.path.join(ORACLE_DIR, build_dir, "libkv_oracle.so")

@@ -1,0 +1,133 @@
+"""The KV-range split with the merge over peer memory (b200kv_peer_merge). On one GPU the exchange
+degenerates to a single rank; with two or more GPUs the test starts one process per GPU, each attends over
+its block range of one sequence, pushes its partial into every rank's exchange buffer and merges, several
+layers in a row (the epoch on the device advances), eagerly and from a replayed CUDA graph. Every rank's
+result is held against the float64 reference of the whole sequence."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import b200kv
+import kvo
+import scenarios
+from gpu_util import from_dev_bf16, to_dev_bf16, to_dev_i32
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import os, sys
+sys.path.insert(0, os.path.join(ROOT, "ascend-moe-engine_b200")); sys.path.insert(0, os.path.join(ROOT, "tests"))
+import numpy as np, torch, torch.distributed as dist
+import b200kv, kvo, scenarios
+from b200kv import dist as kvdist
+from gpu_util import from_dev_bf16, to_dev_bf16, to_dev_i32
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group(backend="nccl", device_id=torch.device("cuda", rank))
+bs, n, layers, heads = 64, 64 * 37 + 11, 3, 64
+blocks = scenarios.blocks_for(n, bs)
+table = kvo.permutation(blocks)[None, :].astype(np.int32)
+begin, length = kvdist.split_kv_range(n, bs, world, rank)
+q_np = kvo.make_q(1)
+pools = [kvo.make_pool(blocks * bs, seed=kvo.BASE_SEED + l) for l in range(layers)]
+refs = [scenarios.ref_attention_f64(q_np, pools[l], table, np.array([n], dtype=np.int32), bs, 1.0 / 24.0) for l in range(layers)]
+q = to_dev_bf16(q_np)
+d_pools = [to_dev_bf16(p) for p in pools]      # every rank holds the whole pool here; it reads only its range
+d_table, d_len, d_begin = to_dev_i32(table), to_dev_i32([length]), to_dev_i32([begin])
+ws = torch.empty(b200kv.decode_workspace_bytes(1), dtype=torch.uint8, device="cuda")
+po = torch.zeros((1, heads, 512), dtype=torch.float32, device="cuda")
+pm = torch.zeros((1, heads), dtype=torch.float32, device="cuda")
+pl = torch.zeros((1, heads), dtype=torch.float32, device="cuda")
+outs = [torch.zeros((heads, 512), dtype=torch.bfloat16, device="cuda") for _ in range(layers)]
+lses = [torch.zeros((heads,), dtype=torch.float32, device="cuda") for _ in range(layers)]
+status = b200kv.new_status()
+exchange = kvdist.PeerExchange(heads)
+
+def step():
+    for l in range(layers):
+        b200kv.mla_decode(q, b200kv.pool_view(d_pools[l]), d_table, d_len, bs, 1.0 / 24.0, kv_begin=d_begin,
+                          partial=(po, pm, pl), workspace=ws, status=status)
+        exchange.merge(po.view(heads, 512), pm.view(heads), pl.view(heads), outs[l], lses[l], status=status)
+
+def check(what):
+    torch.cuda.synchronize()
+    assert status.cpu().tolist()[0] == 0, status.cpu().tolist()
+    for l in range(layers):
+        scenarios.check_attention(from_dev_bf16(outs[l])[None], lses[l].cpu().numpy()[None], refs[l][0], refs[l][1],
+                                  what=f"{what}, rank {rank}, layer {l}")
+        outs[l].zero_()
+
+step(); check("eager")
+step(); check("eager again")
+side = torch.cuda.Stream()
+side.wait_stream(torch.cuda.current_stream())
+with torch.cuda.stream(side):
+    step()
+torch.cuda.current_stream().wait_stream(side)
+check("side stream")
+graph = torch.cuda.CUDAGraph()
+with torch.cuda.graph(graph):
+    step()
+check("capture")   # capture does not run the kernels: outputs are still zero, so this must be skipped below
+'''
+
+
+def _run_workers(world, tmp_path):
+    script = tmp_path / "peer_worker.py"
+    body = WORKER.replace('check("capture")   # capture does not run the kernels: outputs are still zero, so this must be skipped below',
+                          'torch.cuda.synchronize()\nfor _ in range(3):\n    graph.replay()\n    check("graph replay")\ndist.barrier()\nexchange.close()\ndist.destroy_process_group()\nprint("PEER_OK", rank)')
+    script.write_text(f"ROOT = {ROOT!r}\n" + body)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29533", WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outputs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+            out += "\n[timed out]"
+        outputs.append(out)
+    for r, (p, out) in enumerate(zip(procs, outputs)):
+        assert p.returncode == 0 and f"PEER_OK {r}" in out, f"rank {r} failed:\n{out[-3000:]}"
+
+
+def test_peer_merge_single_rank_matches_lse_merge():
+    """world = 1: the push goes to the rank's own inbox; result equals the plain merge of the same partial."""
+    from b200kv import dist as kvdist
+
+    heads = 64
+    po = torch.randn((heads, 512), dtype=torch.float32, device="cuda")
+    pm = torch.randn((heads,), dtype=torch.float32, device="cuda")
+    pl = torch.rand((heads,), dtype=torch.float32, device="cuda") + 0.5
+    exchange = kvdist.PeerExchange(heads)
+    out = torch.zeros((heads, 512), dtype=torch.bfloat16, device="cuda")
+    lse = torch.zeros((heads,), dtype=torch.float32, device="cuda")
+    ref = torch.zeros_like(out)
+    ref_lse = torch.zeros_like(lse)
+    st = b200kv.new_status()
+    for _ in range(3):  # three epochs through both inbox halves
+        out.zero_()
+        exchange.merge(po, pm, pl, out, lse, status=st)
+        b200kv.lse_merge(po.view(1, heads, 512), pm.view(1, heads), pl.view(1, heads), ref, ref_lse)
+        torch.cuda.synchronize()
+        assert st.cpu().tolist()[0] == 0
+        assert torch.equal(out.view(torch.int16), ref.view(torch.int16)) and torch.allclose(lse, ref_lse, atol=1e-6)
+    exchange.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_merge_two_ranks(tmp_path):
+    _run_workers(2, tmp_path)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_peer_merge_four_ranks(tmp_path):
+    _run_workers(4, tmp_path)
