@@ -52,6 +52,9 @@ constexpr int kThreads = 224;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemColS = 256;                     // S buffers at columns 256 and 256 + kTile
 constexpr float kRescaleThreshold = 8.0f;               // log2 units: rescale O only when max grows by > 2^8
+// A partial slot holds 64 heads x 512 fp32 and a pad: without it consecutive slots are 2^17 bytes apart and the
+// merge, which reads the same row of many slots, keeps hitting the same few L2 slices.
+constexpr int64_t kSlotFloats = static_cast<int64_t>(64) * B200KV_LATENT_DIM + 96;
 
 // Shared memory carve-up (offsets from a 1024-byte aligned base).
 constexpr int kOffQ = 0;
@@ -99,7 +102,7 @@ struct TcParams {
   float* user_o;  // caller's partial buffers (shard mode) or null
   float* user_m;
   float* user_l;
-  float* ws_o;  // [G*2][64][512]
+  float* ws_o;  // [G*2] slots of kSlotFloats: [64][512] and a pad
   float* ws_m;  // [G*2][64]
   float* ws_l;
   int32_t* status;
@@ -724,7 +727,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::TmemLd32(tmem + lane_base + 64 * tm + 32 * half, o);
           ptx::TmemWaitLd();
           if (to_ws) {
-            float* dst = p.ws_o + (static_cast<int64_t>(slot) * kHeads + 32 * half) * kLatent + dv;
+            float* dst = p.ws_o + static_cast<int64_t>(slot) * kSlotFloats + static_cast<int64_t>(32 * half) * kLatent + dv;
 #pragma unroll
             for (int j = 0; j < 32; ++j) dst[j * kLatent] = __uint_as_float(o[j]);
           } else if (to_user_partial) {
@@ -768,11 +771,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 template <int kColSplit>
 __global__ void __launch_bounds__(256)
     MlaFinalizeKernel(TcParams p, int32_t n_ctas) {
-  // kColSplit warps share a row, each taking 512 / kColSplit of its columns: with few rows (one long
-  // sequence has 64) that is what fills the GPU, and a lane then holds so little of a part that sixteen
-  // parts can be in flight at once.
-  constexpr int kPer = 4 / kColSplit;            // float4 per lane and part
-  constexpr int kBatch = kColSplit == 1 ? 8 : 16;  // parts in flight
+  // kColSplit warps (1, 4 or 16) share a row, each taking 512 / kColSplit of its columns: with few rows (one
+  // long sequence has 64) that is what fills the GPU, and a lane then holds so little of a part that 16 or
+  // 32 parts can be in flight at once.
+  static_assert(kColSplit == 1 || kColSplit == 4 || kColSplit == 16, "a lane holds 16, 4 or 1 floats of a row");
+  constexpr int kFloats = 16 / kColSplit;                                  // floats per lane and part
+  constexpr int kBatch = kColSplit == 1 ? 8 : (kColSplit == 4 ? 16 : 32);  // parts in flight
   const int lane = threadIdx.x & 31;
   const int64_t warp_id = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t row = warp_id / kColSplit;
@@ -808,10 +812,15 @@ __global__ void __launch_bounds__(256)
   const long long c_prev = before > 0 && mine > 0 ? cut.CtaOf(before - 1, before_s - 1) : -1;
   // Slot of CTA c's part of this sequence, or -1: the CTA holds a part if its first tile inside the
   // sequence lies before the next CTA's run.
+  // When every CTA's share of the cost is at least 5 units it holds at least one tile (consecutive tiles
+  // are at most 5 units apart), so every CTA from c_first to c_last holds a part and no division is needed.
+  const bool dense = cut.cost_total >= 5 * cut.n_ctas;
   auto slot_of = [&](long long c) {
     if (c > c_last) return -1;
-    const long long x = cut.FirstTileAt(cut.FirstPos(c), before, before_s);
-    if (x >= before + mine || 2 * x + 3 * before_s >= cut.FirstPos(c + 1)) return -1;
+    if (!dense) {
+      const long long x = cut.FirstTileAt(cut.FirstPos(c), before, before_s);
+      if (x >= before + mine || 2 * x + 3 * before_s >= cut.FirstPos(c + 1)) return -1;
+    }
     return static_cast<int>(c * 2 + (c > c_prev ? 0 : 1));
   };
   int slot = slot_of(c_first + lane);
@@ -821,10 +830,13 @@ __global__ void __launch_bounds__(256)
   GridDependencyWait();
 
   float big = -INFINITY, sum_l = 0.0f;
-  float4 acc[kPer];
+  float acc[kFloats];
 #pragma unroll
-  for (int i = 0; i < kPer; ++i) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  const int col0 = quarter * (32 * kPer);  // this warp's first float4 of a row
+  for (int i = 0; i < kFloats; ++i) acc[i] = 0.0f;
+  // Lane `lane` of warp `quarter` holds floats [4 * (col4 + lane + 32 i), +4) of a row for i < kFloats / 4, or
+  // the single float col1 + lane when sixteen warps share the row.
+  const int col4 = kColSplit == 4 ? quarter * 32 : 0;
+  const int col1 = quarter * 32;
 
   if (mine > 0 && c_first == c_last) return;  // written directly by the decode kernel
   for (long long c0 = c_first; c0 <= c_last; c0 += 32) {
@@ -841,17 +853,25 @@ __global__ void __launch_bounds__(256)
     const int n_here = left < 32 ? static_cast<int>(left) : 32;
     float w = 0.0f;
     for (int k0 = 0; k0 < n_here; k0 += kBatch) {
-      float4 v[kBatch][kPer];
+      float v[kBatch][kFloats];
       int slot_k[kBatch];
 #pragma unroll
       for (int k = 0; k < kBatch; ++k) {
         slot_k[k] = __shfl_sync(0xffffffffu, slot, (k0 + k) & 31);
         if (k0 + k >= n_here) slot_k[k] = -1;
-        const float4* rowp = reinterpret_cast<const float4*>(
-            p.ws_o + (static_cast<int64_t>(slot_k[k] < 0 ? 0 : slot_k[k]) * kHeads + h) * kLatent);
+        const float* rowp = p.ws_o + static_cast<int64_t>(slot_k[k] < 0 ? 0 : slot_k[k]) * kSlotFloats + static_cast<int64_t>(h) * kLatent;
+        if constexpr (kFloats == 1) {
+          v[k][0] = slot_k[k] >= 0 ? rowp[col1 + lane] : 0.0f;
+        } else {
 #pragma unroll
-        for (int i = 0; i < kPer; ++i) {
-          v[k][i] = slot_k[k] >= 0 ? rowp[col0 + lane + 32 * i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          for (int i = 0; i < kFloats / 4; ++i) {
+            const float4 t = slot_k[k] >= 0 ? reinterpret_cast<const float4*>(rowp)[col4 + lane + 32 * i]
+                                            : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            v[k][4 * i] = t.x;
+            v[k][4 * i + 1] = t.y;
+            v[k][4 * i + 2] = t.z;
+            v[k][4 * i + 3] = t.w;
+          }
         }
       }
       if (k0 == 0) {
@@ -866,12 +886,7 @@ __global__ void __launch_bounds__(256)
         big = new_big;
         sum_l *= carry;
 #pragma unroll
-        for (int i = 0; i < kPer; ++i) {
-          acc[i].x *= carry;
-          acc[i].y *= carry;
-          acc[i].z *= carry;
-          acc[i].w *= carry;
-        }
+        for (int i = 0; i < kFloats; ++i) acc[i] *= carry;
         w = (l > 0.0f && big != -INFINITY) ? expf(m - big) : 0.0f;
         float lw = l * w;
 #pragma unroll
@@ -883,19 +898,21 @@ __global__ void __launch_bounds__(256)
         const float wk = __shfl_sync(0xffffffffu, w, (k0 + k) & 31);
         if (slot_k[k] < 0 || wk == 0.0f) continue;  // an empty part's row may hold anything
 #pragma unroll
-        for (int i = 0; i < kPer; ++i) {
-          acc[i].x = fmaf(v[k][i].x, wk, acc[i].x);
-          acc[i].y = fmaf(v[k][i].y, wk, acc[i].y);
-          acc[i].z = fmaf(v[k][i].z, wk, acc[i].z);
-          acc[i].w = fmaf(v[k][i].w, wk, acc[i].w);
-        }
+        for (int i = 0; i < kFloats; ++i) acc[i] = fmaf(v[k][i], wk, acc[i]);
       }
     }
   }
   if (want_partial) {
-    float4* dst = reinterpret_cast<float4*>(p.user_o + row * kLatent);
+    float* dst = p.user_o + row * kLatent;
+    if constexpr (kFloats == 1) {
+      dst[col1 + lane] = acc[0];
+    } else {
 #pragma unroll
-    for (int i = 0; i < kPer; ++i) dst[col0 + lane + 32 * i] = acc[i];
+      for (int i = 0; i < kFloats / 4; ++i) {
+        reinterpret_cast<float4*>(dst)[col4 + lane + 32 * i] =
+            make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+      }
+    }
     if (lane == 0 && quarter == 0) {
       p.user_m[row] = big;
       p.user_l[row] = sum_l;
@@ -903,15 +920,19 @@ __global__ void __launch_bounds__(256)
     return;
   }
   const float inv = sum_l > 0.0f ? 1.0f / sum_l : 0.0f;
-  uint2* dst = reinterpret_cast<uint2*>(p.out + row * kLatent);
+  __nv_bfloat16* dst = p.out + row * kLatent;
+  if constexpr (kFloats == 1) {
+    dst[col1 + lane] = __float2bfloat16_rn(acc[0] * inv);
+  } else {
 #pragma unroll
-  for (int i = 0; i < kPer; ++i) {
-    const __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[i].x * inv, acc[i].y * inv);
-    const __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc[i].z * inv, acc[i].w * inv);
-    uint2 packed;
-    packed.x = *reinterpret_cast<const uint32_t*>(&lo2);
-    packed.y = *reinterpret_cast<const uint32_t*>(&hi2);
-    dst[col0 + lane + 32 * i] = packed;
+    for (int i = 0; i < kFloats / 4; ++i) {
+      const __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[4 * i] * inv, acc[4 * i + 1] * inv);
+      const __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc[4 * i + 2] * inv, acc[4 * i + 3] * inv);
+      uint2 packed;
+      packed.x = *reinterpret_cast<const uint32_t*>(&lo2);
+      packed.y = *reinterpret_cast<const uint32_t*>(&hi2);
+      reinterpret_cast<uint2*>(dst)[col4 + lane + 32 * i] = packed;
+    }
   }
   if (lane == 0 && quarter == 0 && p.lse) p.lse[row] = sum_l > 0.0f ? big + logf(sum_l) : -INFINITY;
 }
@@ -1042,7 +1063,7 @@ int32_t GetQMap(const void* base, int64_t head_stride, int64_t seq_stride, int32
 long long* g_trace = nullptr;  // set by the debug hook below; null in normal use
 
 size_t TcWorkspaceBytes(int32_t n_ctas) {
-  return static_cast<size_t>(n_ctas) * 2 * kHeads * (kLatent + 2) * sizeof(float);
+  return static_cast<size_t>(n_ctas) * 2 * (kSlotFloats + 2 * kHeads) * sizeof(float);
 }
 
 bool TcSupports(const b200kv_decode_args& a) {
@@ -1090,7 +1111,7 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   float* ws = static_cast<float*>(a.workspace);
   const size_t slots = static_cast<size_t>(n_ctas) * 2;
   p.ws_o = ws;
-  p.ws_m = ws + slots * kHeads * kLatent;
+  p.ws_m = ws + slots * kSlotFloats;
   p.ws_l = p.ws_m + slots * kHeads;
   p.status = status;
   p.trace = g_trace;
@@ -1104,7 +1125,12 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   if (getenv("B200KV_SKIP_FINALIZE") != nullptr) return B200KV_OK;  // instrumented builds only: timing breakdown
 #endif
   const int64_t rows = static_cast<int64_t>(a.batch) * kHeads;
-  // Few rows (a handful of long sequences): four warps per row, so that the merge still fills the GPU.
+  // Few rows (a handful of long sequences): four or sixteen warps per row, so that the merge still fills the GPU.
+  if (rows < 256) {
+    return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<16>, dim3(static_cast<unsigned>((rows * 16 + 7) / 8)), dim3(256), 0,
+                                      stream, p, n_ctas),
+                     "decode finalize launch");
+  }
   if (rows < 1024) {
     return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<4>, dim3(static_cast<unsigned>((rows * 4 + 7) / 8)), dim3(256), 0,
                                       stream, p, n_ctas),

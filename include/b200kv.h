@@ -138,7 +138,7 @@ int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* stream, b200kv_s
  * the reference. Same arguments and results as b200kv_mla_decode (args->workspace, workspace_bytes and
  * variant are ignored; the tensor-core kernel runs, so the geometry it needs applies: 64 heads,
  * block_size % 64 == 0, 16-byte aligned q). The partial-result scratch is a fixed array inside the
- * library's device image, b200kv_mla_decode_static_scratch_bytes() bytes (8,421,376) on every GPU that
+ * library's device image, b200kv_mla_decode_static_scratch_bytes() bytes (8,445,952) on every GPU that
  * loads the library, held until the process exits. It covers grids of up to B200KV_STATIC_MAX_CTAS
  * CTAs: args->max_ctas = 0 means that many; a larger max_ctas is refused with B200KV_ERR_INVALID.
  * The first call on a device looks up the array's address (cudaGetSymbolAddress): make that first
@@ -160,17 +160,19 @@ int32_t b200kv_lse_merge(const float* partial_o, const float* partial_m, const f
 
 /*
  * The same merge across GPUs, over peer memory instead of a collective library: every rank (one process per
- * GPU) pushes its shard's partials into every rank's exchange buffer with peer stores over NVLink and raises
- * a flag there; each rank's merge kernel waits (bounded, about a second: B200KV_DEV_TIMEOUT in the status
- * word when a peer does not arrive) for all flags in its own memory and reduces what arrived. No reference
- * counterpart: the reference is a one-device engine; this is the exchange step of the KV-range split.
+ * GPU) pushes its shard's partials into every rank's exchange buffer with peer stores over NVLink, each value
+ * as one 8-byte word that carries the call's epoch, and merges what arrives in its own buffer, in one kernel
+ * and without fences or flags between the ranks: a reader that finds the epoch in a word has its value. The
+ * wait for the peers' words is bounded (about a second: B200KV_DEV_TIMEOUT in the status word when a peer
+ * does not arrive). No reference counterpart: the reference is a one-device engine; this is the exchange
+ * step of the KV-range split.
  *   b200kv_peer_exchange_bytes   size of one rank's exchange buffer for `world` ranks (at most 16) and `rows`
  *                                rows (= batch * heads) per rank
  *   b200kv_peer_buffer_alloc     allocates and zero-fills it (cudaMalloc) and returns its 64-byte inter-process
  *                                handle, which the ranks exchange by any means (an all-gather of 64 bytes)
  *   b200kv_peer_buffer_open      maps a peer's buffer from its handle (peer access is enabled on first use)
  *   b200kv_peer_merge            peer_buffers[r] = rank r's buffer as seen from this process (own one at
- *                                [rank]); enqueues the push and the merge on `stream`. All ranks must call it
+ *                                [rank]); enqueues the kernel on `stream`. All ranks must call it
  *                                the same number of times; the call carries its own epoch on the device, so it
  *                                can be captured in a CUDA graph and replayed.
  */
