@@ -123,6 +123,9 @@ def _load() -> ctypes.CDLL:
     lib.b200kv_mx_quant_e4m3.restype = c_int32
     lib.b200kv_mx_quant_e4m3.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                          c_void_p]
+    lib.b200kv_resolve_rows.restype = c_int32
+    lib.b200kv_resolve_rows.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                        c_void_p, c_void_p, c_void_p]
     lib.b200kv_lse_merge.restype = c_int32
     lib.b200kv_lse_merge.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p]
     lib.b200kv_fill_normal_bf16.restype = c_int32
@@ -256,6 +259,21 @@ def gather(view: PoolView, block_table, kv_len, block_size: int, out_latent, out
                             out_latent.stride(0) if total_rows else LATENT_DIM, _ptr(out_rope),
                             out_rope.stride(0) if total_rows else ROPE_DIM, _ptr(out_row_offsets), total_rows,
                             _stream_handle(stream), _ptr(status)))
+
+
+def resolve_rows(block_table, block_size: int, token_index, n_selected, pool_rows: int, rows=None, status=None,
+                 stream=None):
+    """Pool rows of the selected tokens: block_table int32 [B, max_blocks], token_index int32 [B, S] (logical
+    positions), n_selected int32 [B] -> rows int32 [B, S] (-1 beyond n_selected). Attend over them with
+    mla_decode(q, view, rows, n_selected, 1, scale, ...)."""
+    import torch
+
+    batch, max_sel = int(token_index.shape[0]), int(token_index.shape[1])
+    if rows is None:
+        rows = torch.empty((batch, max_sel), dtype=torch.int32, device=token_index.device)
+    check(lib.b200kv_resolve_rows(_ptr(block_table), block_table.shape[1], block_size, _ptr(token_index), max_sel,
+                                  _ptr(n_selected), batch, pool_rows, _ptr(rows), _stream_handle(stream), _ptr(status)))
+    return rows
 
 
 def decode_workspace_bytes(batch: int, heads: int = HEADS, max_ctas: int = 0) -> int:

@@ -9,7 +9,11 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <iomanip>
+#include <locale>
 #include <new>
+#include <sstream>
+#include <string>
 
 #include "b200kv.h"
 
@@ -277,4 +281,25 @@ extern "C" int32_t b200kv_plan_reservation(int64_t max_context, int64_t block_si
 extern "C" double b200kv_utilisation(int64_t active_tokens, int64_t blocks_per_layer, int64_t block_size) {
   const int64_t capacity = blocks_per_layer * block_size;
   return capacity > 0 ? static_cast<double>(active_tokens) / static_cast<double>(capacity) : 0.0;
+}
+
+// The "paged_attention" object of the reference's diagnostics file, key for key and with its number
+// formatting (std::setprecision(12) in the classic locale; src/diagnostics/inference_stats.cpp:22, 42-47).
+extern "C" int64_t b200kv_paged_attention_stats_json(int64_t blocks_per_layer, int64_t layers, int64_t active_tokens,
+                                                     int64_t block_size, char* buffer, int64_t capacity) {
+  std::ostringstream out;
+  out.imbue(std::locale::classic());
+  out << std::setprecision(12);
+  out << "\"paged_attention\": {\n"
+      << "    \"total_blocks_allocated\": " << blocks_per_layer * layers << ",\n"
+      << "    \"active_context_tokens\": " << active_tokens << ",\n"
+      << "    \"block_size\": " << block_size << ",\n"
+      << "    \"kv_cache_utilization\": " << b200kv_utilisation(active_tokens, blocks_per_layer, block_size) << "\n  }";
+  const std::string text = out.str();
+  if (buffer != nullptr && capacity > 0) {
+    const size_t n = text.size() < static_cast<size_t>(capacity - 1) ? text.size() : static_cast<size_t>(capacity - 1);
+    std::memcpy(buffer, text.data(), n);
+    buffer[n] = '\0';
+  }
+  return static_cast<int64_t>(text.size());
 }

@@ -212,6 +212,34 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 4)
   }
 }
 
+// Physical pool row of every selected token: rows[b][j] = table[b][t / bs] * bs + t % bs for t = index[b][j],
+// j < n_selected[b]; the rest of a row of `rows` is filled with -1.
+__global__ void __launch_bounds__(256)
+    ResolveRowsKernel(const int32_t* __restrict__ block_table, int64_t max_blocks, int32_t block_size,
+                      const int32_t* __restrict__ token_index, int64_t max_selected, const int32_t* __restrict__ n_selected,
+                      int32_t batch, int64_t pool_rows, int32_t* __restrict__ rows, int32_t* status) {
+  GridDependencyTrigger();
+  GridDependencyWait();
+  const int64_t total = static_cast<int64_t>(batch) * max_selected;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t b = i / max_selected, j = i % max_selected;
+    int32_t row = -1;
+    if (j < n_selected[b]) {
+      const int64_t t = token_index[i];
+      const int64_t column = t / block_size;
+      const int64_t block = (t >= 0 && column < max_blocks) ? block_table[b * max_blocks + column] : -1;
+      const int64_t r = block * block_size + t % block_size;
+      if (t < 0 || block < 0 || r >= pool_rows) {
+        RecordError(status, B200KV_DEV_BAD_BLOCK, static_cast<int32_t>(b), static_cast<int32_t>(j), static_cast<int32_t>(t));
+      } else {
+        row = static_cast<int32_t>(r);
+      }
+    }
+    rows[i] = row;
+  }
+}
+
 int GridFor(int64_t rows) {
   const int64_t groups = (rows + kRowsPerWarp - 1) / kRowsPerWarp;
   const int64_t ctas = (groups + kWarpsPerCta - 1) / kWarpsPerCta;
@@ -300,4 +328,29 @@ extern "C" int32_t b200kv_gather(const b200kv_pool_view* pool, const int32_t* bl
           static_cast<char*>(out_latent), out_latent_stride * 2, static_cast<char*>(out_rope), out_rope_stride * 2,
           out_row_offsets, total_rows, B200KV_LATENT_DIM / 8, B200KV_ROPE_DIM / 8, status);
   return CheckCuda(cudaGetLastError(), "gather launch");
+}
+
+extern "C" int32_t b200kv_resolve_rows(const int32_t* block_table, int64_t max_blocks, int64_t block_size,
+                                       const int32_t* token_index, int64_t max_selected, const int32_t* n_selected,
+                                       int64_t batch, int64_t pool_rows, int32_t* rows, void* stream,
+                                       b200kv_status_word* status) {
+  if (batch == 0 || max_selected == 0) return B200KV_OK;
+  if (block_table == nullptr || token_index == nullptr || n_selected == nullptr || rows == nullptr) {
+    SetLastError("resolve_rows: block_table, token_index, n_selected and rows must be non-null");
+    return B200KV_ERR_NULLPTR;
+  }
+  if (batch < 0 || batch > INT32_MAX || max_selected < 0 || block_size <= 0 || block_size > INT32_MAX || max_blocks <= 0 ||
+      pool_rows <= 0 || pool_rows > INT32_MAX) {
+    SetLastError("resolve_rows refused: batch %lld, max_selected %lld, block_size %lld, max_blocks %lld, pool_rows %lld",
+                 static_cast<long long>(batch), static_cast<long long>(max_selected), static_cast<long long>(block_size),
+                 static_cast<long long>(max_blocks), static_cast<long long>(pool_rows));
+    return B200KV_ERR_INVALID;
+  }
+  const int64_t total = batch * max_selected;
+  const int64_t want = (total + 255) / 256;
+  const int grid = static_cast<int>(want > 1184 ? 1184 : want);
+  return CheckCuda(LaunchOverlapped(ResolveRowsKernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                    block_table, max_blocks, static_cast<int32_t>(block_size), token_index, max_selected,
+                                    n_selected, static_cast<int32_t>(batch), pool_rows, rows, status),
+                   "resolve_rows launch");
 }

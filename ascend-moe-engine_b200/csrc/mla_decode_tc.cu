@@ -52,9 +52,6 @@ constexpr int kThreads = 224;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemColS = 256;                     // S buffers at columns 256 and 256 + kTile
 constexpr float kRescaleThreshold = 8.0f;               // log2 units: rescale O only when max grows by > 2^8
-// A partial slot holds 64 heads x 512 fp32 and a pad: without it consecutive slots are 2^17 bytes apart and the
-// merge, which reads the same row of many slots, keeps hitting the same few L2 slices.
-constexpr int64_t kSlotFloats = static_cast<int64_t>(64) * B200KV_LATENT_DIM + 96;
 
 // Shared memory carve-up (offsets from a 1024-byte aligned base).
 constexpr int kOffQ = 0;
@@ -102,7 +99,11 @@ struct TcParams {
   float* user_o;  // caller's partial buffers (shard mode) or null
   float* user_m;
   float* user_l;
-  float* ws_o;  // [G*2] slots of kSlotFloats: [64][512] and a pad
+  // Partials, head-major: [64 heads][2G slots][512] and [64][2G]. The merge of one head reads that head's
+  // row of many slots: head-major puts them side by side (slot-major put them 2^17 bytes apart, which the L2
+  // serves badly, and made the (m, l) reads of a warp 32 separate lines).
+  float* ws_o;
+  int32_t n_slots;  // 2G
   float* ws_m;  // [G*2][64]
   float* ws_l;
   int32_t* status;
@@ -708,8 +709,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (row_ok) {
         misc->inv_l[head] = l_run > 0.0f ? 1.0f / l_run : 0.0f;
         if (to_ws) {
-          p.ws_m[slot * kHeads + head] = m_nat;
-          p.ws_l[slot * kHeads + head] = l_run;
+          p.ws_m[head * p.n_slots + slot] = m_nat;
+          p.ws_l[head * p.n_slots + slot] = l_run;
         } else if (to_user_partial) {
           p.user_m[static_cast<int64_t>(seq) * kHeads + head] = m_nat;
           p.user_l[static_cast<int64_t>(seq) * kHeads + head] = l_run;
@@ -727,9 +728,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::TmemLd32(tmem + lane_base + 64 * tm + 32 * half, o);
           ptx::TmemWaitLd();
           if (to_ws) {
-            float* dst = p.ws_o + static_cast<int64_t>(slot) * kSlotFloats + static_cast<int64_t>(32 * half) * kLatent + dv;
+            float* dst = p.ws_o + (static_cast<int64_t>(32 * half) * p.n_slots + slot) * kLatent + dv;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) dst[j * kLatent] = __uint_as_float(o[j]);
+            for (int j = 0; j < 32; ++j) dst[static_cast<int64_t>(j) * p.n_slots * kLatent] = __uint_as_float(o[j]);
           } else if (to_user_partial) {
             float* dst = p.user_o + (static_cast<int64_t>(seq) * kHeads + 32 * half) * kLatent + dv;
 #pragma unroll
@@ -824,6 +825,11 @@ __global__ void __launch_bounds__(256)
     return static_cast<int>(c * 2 + (c > c_prev ? 0 : 1));
   };
   int slot = slot_of(c_first + lane);
+  // 32-bit copies for the part loop below (CTA numbers and slots are small; the loop runs once per part and
+  // its instruction count, not memory, is what bounds this kernel when a sequence has a hundred parts).
+  const int cf = static_cast<int>(c_first), cl = static_cast<int>(c_last), cp = static_cast<int>(c_prev);
+  const int n_slots = p.n_slots;
+  const float* head_rows = p.ws_o + static_cast<int64_t>(h) * n_slots * kLatent;
   // All of the above came from the lengths, which were stable before the decode kernel ran; the partials
   // below are what that kernel wrote, so they wait for its completion.
   GridDependencyTrigger();
@@ -839,27 +845,32 @@ __global__ void __launch_bounds__(256)
   const int col1 = quarter * 32;
 
   if (mine > 0 && c_first == c_last) return;  // written directly by the decode kernel
-  for (long long c0 = c_first; c0 <= c_last; c0 += 32) {
+  for (int c0 = cf; c0 <= cl; c0 += 32) {
     // One wave of loads per chunk of 32 parts: lane k asks for the (m, l) of CTA c0 + k's part while the
     // rows of the chunk's first parts are requested as well; where a part lies follows from
     // arithmetic, so nothing here waits for an earlier load.
-    if (c0 != c_first) slot = slot_of(c0 + lane);
+    if (c0 != cf) slot = slot_of(c0 + lane);
     float m = -INFINITY, l = 0.0f;
     if (slot >= 0) {
-      l = p.ws_l[slot * kHeads + h];
-      m = p.ws_m[slot * kHeads + h];
+      l = p.ws_l[h * n_slots + slot];
+      m = p.ws_m[h * n_slots + slot];
     }
-    const long long left = c_last - c0 + 1;
-    const int n_here = left < 32 ? static_cast<int>(left) : 32;
+    const int left = cl - c0 + 1;
+    const int n_here = left < 32 ? left : 32;
     float w = 0.0f;
     for (int k0 = 0; k0 < n_here; k0 += kBatch) {
       float v[kBatch][kFloats];
       int slot_k[kBatch];
 #pragma unroll
       for (int k = 0; k < kBatch; ++k) {
-        slot_k[k] = __shfl_sync(0xffffffffu, slot, (k0 + k) & 31);
-        if (k0 + k >= n_here) slot_k[k] = -1;
-        const float* rowp = p.ws_o + static_cast<int64_t>(slot_k[k] < 0 ? 0 : slot_k[k]) * kSlotFloats + static_cast<int64_t>(h) * kLatent;
+        if (dense) {  // every CTA of the range holds a part: its slot is arithmetic, no shuffle
+          const int c = c0 + k0 + k;
+          slot_k[k] = k0 + k < n_here ? 2 * c + (c > cp ? 0 : 1) : -1;
+        } else {
+          slot_k[k] = __shfl_sync(0xffffffffu, slot, (k0 + k) & 31);
+          if (k0 + k >= n_here) slot_k[k] = -1;
+        }
+        const float* rowp = head_rows + (slot_k[k] < 0 ? 0 : slot_k[k]) * kLatent;
         if constexpr (kFloats == 1) {
           v[k][0] = slot_k[k] >= 0 ? rowp[col1 + lane] : 0.0f;
         } else {
@@ -895,10 +906,11 @@ __global__ void __launch_bounds__(256)
       }
 #pragma unroll
       for (int k = 0; k < kBatch; ++k) {
-        const float wk = __shfl_sync(0xffffffffu, w, (k0 + k) & 31);
-        if (slot_k[k] < 0 || wk == 0.0f) continue;  // an empty part's row may hold anything
+        // An empty part's row may hold anything (its weight is zero, but 0 x NaN is not): select, no branch.
+        const float from_lane = __shfl_sync(0xffffffffu, w, (k0 + k) & 31);
+        const float wk = slot_k[k] >= 0 ? from_lane : 0.0f;
 #pragma unroll
-        for (int i = 0; i < kFloats; ++i) acc[i] = fmaf(v[k][i], wk, acc[i]);
+        for (int i = 0; i < kFloats; ++i) acc[i] = fmaf(wk != 0.0f ? v[k][i] : 0.0f, wk, acc[i]);
       }
     }
   }
@@ -1063,7 +1075,7 @@ int32_t GetQMap(const void* base, int64_t head_stride, int64_t seq_stride, int32
 long long* g_trace = nullptr;  // set by the debug hook below; null in normal use
 
 size_t TcWorkspaceBytes(int32_t n_ctas) {
-  return static_cast<size_t>(n_ctas) * 2 * (kSlotFloats + 2 * kHeads) * sizeof(float);
+  return static_cast<size_t>(n_ctas) * 2 * kHeads * (kLatent + 2) * sizeof(float);
 }
 
 bool TcSupports(const b200kv_decode_args& a) {
@@ -1111,7 +1123,8 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   float* ws = static_cast<float*>(a.workspace);
   const size_t slots = static_cast<size_t>(n_ctas) * 2;
   p.ws_o = ws;
-  p.ws_m = ws + slots * kSlotFloats;
+  p.n_slots = static_cast<int32_t>(slots);
+  p.ws_m = ws + slots * kHeads * kLatent;
   p.ws_l = p.ws_m + slots * kHeads;
   p.status = status;
   p.trace = g_trace;

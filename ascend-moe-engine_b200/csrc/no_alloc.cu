@@ -20,10 +20,9 @@ using namespace b200kv;
 
 namespace {
 
-// Two partial slots per CTA of 64 heads x 512 fp32 plus a 96-float pad, and 64 (m, l) pairs each:
-// 263,936 bytes per CTA, 32 CTAs at most.
+// Two partial slots per CTA of 64 heads x (512 + 2) fp32: 263,168 bytes per CTA, 32 CTAs at most.
 constexpr int kStaticMaxCtas = B200KV_STATIC_MAX_CTAS;
-constexpr size_t kStaticScratchBytes = static_cast<size_t>(kStaticMaxCtas) * 2 * (64 * 512 + 96 + 2 * 64) * sizeof(float);
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(kStaticMaxCtas) * 2 * 64 * (512 + 2) * sizeof(float);
 
 // In host code this name is only a handle for the runtime's symbol lookup, never a device address.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];

@@ -134,11 +134,24 @@ size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t m
 int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* stream, b200kv_status_word* status);
 
 /*
+ * Attention over a selected subset of a sequence's tokens (what a top-k indexer in front of attention hands
+ * over; the reference vendors such an indexer but does not apply it, include/moe/pipeline/pipeline.hpp:57-66).
+ * b200kv_resolve_rows turns the selection into pool rows: rows[b][j] = block_table[b][t / bs] * bs + t % bs for
+ * t = token_index[b][j], j < n_selected[b] (the rest -1; a token outside the table or the pool is recorded
+ * as B200KV_DEV_BAD_BLOCK). b200kv_mla_decode then attends over exactly those rows when it is given
+ * block_table = rows, max_blocks = max_selected, kv_len = n_selected and block_size = 1 (a table of single-row
+ * blocks); that geometry runs on the CUDA-core kernel. All arrays device int32.
+ */
+int32_t b200kv_resolve_rows(const int32_t* block_table, int64_t max_blocks, int64_t block_size, const int32_t* token_index,
+                            int64_t max_selected, const int32_t* n_selected, int64_t batch, int64_t pool_rows,
+                            int32_t* rows, void* stream, b200kv_status_word* status);
+
+/*
  * Decode attention without a caller workspace and without any device allocation. No counterpart in
  * the reference. Same arguments and results as b200kv_mla_decode (args->workspace, workspace_bytes and
  * variant are ignored; the tensor-core kernel runs, so the geometry it needs applies: 64 heads,
  * block_size % 64 == 0, 16-byte aligned q). The partial-result scratch is a fixed array inside the
- * library's device image, b200kv_mla_decode_static_scratch_bytes() bytes (8,445,952) on every GPU that
+ * library's device image, b200kv_mla_decode_static_scratch_bytes() bytes (8,421,376) on every GPU that
  * loads the library, held until the process exits. It covers grids of up to B200KV_STATIC_MAX_CTAS
  * CTAs: args->max_ctas = 0 means that many; a larger max_ctas is refused with B200KV_ERR_INVALID.
  * The first call on a device looks up the array's address (cudaGetSymbolAddress): make that first
@@ -302,6 +315,12 @@ typedef struct b200kv_reservation {
 int32_t b200kv_plan_reservation(int64_t max_context, int64_t block_size, int64_t layers, int64_t max_seqs,
                                 int64_t tokens_per_step, b200kv_reservation* out);
 double b200kv_utilisation(int64_t active_tokens, int64_t blocks_per_layer, int64_t block_size);
+/* The "paged_attention" object of the reference's diagnostics JSON (include/moe/diagnostics/inference_stats.hpp:
+ * 21-28, written by src/diagnostics/inference_stats.cpp:42-47), key for key and with its number formatting:
+ * total_blocks_allocated = blocks_per_layer * layers, active_context_tokens, block_size, kv_cache_utilization.
+ * Writes at most capacity - 1 characters and a terminator; returns the length of the whole text. */
+int64_t b200kv_paged_attention_stats_json(int64_t blocks_per_layer, int64_t layers, int64_t active_tokens,
+                                          int64_t block_size, char* buffer, int64_t capacity);
 
 /* ------------------------------------------------------------------------------------------------
  * Static arena and the KV cache carved from it.

@@ -175,3 +175,45 @@ def test_decode_reports_bad_block_without_faulting():
         torch.cuda.synchronize()
         st = status.cpu().tolist()
         assert st[0] == b200kv.DEV_BAD_BLOCK and st[1] == 0 and st[2] == 1 and st[3] == 99
+
+
+def test_attention_over_a_selected_subset_of_tokens():
+    """A top-k style selection (512 of a few thousand tokens per sequence, in arbitrary order) resolved to pool
+    rows and attended over as a table of single-row blocks; the oracle gets the same rows as its table."""
+    import torch
+
+    from gpu_util import to_dev_i32
+
+    bs, sel = 64, 512
+    kv_len = np.array([3000, 640, 4096, 17], dtype=np.int32)
+    B = len(kv_len)
+    blocks = int(sum(scenarios.blocks_for(int(n), bs) for n in kv_len)) + 3
+    table = scenarios.build_tables(kv_len, bs, blocks, order=kvo.permutation(blocks))
+    pool = kvo.make_pool(blocks * bs)
+    q = kvo.make_q(B)
+    index = np.full((B, sel), -7, dtype=np.int32)
+    n_sel = np.minimum(kv_len, sel).astype(np.int32)
+    for b in range(B):
+        picks = kvo.permutation(int(kv_len[b]), seed=kvo.BASE_SEED + b)[: n_sel[b]]   # distinct, unordered
+        index[b, : n_sel[b]] = picks
+    d_table, d_index, d_n = to_dev_i32(table), to_dev_i32(index), to_dev_i32(n_sel)
+    st = b200kv.new_status()
+    rows = b200kv.resolve_rows(d_table, bs, d_index, d_n, blocks * bs, status=st)
+    torch.cuda.synchronize()
+    rows_np = rows.cpu().numpy()
+    expect = np.full((B, sel), -1, dtype=np.int32)
+    for b in range(B):
+        t = index[b, : n_sel[b]].astype(np.int64)
+        expect[b, : n_sel[b]] = table[b, t // bs].astype(np.int64) * bs + t % bs
+    assert np.array_equal(rows_np, expect) and st.cpu().tolist()[0] == 0
+    out, lse = run_decode(q, pool, rows_np, n_sel, 1, 1.0 / 24.0, b200kv.DECODE_AUTO)
+    ref_out, ref_lse = scenarios.ref_attention_f64(q, pool, rows_np, n_sel, 1, 1.0 / 24.0)
+    scenarios.check_attention(out, lse, ref_out, ref_lse, what="selected subset")
+    o_out, o_lse = kvo.mla_decode(q, pool, rows_np, n_sel, 1, 1.0 / 24.0)[:2]
+    scenarios.check_attention(o_out, o_lse, ref_out, ref_lse, what="oracle on the same rows")
+    # a token outside the sequence's table is recorded, not dereferenced
+    index[1, 0] = 64 * 4096
+    st2 = b200kv.new_status()
+    b200kv.resolve_rows(d_table, bs, to_dev_i32(index), d_n, blocks * bs, status=st2)
+    torch.cuda.synchronize()
+    assert st2.cpu().tolist()[0] == b200kv.DEV_BAD_BLOCK

@@ -131,3 +131,50 @@ def test_peer_merge_two_ranks(tmp_path):
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
 def test_peer_merge_four_ranks(tmp_path):
     _run_workers(4, tmp_path)
+
+
+def test_peer_merge_wait_runs_out_when_a_peer_never_arrives():
+    """A rank whose peer never pushes: the wait for the peer's words is bounded (about a second), the kernel
+    returns with B200KV_DEV_TIMEOUT in the status word, and the GPU context stays usable. The missing peer is
+    a second exchange buffer on the same GPU that nothing ever writes to; nothing faults or hangs."""
+    import ctypes
+    import time
+    from ctypes import c_void_p
+
+    from b200kv import dist as kvdist  # declares the argument types
+
+    lib = b200kv.lib
+    rows, world = 64, 2
+    nbytes = lib.b200kv_peer_exchange_bytes(world, rows)
+    assert nbytes > 2 * world * rows * 514 * 8
+    bufs, handle = [], (ctypes.c_ubyte * 64)()
+    for _ in range(world):
+        ptr = c_void_p()
+        b200kv.check(lib.b200kv_peer_buffer_alloc(nbytes, ctypes.byref(ptr), handle))
+        bufs.append(ptr)
+    table = (c_void_p * world)(bufs[0].value, bufs[1].value)
+    po = torch.randn((rows, 512), dtype=torch.float32, device="cuda")
+    pm = torch.zeros((rows,), dtype=torch.float32, device="cuda")
+    pl = torch.ones((rows,), dtype=torch.float32, device="cuda")
+    out = torch.full((rows, 512), 5.0, dtype=torch.bfloat16, device="cuda")
+    st = b200kv.new_status()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    b200kv.check(lib.b200kv_peer_merge(table, world, 0, rows, po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
+                                       None, None, st.data_ptr()))
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    status = st.cpu().tolist()
+    assert status[0] == b200kv.DEV_TIMEOUT and status[1] == 50 and status[2] == 1, status   # site 50, source rank 1
+    assert 0.5 < waited < 10.0, waited
+    assert bool((out == 5.0).all())                       # nothing was merged
+    # the context is alive and the same buffers work once the "peer" is the rank itself
+    single = (c_void_p * 1)(bufs[1].value)
+    st2 = b200kv.new_status()
+    b200kv.check(lib.b200kv_peer_merge(single, 1, 0, rows, po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
+                                       None, None, st2.data_ptr()))
+    torch.cuda.synchronize()
+    assert st2.cpu().tolist()[0] == 0
+    assert torch.allclose(out.float(), po, atol=0.02, rtol=0.01)
+    for ptr in bufs:
+        b200kv.check(lib.b200kv_peer_buffer_free(ptr))

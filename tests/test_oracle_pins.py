@@ -78,3 +78,31 @@ def test_bf16_round_to_nearest_even():
     assert [int(b) for b in bits[:5]] == [0x3F80, 0x3F80, 0x3F81, 0x3F80, 0xC020]
     assert int(bits[5]) == 0x7F7F and int(bits[6]) == 0
     assert np.isnan(kvo.bf16_to_f32(kvo.f32_to_bf16(np.array([np.nan], dtype=np.float32)))).all()
+
+
+def test_paged_attention_stats_json_has_the_reference_shape():
+    """The diagnostics object the reference writes (src/diagnostics/inference_stats.cpp:42-47): same keys, same
+    number formatting, and the two structural known answers of its tests and examples (2,752 blocks at context
+    8192 / block 128, docs/examples/inference_diagnostics_dry_run.json:20-24; utilisation (128 + 1) / 8192 after
+    a 128-token prompt and one decoded token, tests/mock_pipeline_e2e.cpp:663-666)."""
+    import ctypes
+    import json
+
+    import b200kv
+
+    fn = b200kv.lib.b200kv_paged_attention_stats_json
+    fn.restype = ctypes.c_int64
+    fn.argtypes = [ctypes.c_int64] * 4 + [ctypes.c_char_p, ctypes.c_int64]
+    buf = ctypes.create_string_buffer(512)
+    n = fn(64, 43, 0, 128, buf, 512)
+    text = buf.value.decode()
+    assert n == len(text)
+    assert text == ('"paged_attention": {\n    "total_blocks_allocated": 2752,\n    "active_context_tokens": 0,\n'
+                    '    "block_size": 128,\n    "kv_cache_utilization": 0\n  }')
+    fn(64, 43, 129, 128, buf, 512)
+    obj = json.loads("{" + buf.value.decode() + "}")["paged_attention"]
+    assert obj == {"total_blocks_allocated": 2752, "active_context_tokens": 129, "block_size": 128,
+                   "kv_cache_utilization": 0.0157470703125}
+    assert fn(64, 43, 129, 128, None, 0) == len(buf.value)   # sizing call
+    small = ctypes.create_string_buffer(16)
+    assert fn(64, 43, 129, 128, small, 16) == len(buf.value) and len(small.value) == 15

@@ -63,4 +63,4 @@ def test_static_scratch_entry_refuses_grids_beyond_its_array():
         b200kv.mla_decode_static(q, b200kv.pool_view(pool), to_dev_i32(table), to_dev_i32(kv_len), bs, 1.0 / 24.0,
                                  out=out, max_ctas=33)
     assert err.value.code == b200kv.ERR_INVALID and "at most 32" in str(err.value)
-    assert b200kv.lib.b200kv_mla_decode_static_scratch_bytes() == 32 * 2 * (64 * 512 + 96 + 2 * 64) * 4
+    assert b200kv.lib.b200kv_mla_decode_static_scratch_bytes() == 32 * 2 * 64 * 514 * 4
