@@ -156,8 +156,13 @@ __device__ __noinline__ bool BoundedWait(uint32_t bar, uint32_t parity, Misc* mi
 struct CostCut {
   long long cost_total;  // C, at least 2 when there is any tile
   long long n_ctas;      // G
-  __device__ long long CtaOf(long long x, long long s) const { return (2 * x + 3 * s) * n_ctas / cost_total; }
-  __device__ long long FirstPos(long long c) const { return (c * cost_total + n_ctas - 1) / n_ctas; }
+  // Non-negative quotient; the 32-bit division is several times shorter and covers every realistic size.
+  __device__ static long long Div(long long a, long long b) {
+    if (((a | b) >> 32) == 0) return static_cast<long long>(static_cast<uint32_t>(a) / static_cast<uint32_t>(b));
+    return a / b;
+  }
+  __device__ long long CtaOf(long long x, long long s) const { return Div((2 * x + 3 * s) * n_ctas, cost_total); }
+  __device__ long long FirstPos(long long c) const { return Div(c * cost_total + n_ctas - 1, n_ctas); }
   // First tile of a sequence (first tile `first`, ordinal s) at or after cost position k.
   __device__ long long FirstTileAt(long long k, long long first, long long s) const {
     const long long x = (k - 3 * s + 1) >> 1;  // ceil((k - 3s) / 2), also right for negative values
@@ -782,35 +787,54 @@ __global__ void __launch_bounds__(256)
   const int64_t warp_id = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t row = warp_id / kColSplit;
   const int quarter = static_cast<int>(warp_id % kColSplit);
-  if (row >= static_cast<int64_t>(p.batch) * kHeads) return;
-  const int b = static_cast<int>(row / kHeads);
+  const bool in_range = row < static_cast<int64_t>(p.batch) * kHeads;  // the last CTA may have spare warps
+  const int b = in_range ? static_cast<int>(row / kHeads) : p.batch - 1;
   const int h = static_cast<int>(row % kHeads);
-  long long before = 0, total = 0, before_s = 0, nonempty = 0;
-  for (int i = lane; i < p.batch; i += 32) {
-    const long long t = TilesOf(p.kv_len[i]);
-    total += t;
-    nonempty += t > 0 ? 1 : 0;
-    if (i < b) {
-      before += t;
-      before_s += t > 0 ? 1 : 0;
+  // Where the sequence's parts lie follows from the lengths alone (the decode kernel's cut of the tile list,
+  // CostCut). All warps of a CTA work on the same sequence (a CTA covers at most eight consecutive rows and a
+  // sequence has 64), so the first warp works it out once for all of them: this arithmetic, not memory, is
+  // what the kernel spends its time on otherwise.
+  __shared__ long long shared_meta[8];
+  if (threadIdx.x < 32) {
+    long long before = 0, total = 0, before_s = 0, nonempty = 0;
+    for (int i = lane; i < p.batch; i += 32) {
+      const long long t = TilesOf(p.kv_len[i]);
+      total += t;
+      nonempty += t > 0 ? 1 : 0;
+      if (i < b) {
+        before += t;
+        before_s += t > 0 ? 1 : 0;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      total += __shfl_xor_sync(0xffffffffu, total, off);
+      nonempty += __shfl_xor_sync(0xffffffffu, nonempty, off);
+      before += __shfl_xor_sync(0xffffffffu, before, off);
+      before_s += __shfl_xor_sync(0xffffffffu, before_s, off);
+    }
+    if (lane == 0) {
+      const long long tiles = TilesOf(p.kv_len[b]);
+      const CostCut c{2 * total + 3 * (nonempty > 0 ? nonempty - 1 : 0), n_ctas};
+      shared_meta[0] = total;
+      shared_meta[1] = nonempty;
+      shared_meta[2] = before;
+      shared_meta[3] = before_s;
+      shared_meta[4] = tiles;
+      // c_prev is the CTA that took the tile before this sequence: if it is c_first, this sequence is not that
+      // CTA's first segment and its part sits in the CTA's second slot.
+      shared_meta[5] = tiles > 0 ? c.CtaOf(before, before_s) : 0;
+      shared_meta[6] = tiles > 0 ? c.CtaOf(before + tiles - 1, before_s) : -1;
+      shared_meta[7] = before > 0 && tiles > 0 ? c.CtaOf(before - 1, before_s - 1) : -1;
     }
   }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    total += __shfl_xor_sync(0xffffffffu, total, off);
-    nonempty += __shfl_xor_sync(0xffffffffu, nonempty, off);
-    before += __shfl_xor_sync(0xffffffffu, before, off);
-    before_s += __shfl_xor_sync(0xffffffffu, before_s, off);
-  }
-  const long long mine = TilesOf(p.kv_len[b]);
+  __syncthreads();
+  if (!in_range) return;
+  const long long total = shared_meta[0], nonempty = shared_meta[1], before = shared_meta[2], before_s = shared_meta[3];
+  const long long mine = shared_meta[4];
+  const long long c_first = shared_meta[5], c_last = shared_meta[6], c_prev = shared_meta[7];
   const bool want_partial = p.user_o != nullptr;
-  // The decode kernel's cut of the tile list (CostCut): this sequence has ordinal before_s and owns tiles
-  // [before, before + mine). c_prev is the CTA that took the tile before this sequence: if it is c_first,
-  // this sequence is not that CTA's first segment and its part sits in the CTA's second slot.
   const CostCut cut{2 * total + 3 * (nonempty > 0 ? nonempty - 1 : 0), n_ctas};
-  const long long c_first = mine > 0 ? cut.CtaOf(before, before_s) : 0;
-  const long long c_last = mine > 0 ? cut.CtaOf(before + mine - 1, before_s) : -1;
-  const long long c_prev = before > 0 && mine > 0 ? cut.CtaOf(before - 1, before_s - 1) : -1;
   // Slot of CTA c's part of this sequence, or -1: the CTA holds a part if its first tile inside the
   // sequence lies before the next CTA's run.
   // When every CTA's share of the cost is at least 5 units it holds at least one tile (consecutive tiles
