@@ -316,16 +316,21 @@ __global__ void __launch_bounds__(kThreads, 1)
     GridDependencyWait();
     // This CTA's run of the flat tile list (see CostCut): totals first, then the tile at which the run
     // starts and the tile at which the next CTA's run starts.
+    // Per-lane and per-chunk quantities are 32-bit (a sequence has at most 2^25 tiles, a chunk of 32 at most
+    // 2^30); only the running totals are 64-bit. This warp's instruction count is on every launch's critical
+    // path, so the scans are kept short.
     long long total = 0, nonempty = 0;
-    for (int b = lane; b < p.batch; b += 32) {
-      const int t = TilesOf(p.kv_len[b]);
-      total += t;
-      nonempty += t > 0 ? 1 : 0;
-    }
+    const int first_tiles = lane < p.batch ? TilesOf(p.kv_len[lane]) : 0;  // the first chunk's lengths, kept
+    for (int b0 = 0; b0 < p.batch; b0 += 32) {
+      int t = b0 == 0 ? first_tiles : (b0 + lane < p.batch ? TilesOf(p.kv_len[b0 + lane]) : 0);
+      int ne = t > 0 ? 1 : 0;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      total += __shfl_xor_sync(0xffffffffu, total, off);
-      nonempty += __shfl_xor_sync(0xffffffffu, nonempty, off);
+      for (int off = 16; off > 0; off >>= 1) {
+        t += __shfl_xor_sync(0xffffffffu, t, off);
+        ne += __shfl_xor_sync(0xffffffffu, ne, off);
+      }
+      total += t;
+      nonempty += ne;
     }
     const CostCut cut{2 * total + 3 * (nonempty > 0 ? nonempty - 1 : 0), n_ctas};
     // One pass over the sequences finds both the first tile at or after this CTA's first cost position
@@ -339,13 +344,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool have_lo = false, have_hi = false;
       long long before = 0, before_s = 0;
       for (int b0 = 0; b0 < p.batch && !have_hi; b0 += 32) {
-        const int b = b0 + lane;
-        const long long mine = b < p.batch ? TilesOf(p.kv_len[b]) : 0;
-        long long incl = mine, incl_s = mine > 0 ? 1 : 0;
+        const int mine = b0 == 0 ? first_tiles : (b0 + lane < p.batch ? TilesOf(p.kv_len[b0 + lane]) : 0);
+        int incl = mine, incl_s = mine > 0 ? 1 : 0;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
-          const long long up = __shfl_up_sync(0xffffffffu, incl, off);
-          const long long up_s = __shfl_up_sync(0xffffffffu, incl_s, off);
+          const int up = __shfl_up_sync(0xffffffffu, incl, off);
+          const int up_s = __shfl_up_sync(0xffffffffu, incl_s, off);
           if (lane >= off) {
             incl += up;
             incl_s += up_s;
@@ -359,14 +363,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int src = __ffs(hit_lo) - 1;
           start_first = before + __shfl_sync(0xffffffffu, incl - mine, src);
           start_seq = b0 + src;
-          start_seq_tiles = static_cast<int>(__shfl_sync(0xffffffffu, mine, src));
-          lo = cut.FirstTileAt(k_lo, start_first, __shfl_sync(0xffffffffu, s, src));
+          start_seq_tiles = __shfl_sync(0xffffffffu, mine, src);
+          lo = cut.FirstTileAt(k_lo, start_first, before_s + __shfl_sync(0xffffffffu, incl_s, src) - 1);
           have_lo = true;
         }
         if (hit_hi != 0) {
           const int src = __ffs(hit_hi) - 1;
           const long long first = before + __shfl_sync(0xffffffffu, incl - mine, src);
-          hi = cut.FirstTileAt(k_hi, first, __shfl_sync(0xffffffffu, s, src));
+          hi = cut.FirstTileAt(k_hi, first, before_s + __shfl_sync(0xffffffffu, incl_s, src) - 1);
           have_hi = true;
         }
         before += __shfl_sync(0xffffffffu, incl, 31);

@@ -705,7 +705,7 @@ def run_extra_workload(args):
                 else:
                     b200kv.lse_merge(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS), out, lse)
         tokens_per_step = 1
-        bytes_per_step = float(n) * ROW * 2 * layers
+        bytes_per_step = float(length) * ROW * 2 * layers  # this rank's shard: the roofline is per GPU
         how = ("partials pushed into every rank's inbox over peer memory (NVLink), merged by a kernel that waits for "
                "the peers' flags" if exchange is not None else "all-gather of 131,584-byte partials (NCCL) + LSE merge")
         desc = (f"configs[3]: one sequence of {n} tokens split by KV range over {world} rank(s) "
