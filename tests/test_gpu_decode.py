@@ -217,3 +217,29 @@ def test_attention_over_a_selected_subset_of_tokens():
     b200kv.resolve_rows(d_table, bs, to_dev_i32(index), d_n, blocks * bs, status=st2)
     torch.cuda.synchronize()
     assert st2.cpu().tolist()[0] == b200kv.DEV_BAD_BLOCK
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_batches_and_grid_sizes_match_the_reference(seed):
+    """Many small random batches (lengths around the tile and block edges, empty sequences, one long sequence)
+    on grids of 1 to 148 CTAs: the cut of the tile list, the slots of the partials and the merge must agree
+    for every combination (grids larger than the number of tiles leave CTAs without work)."""
+    rng = np.random.default_rng(1000 + seed)
+    bs = 64
+    for case in range(10):
+        B = int(rng.integers(1, 24))
+        choices = np.array([0, 1, 63, 64, 65, 127, 128, 129, 500, 1000, 2100])
+        kv_len = rng.choice(choices, size=B).astype(np.int32)
+        if case % 3 == 0:
+            kv_len[int(rng.integers(0, B))] = int(rng.integers(3000, 9000))
+        if not kv_len.any():
+            kv_len[0] = 65
+        blocks = int(sum(scenarios.blocks_for(int(n), bs) for n in kv_len)) + 2
+        table = scenarios.build_tables(kv_len, bs, blocks, order=rng.permutation(blocks).astype(np.int32))
+        pool = kvo.make_pool(blocks * bs, seed=kvo.BASE_SEED + 31 * seed + case)
+        q = kvo.make_q(B, seed=kvo.BASE_SEED + 7 * seed + case)
+        ref_out, ref_lse = scenarios.ref_attention_f64(q, pool, table, kv_len, bs, 1.0 / 24.0)
+        for max_ctas in (int(rng.choice([1, 2, 3, 5, 7])), int(rng.choice([16, 31, 32, 64])), 0):
+            out, lse = run_decode(q, pool, table, kv_len, bs, 1.0 / 24.0, b200kv.DECODE_TCGEN05, max_ctas=max_ctas)
+            scenarios.check_attention(out, lse, ref_out, ref_lse,
+                                      what=f"seed {seed} case {case} lens {kv_len.tolist()} ctas {max_ctas}")
