@@ -88,6 +88,18 @@ class ProducerArgs(Structure):
     ]
 
 
+class IndexerArgs(Structure):
+    """b200kv_indexer_args (include/b200kv.h)."""
+
+    _fields_ = [
+        ("q", c_void_p), ("q_scale", c_void_p), ("weights", c_void_p), ("heads", c_int32),
+        ("key_pool", c_void_p), ("key_stride", c_int64), ("k_scale", c_void_p), ("pool_rows", c_int64),
+        ("block_table", c_void_p), ("max_blocks", c_int64), ("kv_len", c_void_p), ("batch", c_int32),
+        ("block_size", c_int32), ("max_kv_len", c_int64), ("k", c_int32),
+        ("index_out", c_void_p), ("n_selected_out", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+    ]
+
+
 class Reservation(Structure):
     _fields_ = [
         ("blocks_per_layer", c_int64),
@@ -123,6 +135,10 @@ def _load() -> ctypes.CDLL:
     lib.b200kv_mx_quant_e4m3.restype = c_int32
     lib.b200kv_mx_quant_e4m3.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                          c_void_p]
+    lib.b200kv_indexer_workspace_bytes.restype = c_size_t
+    lib.b200kv_indexer_workspace_bytes.argtypes = [c_int32, c_int64]
+    lib.b200kv_indexer_topk.restype = c_int32
+    lib.b200kv_indexer_topk.argtypes = [POINTER(IndexerArgs), c_void_p, c_void_p]
     lib.b200kv_resolve_rows.restype = c_int32
     lib.b200kv_resolve_rows.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                         c_void_p, c_void_p, c_void_p]
@@ -259,6 +275,26 @@ def gather(view: PoolView, block_table, kv_len, block_size: int, out_latent, out
                             out_latent.stride(0) if total_rows else LATENT_DIM, _ptr(out_rope),
                             out_rope.stride(0) if total_rows else ROPE_DIM, _ptr(out_row_offsets), total_rows,
                             _stream_handle(stream), _ptr(status)))
+
+
+def indexer_topk(q_fp8, q_scale, weights, key_pool, k_scale, block_table, kv_len, block_size: int, max_kv_len: int,
+                 k: int, status=None, stream=None):
+    """The k best-scoring tokens of every sequence: q_fp8 uint8 [B, H, 128], q_scale fp32 [B, H], weights bf16
+    [B, H], key_pool uint8 [rows, >=128], k_scale fp32 [rows] -> (index int32 [B, k], n_selected int32 [B])."""
+    import torch
+
+    batch, heads = int(q_fp8.shape[0]), int(q_fp8.shape[1])
+    index = torch.empty((batch, k), dtype=torch.int32, device=q_fp8.device)
+    n_sel = torch.empty((batch,), dtype=torch.int32, device=q_fp8.device)
+    ws = torch.empty(lib.b200kv_indexer_workspace_bytes(batch, max_kv_len), dtype=torch.uint8, device=q_fp8.device)
+    a = IndexerArgs()
+    a.q, a.q_scale, a.weights, a.heads = _ptr(q_fp8), _ptr(q_scale), _ptr(weights), heads
+    a.key_pool, a.key_stride, a.k_scale, a.pool_rows = _ptr(key_pool), key_pool.stride(0), _ptr(k_scale), key_pool.shape[0]
+    a.block_table, a.max_blocks, a.kv_len = _ptr(block_table), block_table.shape[1], _ptr(kv_len)
+    a.batch, a.block_size, a.max_kv_len, a.k = batch, block_size, max_kv_len, k
+    a.index_out, a.n_selected_out, a.workspace, a.workspace_bytes = _ptr(index), _ptr(n_sel), _ptr(ws), ws.numel()
+    check(lib.b200kv_indexer_topk(ctypes.byref(a), _stream_handle(stream), _ptr(status)))
+    return index, n_sel
 
 
 def resolve_rows(block_table, block_size: int, token_index, n_selected, pool_rows: int, rows=None, status=None,

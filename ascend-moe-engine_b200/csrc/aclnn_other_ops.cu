@@ -77,7 +77,6 @@ constexpr char kNameGroupedMatmulFinalizeRoutingV3[] = "aclnnGroupedMatmulFinali
 constexpr char kNameMhcPre[] = "aclnnMhcPre";
 constexpr char kNameMhcSinkhorn[] = "aclnnMhcSinkhorn";
 constexpr char kNameMhcPost[] = "aclnnMhcPost";
-constexpr char kNameQuantLightningIndexer[] = "aclnnQuantLightningIndexer";
 
 }  // namespace
 
@@ -247,6 +246,101 @@ extern "C" aclnnStatus aclnnDynamicMxQuant(void* workspace, uint64_t workspace_s
   const int32_t rc = b200kv_mx_quant_e4m3(x->Address(), cols, rows, cols, executor->stage_tensor[1]->Address(), cols,
                                           executor->stage_tensor[2]->Address(), cols / 32, stream);
   return Finish(executor, rc);
+}
+
+// aclnnQuantLightningIndexer for the decode step: one query token per sequence (TND query [T, N1, 128], T =
+// sequences), paged FP8 keys [blocks, block_size, 1, 128] with their block table and lengths, out [T, 1, k].
+// The positions come out best first, -1 beyond min(k, length). Other layouts plan as stand-ins.
+namespace {
+constexpr char kNameQuantLightningIndexer[] = "aclnnQuantLightningIndexer";
+}
+
+extern "C" aclnnStatus aclnnQuantLightningIndexerGetWorkspaceSize(
+    const aclTensor* query, const aclTensor* key, const aclTensor* weights, const aclTensor* query_dequant_scale,
+    const aclTensor* key_dequant_scale, const aclTensor* actual_seq_lengths_query_optional,
+    const aclTensor* actual_seq_lengths_key_optional, const aclTensor* block_table_optional, int64_t query_quant_mode,
+    int64_t key_quant_mode, char* layout_query_optional, char* layout_key_optional, int64_t sparse_count,
+    int64_t sparse_mode, int64_t pre_tokens, int64_t next_tokens, const aclTensor* out, uint64_t* workspace_size,
+    aclOpExecutor** executor) {
+  (void)actual_seq_lengths_query_optional;
+  (void)sparse_mode;
+  (void)pre_tokens;
+  (void)next_tokens;
+  (void)layout_query_optional;
+  const void* required[] = {query, key, weights, query_dequant_scale, key_dequant_scale, out};
+  const bool ours =
+      query != nullptr && key != nullptr && weights != nullptr && query_dequant_scale != nullptr &&
+      key_dequant_scale != nullptr && out != nullptr && workspace_size != nullptr && executor != nullptr &&
+      actual_seq_lengths_key_optional != nullptr && block_table_optional != nullptr && layout_key_optional != nullptr &&
+      std::strcmp(layout_key_optional, "PA_BSND") == 0 && query_quant_mode == 0 && key_quant_mode == 0 &&
+      query->dtype == ACL_FLOAT8_E4M3FN && key->dtype == ACL_FLOAT8_E4M3FN && query->dims.size() == 3 &&
+      query->dims[2] == 128 && query->dims[1] >= 1 && query->dims[1] <= 64 && key->dims.size() == 4 && key->dims[2] == 1 &&
+      key->dims[3] == 128 && Contiguous(query) && Contiguous(key) && weights->dtype == ACL_BF16 &&
+      weights->Elements() == query->dims[0] * query->dims[1] && Contiguous(weights) &&
+      query_dequant_scale->dtype == ACL_FLOAT32 && query_dequant_scale->Elements() == weights->Elements() &&
+      Contiguous(query_dequant_scale) && key_dequant_scale->dtype == ACL_FLOAT32 &&
+      key_dequant_scale->Elements() == key->dims[0] * key->dims[1] && Contiguous(key_dequant_scale) &&
+      actual_seq_lengths_key_optional->dtype == ACL_INT32 && actual_seq_lengths_key_optional->Elements() == query->dims[0] &&
+      block_table_optional->dtype == ACL_INT32 && block_table_optional->dims.size() == 2 &&
+      block_table_optional->dims[0] == query->dims[0] && Contiguous(block_table_optional) && out->dtype == ACL_INT32 &&
+      out->Elements() == query->dims[0] * sparse_count && Contiguous(out) && sparse_count >= 1 && sparse_count <= 2048;
+  if (!ours) return PlanOnly(kNameQuantLightningIndexer, required, 6, workspace_size, executor);
+  aclOpExecutor* exec = nullptr;
+  if (aclnnStatus rc = NewStageExecutor(aclOpExecutor::kIndexer, kNameQuantLightningIndexer, workspace_size, executor, &exec)) {
+    return rc;
+  }
+  exec->stage_tensor[0] = query;
+  exec->stage_tensor[1] = key;
+  exec->stage_tensor[2] = weights;
+  exec->stage_tensor[3] = query_dequant_scale;
+  exec->stage_tensor[4] = key_dequant_scale;
+  exec->stage_tensor[5] = actual_seq_lengths_key_optional;
+  exec->stage_tensor[6] = block_table_optional;
+  exec->stage_tensor[7] = out;
+  exec->stage_scalar = static_cast<double>(sparse_count);
+  // scores for the longest sequence the table can address, then one count per sequence
+  const int64_t batch = query->dims[0];
+  const int64_t max_len = block_table_optional->dims[1] * key->dims[1];
+  *workspace_size = b200kv_indexer_workspace_bytes(static_cast<int32_t>(batch), max_len) + ((batch * 4 + 255) & ~255ll);
+  return 0;
+}
+
+extern "C" aclnnStatus aclnnQuantLightningIndexer(void* workspace, uint64_t workspace_size, aclOpExecutor* executor,
+                                                  aclrtStream stream) {
+  bool plan_only = false;
+  if (aclnnStatus rc = CheckStageLaunch(kNameQuantLightningIndexer, aclOpExecutor::kIndexer, executor, &plan_only)) return rc;
+  if (plan_only) return LaunchNothing(kNameQuantLightningIndexer, workspace, workspace_size, executor, stream);
+  const aclTensor* query = executor->stage_tensor[0];
+  const aclTensor* key = executor->stage_tensor[1];
+  const aclTensor* table = executor->stage_tensor[6];
+  const int64_t batch = query->dims[0];
+  const int64_t max_len = table->dims[1] * key->dims[1];
+  const size_t score_bytes = b200kv_indexer_workspace_bytes(static_cast<int32_t>(batch), max_len);
+  if (workspace == nullptr || workspace_size < score_bytes + static_cast<size_t>(batch) * 4) {
+    SetLastError("%s: workspace of %zu bytes required", kNameQuantLightningIndexer, score_bytes + static_cast<size_t>(batch) * 4);
+    return workspace == nullptr ? kErrNull : kErrInvalid;
+  }
+  b200kv_indexer_args a{};
+  a.q = query->Address();
+  a.q_scale = static_cast<const float*>(executor->stage_tensor[3]->Address());
+  a.weights = executor->stage_tensor[2]->Address();
+  a.heads = static_cast<int32_t>(query->dims[1]);
+  a.key_pool = key->Address();
+  a.key_stride = 128;
+  a.k_scale = static_cast<const float*>(executor->stage_tensor[4]->Address());
+  a.pool_rows = key->dims[0] * key->dims[1];
+  a.block_table = static_cast<const int32_t*>(table->Address());
+  a.max_blocks = table->dims[1];
+  a.kv_len = static_cast<const int32_t*>(executor->stage_tensor[5]->Address());
+  a.batch = static_cast<int32_t>(batch);
+  a.block_size = static_cast<int32_t>(key->dims[1]);
+  a.max_kv_len = max_len;
+  a.k = static_cast<int32_t>(executor->stage_scalar);
+  a.index_out = static_cast<int32_t*>(executor->stage_tensor[7]->Address());
+  a.n_selected_out = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + score_bytes);
+  a.workspace = workspace;
+  a.workspace_bytes = score_bytes;
+  return Finish(executor, b200kv_indexer_topk(&a, stream, nullptr));
 }
 
 // ---- every other operator: plan checks, launch enqueues nothing ------------------------------------------------
@@ -477,16 +571,3 @@ extern "C" aclnnStatus aclnnMhcPost(void* workspace, uint64_t workspace_size, ac
   return LaunchNothing(kNameMhcPost, workspace, workspace_size, executor, stream);
 }
 
-extern "C" aclnnStatus aclnnQuantLightningIndexerGetWorkspaceSize(const aclTensor* query, const aclTensor* key,
-    const aclTensor* weights, const aclTensor* query_dequant_scale, const aclTensor* key_dequant_scale,
-    const aclTensor* actual_seq_lengths_query_optional, const aclTensor* actual_seq_lengths_key_optional,
-    const aclTensor* block_table_optional, int64_t query_quant_mode, int64_t key_quant_mode,
-    char* layout_query_optional, char* layout_key_optional, int64_t sparse_count, int64_t sparse_mode,
-    int64_t pre_tokens, int64_t next_tokens, const aclTensor* out, uint64_t* workspace_size,
-    aclOpExecutor** executor) {
-  const void* required[] = {query, key, weights, query_dequant_scale, key_dequant_scale, out};
-  return PlanOnly(kNameQuantLightningIndexer, required, sizeof(required) / sizeof(required[0]), workspace_size, executor);
-}
-extern "C" aclnnStatus aclnnQuantLightningIndexer(void* workspace, uint64_t workspace_size, aclOpExecutor* executor, aclrtStream stream) {
-  return LaunchNothing(kNameQuantLightningIndexer, workspace, workspace_size, executor, stream);
-}

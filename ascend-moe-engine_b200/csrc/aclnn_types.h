@@ -47,10 +47,10 @@ struct aclScalar {
   aclDataType dtype = ACL_DT_UNDEFINED;
 };
 struct aclOpExecutor {
-  // kScatter and kAttention are the KV path; kRmsNorm, kRope and kMxQuant the stages beside it, which work
+  // kScatter and kAttention are the KV path; kRmsNorm, kRope, kMxQuant and kIndexer the stages beside it, which work
   // for the shapes the path produces and consumes; kPlanOnly belongs to any other operator, whose launch
   // checks the pairing and enqueues nothing.
-  enum Kind { kScatter, kAttention, kRmsNorm, kRope, kMxQuant, kPlanOnly } kind = kScatter;
+  enum Kind { kScatter, kAttention, kRmsNorm, kRope, kMxQuant, kIndexer, kPlanOnly } kind = kScatter;
   const char* op = nullptr;  // operator name the executor was planned for (kPlanOnly)
   bool repeatable = false;
   // scatter
@@ -73,6 +73,6 @@ struct aclOpExecutor {
   bool q_is_fused = false;  // query_rope directly follows query inside one 576-wide row
   uint64_t decode_ws = 0, q_pack_bytes = 0;
   // the stages beside the path (kRmsNorm, kRope, kMxQuant): their tensors in argument order, one scalar
-  const aclTensor* stage_tensor[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  const aclTensor* stage_tensor[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   double stage_scalar = 0.0;
 };

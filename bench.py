@@ -393,7 +393,24 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
         res[name] = {"rows_per_launch": n_rows, "algorithmic_bytes": nbytes, "us_per_launch": t * 1e6,
                      "achieved_gbs": nbytes / t * 1e-9, "frac_of_measured_hbm": nbytes / t * 1e-9 / hbm_peak}
         del xq, q8, sc
-    del src, out_l, out_r, trig, fused_src
+    # The sparse-selection indexer on the step's shape: 32 sequences x 4,096 tokens of FP8 index keys (128 wide),
+    # 64 index heads, top 512. First version on CUDA cores: its bound is the fp32 arithmetic
+    # (32 x 4,096 x 64 x 128 fused multiply-adds), reported as time, with the key bytes it reads for scale.
+    n_rows = wl.blocks * BLOCK
+    key8 = torch.randint(0, 0x50, (2, n_rows, 128), dtype=torch.uint8, device="cuda")
+    q8 = torch.randint(0, 0x50, (BATCH, HEADS, 128), dtype=torch.uint8, device="cuda")
+    k_scale = torch.rand((2, n_rows), dtype=torch.float32, device="cuda") * 0.1 + 0.01
+    q_scale = torch.rand((BATCH, HEADS), dtype=torch.float32, device="cuda") * 0.1 + 0.01
+    w_idx = torch.randn((BATCH, HEADS), dtype=torch.float32, device="cuda").to(torch.bfloat16)
+    # (the binding allocates its outputs and workspace per call: inside a captured graph those come from
+    # the graph's private pool, so the replay measures the two kernels)
+    t = timeit(lambda i: b200kv.indexer_topk(q8, q_scale, w_idx, key8[i % 2], k_scale[i % 2], wl.table, wl.kv_len,
+                                             BLOCK, CONTEXT, 512, status=wl.status), 20)
+    res["indexer_topk"] = {"sequences": BATCH, "tokens_per_sequence": CONTEXT, "index_heads": HEADS, "k": 512,
+                           "us_per_launch": t * 1e6, "key_bytes": n_rows * 132,
+                           "gflop": 2.0 * BATCH * CONTEXT * HEADS * 128 * 1e-9,
+                           "tflops_fp32": 2.0 * BATCH * CONTEXT * HEADS * 128 / t * 1e-12}
+    del src, out_l, out_r, trig, fused_src, key8, k_scale
     return res
 
 

@@ -147,6 +147,45 @@ int32_t b200kv_resolve_rows(const int32_t* block_table, int64_t max_blocks, int6
                             int32_t* rows, void* stream, b200kv_status_word* status);
 
 /*
+ * The selection itself: the sparse indexer the reference vendors in front of attention
+ * (aclnnQuantLightningIndexer; contract mock/mock_ops.cpp:1118-1221, formula
+ * third_party/ops_transformer/attention/quant_lightning_indexer/README.md). For sequence b and its one query
+ * token of the step, every token t < kv_len[b] of the paged index-key cache scores
+ *   score_t = sum_h w[b][h] * ReLU(q_scale[b][h] * k_scale[row_t] * (Q[b][h] . K[row_t])),
+ * Q and K FP8 E4M3 vectors of 128, and index_out[b][0..k) receives the positions of the k best tokens, best
+ * first (ties: lower position first; -1 beyond n_selected_out[b] = min(k, kv_len[b])). The arithmetic is fixed
+ * to the operation (csrc/kv_indexer.cu states it), so the selection is reproducible bit for bit.
+ * q fp8 [batch][heads][128] (heads <= 64); q_scale fp32 and weights bf16 [batch][heads]; key_pool fp8
+ * [pool_rows][key_stride] (16-byte aligned, stride a multiple of 16) with k_scale fp32 [pool_rows], addressed
+ * through block_table / block_size like the KV pool; k <= 2048; workspace of
+ * b200kv_indexer_workspace_bytes(batch, max_kv_len) bytes holds the scores. First version, on CUDA cores.
+ */
+typedef struct b200kv_indexer_args {
+  const void* q;
+  const float* q_scale;
+  const void* weights;
+  int32_t heads;
+  const void* key_pool;
+  int64_t key_stride;
+  const float* k_scale;
+  int64_t pool_rows;
+  const int32_t* block_table;
+  int64_t max_blocks;
+  const int32_t* kv_len;
+  int32_t batch;
+  int32_t block_size;
+  int64_t max_kv_len; /* the largest kv_len[b] (sizes the launch) */
+  int32_t k;
+  int32_t* index_out;      /* device int32 [batch][k] */
+  int32_t* n_selected_out; /* device int32 [batch] */
+  void* workspace;
+  size_t workspace_bytes;
+} b200kv_indexer_args;
+
+size_t b200kv_indexer_workspace_bytes(int32_t batch, int64_t max_kv_len);
+int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* stream, b200kv_status_word* status);
+
+/*
  * Decode attention without a caller workspace and without any device allocation. No counterpart in
  * the reference. Same arguments and results as b200kv_mla_decode (args->workspace, workspace_bytes and
  * variant are ignored; the tensor-core kernel runs, so the geometry it needs applies: 64 heads,

@@ -218,3 +218,82 @@ void kvo_mx_quant_e4m3(const uint16_t* x, int64_t x_stride, int64_t rows, int64_
 uint8_t kvo_f32_to_e4m3(float f) { return F32ToE4m3(f); }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Sparse-selection indexer in front of attention (the reference vendors it and plans it but does not apply
+// it: include/moe/pipeline/pipeline.hpp:57-66; operator contract mock/mock_ops.cpp:1118-1221; formula
+// third_party/ops_transformer/attention/quant_lightning_indexer/README.md: out = Top-k over tokens of
+// sum_h W_h * ReLU(ScaleQ_h * ScaleK_t * (Q_h . K_t)) with FP8 E4M3 Q and K of width 128, N2 = 1).
+// PARITY UNPINNED (a closed operator on the device, a no-op in the mock). The arithmetic is specified:
+//   dot_h  = fma chain over d = 0..127 from 0, fp32, FP8 values converted exactly;
+//   s_h    = max(0, (qs_h * ks_t) * dot_h)          (two fp32 multiplications);
+//   score  = fma chain over h = 0..heads-1 of w_h * s_h from 0;  a NaN score counts as -infinity;
+//   order  = by score descending, ties by token index ascending; the first k tokens are the selection.
+// ---------------------------------------------------------------------------------------------
+namespace {
+inline float E4m3ToF32(uint8_t v) {
+  const int e = (v >> 3) & 15, m = v & 7;
+  float a;
+  if (e == 15 && m == 7) a = std::numeric_limits<float>::quiet_NaN();
+  else if (e == 0) a = std::ldexp(static_cast<float>(m), -9);
+  else a = std::ldexp(1.0f + static_cast<float>(m) / 8.0f, e - 7);
+  return (v & 0x80) ? -a : a;
+}
+}  // namespace
+
+extern "C" {
+
+// scores[b][t] for t < kv_len[b] (the rest untouched). q: fp8 [B][heads][128]; q_scale fp32 [B][heads];
+// weights bf16 [B][heads]; key pool fp8 [rows][key_stride]; k_scale fp32 [rows]; paged by block_table.
+void kvo_indexer_scores(const uint8_t* q, const float* q_scale, const uint16_t* weights, int32_t heads, const uint8_t* key_pool,
+                        int64_t key_stride, const float* k_scale, const int32_t* block_table, int64_t max_blocks,
+                        const int32_t* kv_len, int32_t batch, int32_t block_size, float* scores, int64_t score_stride) {
+  for (int32_t b = 0; b < batch; ++b) {
+    for (int32_t t = 0; t < kv_len[b]; ++t) {
+      const int64_t row = static_cast<int64_t>(block_table[b * max_blocks + t / block_size]) * block_size + t % block_size;
+      const uint8_t* k = key_pool + row * key_stride;
+      float score = 0.0f;
+      for (int32_t h = 0; h < heads; ++h) {
+        const uint8_t* qh = q + (static_cast<int64_t>(b) * heads + h) * 128;
+        float dot = 0.0f;
+        for (int d = 0; d < 128; ++d) dot = std::fmaf(E4m3ToF32(qh[d]), E4m3ToF32(k[d]), dot);
+        const float scaled = (q_scale[b * heads + h] * k_scale[row]) * dot;
+        const float s = scaled > 0.0f ? scaled : 0.0f;  // NaN compares false: 0
+        score = std::fmaf(Bf16ToF32(weights[b * heads + h]), s, score);
+      }
+      scores[b * score_stride + t] = score;
+    }
+  }
+}
+
+// index[b][0..k) = the k best tokens of sequence b (by score descending, then index ascending), -1 beyond
+// min(k, kv_len[b]); n_selected[b] = min(k, kv_len[b]).
+void kvo_topk_tokens(const float* scores, int64_t score_stride, const int32_t* kv_len, int32_t batch, int32_t k,
+                     int32_t* index, int32_t* n_selected) {
+  for (int32_t b = 0; b < batch; ++b) {
+    const int32_t n = kv_len[b];
+    // insertion into a sorted list of at most k entries: small and obviously right
+    int32_t kept = 0;
+    for (int32_t t = 0; t < n; ++t) {
+      float s = scores[b * score_stride + t];
+      if (std::isnan(s)) s = -std::numeric_limits<float>::infinity();
+      int32_t pos = kept;
+      while (pos > 0) {
+        const int32_t other = index[b * k + pos - 1];
+        float so = scores[b * score_stride + other];
+        if (std::isnan(so)) so = -std::numeric_limits<float>::infinity();
+        if (so > s || (so == s && other < t)) break;
+        --pos;
+      }
+      if (pos >= k) continue;
+      const int32_t last = kept < k ? kept : k - 1;
+      for (int32_t i = last; i > pos; --i) index[b * k + i] = index[b * k + i - 1];
+      index[b * k + pos] = t;
+      if (kept < k) ++kept;
+    }
+    for (int32_t i = kept; i < k; ++i) index[b * k + i] = -1;
+    n_selected[b] = kept;
+  }
+}
+
+}  // extern "C"

@@ -90,6 +90,9 @@ def lib() -> ctypes.CDLL:
         L.kvo_mx_quant_e4m3.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64]
         L.kvo_f32_to_e4m3.restype = ctypes.c_uint8
         L.kvo_f32_to_e4m3.argtypes = [c_float]
+        L.kvo_indexer_scores.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_void_p,
+                                         c_int64, c_void_p, c_int32, c_int32, c_void_p, c_int64]
+        L.kvo_topk_tokens.argtypes = [c_void_p, c_int64, c_void_p, c_int32, c_int32, c_void_p, c_void_p]
         L.kvo_lse_merge.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]
         L.kvo_num_threads.restype = c_int32
         L.kvo_set_num_threads.argtypes = [c_int32]
@@ -301,3 +304,23 @@ def mx_quant_e4m3(x: np.ndarray):
     scales = np.empty((rows, cols // 32), dtype=np.uint8)
     lib().kvo_mx_quant_e4m3(_p(x), cols, rows, cols, _p(q), cols, _p(scales), cols // 32)
     return q, scales
+
+
+def indexer_topk(q_fp8: np.ndarray, q_scale: np.ndarray, weights: np.ndarray, key_pool: np.ndarray, k_scale: np.ndarray,
+                 block_table: np.ndarray, kv_len: np.ndarray, block_size: int, k: int):
+    """q_fp8 uint8 [B, H, 128], q_scale f32 [B, H], weights uint16 (bf16) [B, H], key_pool uint8 [rows, 128],
+    k_scale f32 [rows] -> (scores f32 [B, max_len], index int32 [B, k], n_selected int32 [B])."""
+    q_fp8, key_pool = np.ascontiguousarray(q_fp8), np.ascontiguousarray(key_pool)
+    q_scale, k_scale = np.ascontiguousarray(q_scale, dtype=np.float32), np.ascontiguousarray(k_scale, dtype=np.float32)
+    weights = np.ascontiguousarray(weights, dtype=np.uint16)
+    block_table = np.ascontiguousarray(block_table, dtype=np.int32)
+    kv_len = np.ascontiguousarray(kv_len, dtype=np.int32)
+    B, H = q_fp8.shape[0], q_fp8.shape[1]
+    max_len = max(int(kv_len.max()), 1)
+    scores = np.full((B, max_len), -np.inf, dtype=np.float32)
+    lib().kvo_indexer_scores(_p(q_fp8), _p(q_scale), _p(weights), H, _p(key_pool), key_pool.shape[1], _p(k_scale),
+                             _p(block_table), block_table.shape[1], _p(kv_len), B, block_size, _p(scores), max_len)
+    index = np.empty((B, k), dtype=np.int32)
+    n_sel = np.empty(B, dtype=np.int32)
+    lib().kvo_topk_tokens(_p(scores), max_len, _p(kv_len), B, k, _p(index), _p(n_sel))
+    return scores, index, n_sel

@@ -227,3 +227,101 @@ def test_stage_operators_through_the_operator_abi():
     torch.cuda.synchronize()
     exp_q, exp_s = kvo.mx_quant_e4m3(x_np)
     assert np.array_equal(q8.cpu().numpy(), exp_q) and np.array_equal(sc.cpu().numpy(), exp_s)
+
+
+def _indexer_inputs(B, H, lens, bs, seed):
+    import test_stage_oracle
+
+    return test_stage_oracle._indexer_case(B, H, lens, bs, seed)
+
+
+@pytest.mark.parametrize("lens,k", [([4096, 300, 5000, 17, 0, 9000], 512), ([70, 64], 2048), ([12000], 100)])
+def test_indexer_selection_matches_oracle_bit_for_bit(lens, k):
+    B, H, bs = len(lens), 64, 64
+    q, qs, w, key, ks, table, kv_len = _indexer_inputs(B, H, lens, bs, seed=11 + k)
+    # ties on purpose: two tokens with identical keys and scales
+    if lens[0] > 40:
+        r = lambda t: int(table[0, t // bs]) * bs + t % bs
+        key[r(31)] = key[r(5)]
+        ks[r(31)] = ks[r(5)]
+    exp_scores, exp_index, exp_n = kvo.indexer_topk(q, qs, w, key, ks, table, kv_len, bs, k)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    st = b200kv.new_status()
+    index, n_sel = b200kv.indexer_topk(d(q), d(qs), to_dev_bf16(w), d(key), d(ks), to_dev_i32(table), to_dev_i32(kv_len),
+                                       bs, int(max(lens)), k, status=st)
+    torch.cuda.synchronize()
+    assert st.cpu().tolist()[0] == 0
+    assert np.array_equal(n_sel.cpu().numpy(), exp_n)
+    assert np.array_equal(index.cpu().numpy(), exp_index), "selection differs from the oracle"
+
+
+def test_sparse_attention_pipeline_indexer_then_resolved_rows_then_decode():
+    """The whole sparse path on the device: top-k positions from the indexer, their pool rows, attention over
+    exactly those rows; against the float64 reference over the oracle's selection."""
+    import scenarios
+    from gpu_util import run_decode
+
+    lens, bs, k = [3000, 700, 4096], 64, 512
+    B = len(lens)
+    q8, qs, w, key, ks, table, kv_len = _indexer_inputs(B, 64, lens, bs, seed=3)
+    pool = kvo.make_pool(key.shape[0])                    # the latent KV pool shares the index cache's paging
+    q = kvo.make_q(B)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    index, n_sel = b200kv.indexer_topk(d(q8), d(qs), to_dev_bf16(w), d(key), d(ks), to_dev_i32(table), to_dev_i32(kv_len),
+                                       bs, max(lens), k)
+    rows = b200kv.resolve_rows(to_dev_i32(table), bs, index, n_sel, pool.shape[0])
+    torch.cuda.synchronize()
+    _, exp_index, exp_n = kvo.indexer_topk(q8, qs, w, key, ks, table, kv_len, bs, k)
+    exp_rows = np.full((B, k), -1, dtype=np.int32)
+    for b in range(B):
+        t = exp_index[b, : exp_n[b]].astype(np.int64)
+        exp_rows[b, : exp_n[b]] = table[b, t // bs].astype(np.int64) * bs + t % bs
+    assert np.array_equal(rows.cpu().numpy(), exp_rows)
+    out, lse = run_decode(q, pool, exp_rows, exp_n, 1, 1.0 / 24.0, b200kv.DECODE_AUTO)
+    ref_out, ref_lse = scenarios.ref_attention_f64(q, pool, exp_rows, exp_n, 1, 1.0 / 24.0)
+    scenarios.check_attention(out, lse, ref_out, ref_lse, what="sparse pipeline")
+
+
+def test_indexer_operator_through_the_operator_abi():
+    """aclnnQuantLightningIndexer with the contract's shapes (mock/mock_ops.cpp:1118-1221): TND query [T, 64, 128]
+    FP8, paged keys [blocks, block_size, 1, 128], out [T, 1, k]; plan, launch with the workspace the plan asked
+    for, compare with the oracle's selection."""
+    from ctypes import POINTER, byref, c_char_p, c_int32, c_int64, c_uint64, c_void_p
+
+    L = b200kv.lib
+    L.aclCreateTensor.restype = c_void_p
+    L.aclCreateTensor.argtypes = [POINTER(c_int64), c_uint64, c_int32, POINTER(c_int64), c_int64, c_int32,
+                                  POINTER(c_int64), c_uint64, c_void_p]
+    BF16, F32, I32, FP8 = 27, 0, 3, 36
+
+    def tensor(t, dims, dtype):
+        d = (c_int64 * len(dims))(*dims)
+        h = L.aclCreateTensor(d, len(dims), dtype, None, 0, 2, d, len(dims), t.data_ptr())
+        assert h
+        return c_void_p(h)
+
+    lens, bs, k, H = [900, 64, 2000], 128, 256, 64
+    T = len(lens)
+    q, qs, w, key, ks, table, kv_len = _indexer_inputs(T, H, lens, bs, seed=21)
+    blocks = key.shape[0] // bs
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    d_q, d_qs, d_w, d_key, d_ks = d(q), d(qs), to_dev_bf16(w), d(key), d(ks)
+    d_table, d_len = to_dev_i32(table), to_dev_i32(kv_len)
+    d_cum = to_dev_i32(np.arange(1, T + 1))
+    out = torch.full((T, 1, k), -5, dtype=torch.int32, device="cuda")
+    L.aclnnQuantLightningIndexerGetWorkspaceSize.argtypes = [c_void_p] * 8 + [c_int64, c_int64, c_char_p, c_char_p, c_int64,
+                                                                               c_int64, c_int64, c_int64, c_void_p,
+                                                                               POINTER(c_uint64), POINTER(c_void_p)]
+    L.aclnnQuantLightningIndexer.argtypes = [c_void_p, c_uint64, c_void_p, c_void_p]
+    ws_bytes, exe = c_uint64(0), c_void_p()
+    rc = L.aclnnQuantLightningIndexerGetWorkspaceSize(
+        tensor(d_q, [T, H, 128], FP8), tensor(d_key, [blocks, bs, 1, 128], FP8), tensor(d_w, [T, H], BF16),
+        tensor(d_qs, [T, H], F32), tensor(d_ks, [blocks, bs, 1], F32), tensor(d_cum, [T], I32), tensor(d_len, [T], I32),
+        tensor(d_table, [T, table.shape[1]], I32), 0, 0, b"TND", b"PA_BSND", k, 3, 2 ** 62, 2 ** 62,
+        tensor(out, [T, 1, k], I32), byref(ws_bytes), byref(exe))
+    assert rc == 0 and ws_bytes.value > 0
+    ws = torch.empty(ws_bytes.value, dtype=torch.uint8, device="cuda")
+    assert L.aclnnQuantLightningIndexer(ws.data_ptr(), ws_bytes.value, exe, None) == 0
+    torch.cuda.synchronize()
+    _, exp_index, _ = kvo.indexer_topk(q, qs, w, key, ks, table, kv_len, bs, k)
+    assert np.array_equal(out.cpu().numpy()[:, 0, :], exp_index)

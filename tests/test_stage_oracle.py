@@ -105,3 +105,48 @@ def test_mx_quant_blocks_follow_the_scale_rule():
             assert ok.all(), (r, b)
             assert np.isfinite(back).all()
     assert s[0, 0] == 0 and not q[0, :32].any() and (q[4, :32] == 0x7E).all() and s[4, 0] == 127
+
+
+def _indexer_case(B, H, lens, bs, seed=5):
+    rng = np.random.default_rng(seed)
+    blocks = int(sum((int(n) + bs - 1) // bs for n in lens)) + 2
+    table = np.zeros((B, max(1, max((int(n) + bs - 1) // bs for n in lens))), dtype=np.int32)
+    order = rng.permutation(blocks)
+    at = 0
+    for b, n in enumerate(lens):
+        nb = (int(n) + bs - 1) // bs
+        table[b, :nb] = order[at:at + nb]
+        at += nb
+    codes = np.array([c for c in range(256) if (c & 0x7F) != 0x7F], dtype=np.uint8)   # every finite E4M3 code
+    q = rng.choice(codes[(codes & 0x7F) < 0x50], size=(B, H, 128)).astype(np.uint8)
+    key = rng.choice(codes[(codes & 0x7F) < 0x50], size=(blocks * bs, 128)).astype(np.uint8)
+    q_scale = rng.uniform(0.01, 0.1, size=(B, H)).astype(np.float32)
+    k_scale = rng.uniform(0.01, 0.1, size=(blocks * bs,)).astype(np.float32)
+    weights = kvo.f32_to_bf16(rng.normal(0.0, 1.0, size=(B, H)).astype(np.float32))
+    return q, q_scale, weights, key, k_scale, table, np.asarray(lens, dtype=np.int32)
+
+
+def test_indexer_scores_and_selection_match_a_float64_restatement():
+    B, H, bs, k = 3, 16, 16, 24
+    q, qs, w, key, ks, table, lens = _indexer_case(B, H, [100, 7, 33], bs)
+    scores, index, n_sel = kvo.indexer_topk(q, qs, w, key, ks, table, lens, bs, k)
+    qf, kf = e4m3_value(q), e4m3_value(key)
+    wf = f32(w).astype(np.float64)
+    for b in range(B):
+        n = int(lens[b])
+        rows = table[b, np.arange(n) // bs].astype(np.int64) * bs + np.arange(n) % bs
+        dots = kf[rows] @ qf[b].T                                    # [n, H]
+        ref = (np.maximum(dots * (qs[b].astype(np.float64)[None, :] * ks[rows].astype(np.float64)[:, None]), 0.0)
+               * wf[b][None, :]).sum(axis=1)
+        assert np.allclose(scores[b, :n], ref, rtol=2e-5, atol=1e-5)
+        assert n_sel[b] == min(k, n) and (index[b, n_sel[b]:] == -1).all()
+        picked = index[b, : n_sel[b]]
+        assert len(set(picked.tolist())) == len(picked)
+        got = scores[b, picked]
+        assert (np.diff(got) <= 0).all()                              # best first
+        rest = np.setdiff1d(np.arange(n), picked)
+        if len(rest):
+            assert scores[b, rest].max() <= got.min()                 # nothing better was left out
+        for i in range(len(picked) - 1):                              # ties: lower position first
+            if got[i] == got[i + 1]:
+                assert picked[i] < picked[i + 1]
