@@ -148,21 +148,29 @@ __global__ void __launch_bounds__(kSortThreads)
     for (int i = k + tid; i < kMaxK; i += kSortThreads) keys[i] = kEmptyKey;
     for (int i = kMaxK + kChunk + tid; i < kSortSlots; i += kSortThreads) keys[i] = kEmptyKey;
     __syncthreads();
-    // bitonic sort of all kSortSlots keys, ascending
-    for (int size = 2; size <= kSortSlots; size <<= 1) {
+    // Bitonic sort, ascending, of the populated prefix rounded up to a power of two: the first chunk has no
+    // kept keys in front of it, so it is sorted on its own (in place at kMaxK, then moved to the front).
+    const bool first = c0 == 0;
+    uint64_t* base = first ? keys + kMaxK : keys;
+    const int n_sort = first ? kChunk : kSortSlots;
+    for (int size = 2; size <= n_sort; size <<= 1) {
       for (int stride = size >> 1; stride > 0; stride >>= 1) {
-        for (int i = tid; i < kSortSlots / 2; i += kSortThreads) {
+        for (int i = tid; i < n_sort / 2; i += kSortThreads) {
           const int lo = 2 * i - (i & (stride - 1));  // index of the pair's lower element
           const int hi = lo + stride;
           const bool ascending = (lo & size) == 0;
-          const uint64_t a = keys[lo], c = keys[hi];
+          const uint64_t a = base[lo], c = base[hi];
           if ((a > c) == ascending) {
-            keys[lo] = c;
-            keys[hi] = a;
+            base[lo] = c;
+            base[hi] = a;
           }
         }
         __syncthreads();
       }
+    }
+    if (first) {  // the best k of the first chunk to the front (k <= kMaxK: source and destination do not overlap)
+      for (int i = tid; i < k; i += kSortThreads) keys[i] = keys[kMaxK + i];
+      __syncthreads();
     }
   }
   const int kept = len < k ? len : k;
