@@ -784,9 +784,10 @@ __global__ void __launch_bounds__(256)
   // kColSplit warps (1, 4 or 16) share a row, each taking 512 / kColSplit of its columns: with few rows (one
   // long sequence has 64) that is what fills the GPU, and a lane then holds so little of a part that 16 or
   // 32 parts can be in flight at once.
-  static_assert(kColSplit == 1 || kColSplit == 4 || kColSplit == 16, "a lane holds 16, 4 or 1 floats of a row");
+  static_assert(kColSplit == 1 || kColSplit == 2 || kColSplit == 4 || kColSplit == 16,
+                "a lane holds 16, 8, 4 or 1 floats of a row");
   constexpr int kFloats = 16 / kColSplit;                                  // floats per lane and part
-  constexpr int kBatch = kColSplit == 1 ? 8 : (kColSplit == 4 ? 16 : 32);  // parts in flight
+  constexpr int kBatch = kColSplit <= 2 ? 8 : (kColSplit == 4 ? 16 : 32);  // parts in flight
   const int lane = threadIdx.x & 31;
   const int64_t warp_id = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t row = warp_id / kColSplit;
@@ -869,7 +870,7 @@ __global__ void __launch_bounds__(256)
   for (int i = 0; i < kFloats; ++i) acc[i] = 0.0f;
   // Lane `lane` of warp `quarter` holds floats [4 * (col4 + lane + 32 i), +4) of a row for i < kFloats / 4, or
   // the single float col1 + lane when sixteen warps share the row.
-  const int col4 = kColSplit == 4 ? quarter * 32 : 0;
+  const int col4 = kColSplit <= 4 ? quarter * (128 / kColSplit) : 0;
   const int col1 = quarter * 32;
 
   if (mine > 0 && c_first == c_last) return;  // written directly by the decode kernel
@@ -1177,8 +1178,11 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
                                       stream, p, n_ctas),
                      "decode finalize launch");
   }
-  return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<1>, dim3(static_cast<unsigned>((rows + 7) / 8)), dim3(256), 0, stream,
-                                    p, n_ctas),
+  // Many rows: two warps per row (109 registers against 254 for one warp per row, so twice the warps fit an
+  // SM) in CTAs of 128 threads, small enough to become resident beside the decode kernel's CTAs and have their
+  // arithmetic done when it finishes.
+  return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<2>, dim3(static_cast<unsigned>((rows * 2 + 3) / 4)), dim3(128), 0,
+                                    stream, p, n_ctas),
                    "decode finalize launch");
 }
 
