@@ -247,8 +247,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) TRACE(63, 0);
 
   // One tile's nine TMA loads (eight latent slabs, one rope slab) into stage g % kStages.
-  auto issue_tile = [&](int seq, int begin, int t, int g) {
-    const int stage = g % kStages;
+  // Pool row at which tile t of a sequence starts, through the block table.
+  auto tile_row = [&](int seq, int begin, int t) -> int64_t {
     const int tok = begin + t * kTile;
     const int64_t table_col = tok / p.block_size;
     const int64_t block =
@@ -258,6 +258,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, tok / p.block_size, static_cast<int32_t>(block));
       row = 0;  // keep the pipeline moving on addressable memory; the status word tells the host
     }
+    return row;
+  };
+  // A tile that has no free stage yet is brought into L2 meanwhile: with two stages a tile's load can only
+  // start when the tile two before it has been consumed, and from L2 it lands sooner than from DRAM. One tile
+  // ahead is the best distance measured (a 43-layer step of 32 x 4096 tokens: none 2.25 ms, one tile 2.10,
+  // two 2.15, three 2.25, four 2.32); plain prefetch.global.L2 instructions instead of TMA prefetches: 2.31.
+  auto prefetch_tile = [&](int64_t row) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) ptx::TmaPrefetchL2_2D(&latent_map, 64 * c, static_cast<int32_t>(row));
+    ptx::TmaPrefetchL2_2D(&rope_map, 0, static_cast<int32_t>(row));
+  };
+  auto issue_tile = [&](int64_t row, int g) {
+    const int stage = g % kStages;
     const uint32_t dst = kv_addr + stage * kStageBytes;
     TRACE(g, 0);
 #pragma unroll
@@ -387,7 +400,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int begin = p.kv_begin ? p.kv_begin[start_seq] : 0;
         const int t_end = min(start_seq_tiles, start_tile + static_cast<int>(hi - lo));
         for (int t = start_tile; t < t_end && pre_issued < kStages; ++t, ++pre_issued) {
-          issue_tile(start_seq, begin, t, pre_issued);
+          issue_tile(tile_row(start_seq, begin, t), pre_issued);
         }
       }
     }
@@ -428,11 +441,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int begin = p.kv_begin ? p.kv_begin[seq] : 0;
         for (int t = t_lo; t < t_hi; ++t, ++g) {
           if (g < pre_issued) continue;
+          const int64_t row = tile_row(seq, begin, t);
           if (g >= kStages) {
+            prefetch_tile(row);
             ok = BoundedWait(bar(&misc->kv_empty[g % kStages]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
             if (!ok) break;
           }
-          issue_tile(seq, begin, t, g);
+          issue_tile(row, g);
         }
       }
       if (!ok) {

@@ -93,6 +93,11 @@ __device__ __forceinline__ void TmaLoad2D(uint32_t dst, const CUtensorMap* map, 
       : "memory");
 }
 
+// The same box brought into L2 only: no shared-memory destination and no completion to wait for.
+__device__ __forceinline__ void TmaPrefetchL2_2D(const CUtensorMap* map, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+
 __device__ __forceinline__ void TmaLoad3D(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
                                           uint32_t bar) {
   asm volatile(
