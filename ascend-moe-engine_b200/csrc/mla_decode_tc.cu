@@ -43,11 +43,19 @@ constexpr int kLatent = B200KV_LATENT_DIM;
 constexpr int kRope = B200KV_ROPE_DIM;
 constexpr int kTile = 64;      // tokens per tile / KV stage
 constexpr int kStages = 2;
+#ifndef B200KV_PF
+#define B200KV_PF 1
+#endif
+// Tiles on their way into L2 ahead of the one being loaded. One is the best measured (a 43-layer step of
+// 32 x 4096 tokens: none 2.25 ms, one 2.07, two 2.17, three 2.20), with or without L2 eviction hints.
+constexpr int kPrefetchAhead = B200KV_PF;
+constexpr int kGroups = 4;                              // slab groups of a stage: slabs 2c, 2c+1 (and 8 with the last)
 constexpr int kSlabBytes = kTile * 128;                 // one 64-column slab of a tile: kTile rows x 128 B
 constexpr int kStageBytes = 9 * kSlabBytes;             // 73,728
 constexpr int kQSlabBytes = kHeads * 128;               // 8,192
 constexpr int kQBytes = 9 * kQSlabBytes;                // 73,728
 constexpr int kSoftmaxThreads = 128;
+constexpr int kSoftmaxWarps = kSoftmaxThreads / 32;     // one lane of each arrives on the barriers they signal
 constexpr int kThreads = 224;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemColS = 256;                     // S buffers at columns 256 and 256 + kTile
@@ -62,8 +70,12 @@ constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + slack for the man
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 
 struct Misc {
-  uint64_t kv_full[kStages][3];  // one per group of three slabs, so QK can start on a tile's first third
-  uint64_t kv_empty[kStages];
+  // A stage is filled, consumed and given back in four groups of slabs (0-1, 2-3, 4-5, 6-8): QK starts on a
+  // tile's first group while the rest is landing, and PV, which runs one 128-column accumulator after the other,
+  // gives the first group back after a quarter of its work, so the reload of a stage overlaps the PV that is
+  // still reading its other slabs.
+  uint64_t kv_full[kStages][kGroups];
+  uint64_t kv_empty[kStages][kGroups];
   uint64_t s_full[2];
   uint64_t s_empty[2];
   uint64_t p_full[kStages];
@@ -145,6 +157,25 @@ __device__ __noinline__ bool BoundedWait(uint32_t bar, uint32_t parity, Misc* mi
   }
 }
 
+// The same with a non-blocking probe in a tight loop. mbarrier.try_wait parks the thread and, measured here, a
+// parked thread resumes some 500 cycles after the phase completes; the producer's waits sit on the path that
+// refills a stage, so it spins instead (one thread: the issue slots it takes are few).
+__device__ __noinline__ bool BoundedSpin(uint32_t bar, uint32_t parity, Misc* misc, int32_t* status, int site) {
+  uint64_t start = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (ptx::MbarTestWait(bar, parity)) return true;
+    if ((it & 1023u) == 1023u) {
+      if (Aborting(misc)) return false;
+      const uint64_t now = ptx::GlobalTimerNs();
+      if (start == 0) start = now;
+      if (now - start > 1000000000ull) {
+        RaiseTimeout(misc, status, site, parity);
+        return false;
+      }
+    }
+  }
+}
+
 // ---- work partition -----------------------------------------------------------------------------------
 // The tiles of all sequences form one flat list (sequence after sequence, empty ones contribute nothing).
 // Cutting that list into G equal runs of tiles leaves the CTAs uneven: a CTA whose run crosses from one
@@ -211,12 +242,12 @@ __device__ __forceinline__ uint64_t DescAt(uint64_t base_desc, uint32_t byte_off
   return base_desc + static_cast<uint64_t>(byte_offset >> 4);
 }
 
-// Twelve QK k-steps (three 64-column slabs) starting at slab kFirstSlab; called by the whole MMA warp.
-template <int kFirstSlab>
+// The QK k-steps of kSlabs 64-column slabs (four each) starting at slab kFirstSlab; called by the whole MMA warp.
+template <int kFirstSlab, int kSlabs>
 __device__ __forceinline__ void IssueQkGroup(uint64_t q_desc, uint64_t kdesc, uint32_t d) {
   constexpr uint32_t kIdescQk = ptx::InstrDescBf16(64, kTile, 0, 0);
 #pragma unroll
-  for (int i = 0; i < 12; ++i) {
+  for (int i = 0; i < 4 * kSlabs; ++i) {
     const int c = kFirstSlab + (i >> 2), kk = i & 3;
     const uint64_t a = DescAt(q_desc, c * kQSlabBytes + kk * 32);
     const uint64_t b = DescAt(kdesc, c * kSlabBytes + kk * 32);
@@ -247,6 +278,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) TRACE(63, 0);
 
   // One tile's nine TMA loads (eight latent slabs, one rope slab) into stage g % kStages.
+  // A prefetched tile should stay in L2 until its load (one or two tile periods later), and is dead after it.
+  const uint64_t keep_policy = ptx::L2PolicyEvictLast();
+  const uint64_t drop_policy = ptx::L2PolicyEvictFirst();
   // Pool row at which tile t of a sequence starts, through the block table.
   auto tile_row = [&](int seq, int begin, int t) -> int64_t {
     const int tok = begin + t * kTile;
@@ -261,31 +295,27 @@ __global__ void __launch_bounds__(kThreads, 1)
     return row;
   };
   // A tile that has no free stage yet is brought into L2 meanwhile: with two stages a tile's load can only
-  // start when the tile two before it has been consumed, and from L2 it lands sooner than from DRAM. One tile
-  // ahead is the best distance measured (a 43-layer step of 32 x 4096 tokens: none 2.25 ms, one tile 2.10,
-  // two 2.15, three 2.25, four 2.32); plain prefetch.global.L2 instructions instead of TMA prefetches: 2.31.
+  // start when the tile two before it has been consumed, and from L2 it lands sooner than from DRAM. TMA
+  // prefetches; plain prefetch.global.L2 instructions from the producer warp's lanes were slower than none.
   auto prefetch_tile = [&](int64_t row) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) ptx::TmaPrefetchL2_2D(&latent_map, 64 * c, static_cast<int32_t>(row));
-    ptx::TmaPrefetchL2_2D(&rope_map, 0, static_cast<int32_t>(row));
+    for (int c = 0; c < 8; ++c) ptx::TmaPrefetchL2_2DHint(&latent_map, 64 * c, static_cast<int32_t>(row), keep_policy);
+    ptx::TmaPrefetchL2_2DHint(&rope_map, 0, static_cast<int32_t>(row), keep_policy);
   };
-  auto issue_tile = [&](int64_t row, int g) {
+  // Group c of a tile into stage g % kStages: slabs 2c and 2c + 1, and the rope slab with the last group.
+  auto issue_group = [&](int64_t row, int g, int c) {
     const int stage = g % kStages;
     const uint32_t dst = kv_addr + stage * kStageBytes;
+    const uint32_t full = bar(&misc->kv_full[stage][c]);
+    ptx::MbarArriveExpectTx(full, (c == kGroups - 1 ? 3 : 2) * kSlabBytes);
+    ptx::TmaLoad2DHint(dst + 2 * c * kSlabBytes, &latent_map, 128 * c, static_cast<int32_t>(row), full, drop_policy);
+    ptx::TmaLoad2DHint(dst + (2 * c + 1) * kSlabBytes, &latent_map, 128 * c + 64, static_cast<int32_t>(row), full, drop_policy);
+    if (c == kGroups - 1) ptx::TmaLoad2DHint(dst + 8 * kSlabBytes, &rope_map, 0, static_cast<int32_t>(row), full, drop_policy);
+  };
+  auto issue_tile = [&](int64_t row, int g) {
     TRACE(g, 0);
 #pragma unroll
-    for (int k = 0; k < 3; ++k) {
-      const uint32_t full = bar(&misc->kv_full[stage][k]);
-      ptx::MbarArriveExpectTx(full, 3 * kSlabBytes);
-#pragma unroll
-      for (int c = 3 * k; c < 3 * k + 3; ++c) {
-        if (c < 8) {
-          ptx::TmaLoad2D(dst + c * kSlabBytes, &latent_map, 64 * c, static_cast<int32_t>(row), full);
-        } else {
-          ptx::TmaLoad2D(dst + 8 * kSlabBytes, &rope_map, 0, static_cast<int32_t>(row), full);
-        }
-      }
-    }
+    for (int c = 0; c < kGroups; ++c) issue_group(row, g, c);
   };
   // Q of one sequence: nine 64-column slabs of 64 head rows.
   auto issue_q = [&](int seq) {
@@ -302,18 +332,20 @@ __global__ void __launch_bounds__(kThreads, 1)
     // barrier below) then overlaps the first loads' latency instead of preceding it.
     if (lane == 0) {
       for (int s = 0; s < kStages; ++s) {
-        for (int k = 0; k < 3; ++k) ptx::MbarInit(bar(&misc->kv_full[s][k]), 1);
-        ptx::MbarInit(bar(&misc->kv_empty[s]), 1);
-        ptx::MbarInit(bar(&misc->p_full[s]), kSoftmaxThreads);
+        for (int k = 0; k < kGroups; ++k) {
+          ptx::MbarInit(bar(&misc->kv_full[s][k]), 1);
+          ptx::MbarInit(bar(&misc->kv_empty[s][k]), 1);
+        }
+        ptx::MbarInit(bar(&misc->p_full[s]), kSoftmaxWarps);
       }
       for (int s = 0; s < 2; ++s) {
         ptx::MbarInit(bar(&misc->s_full[s]), 1);
-        ptx::MbarInit(bar(&misc->s_empty[s]), kSoftmaxThreads);
+        ptx::MbarInit(bar(&misc->s_empty[s]), kSoftmaxWarps);
       }
       ptx::MbarInit(bar(&misc->q_full), 1);
       ptx::MbarInit(bar(&misc->q_empty), 1);
       ptx::MbarInit(bar(&misc->o_full), 1);
-      ptx::MbarInit(bar(&misc->o_empty), kSoftmaxThreads);
+      ptx::MbarInit(bar(&misc->o_empty), kSoftmaxWarps);
       ptx::MbarInit(bar(&misc->drain[0]), 1);
       ptx::MbarInit(bar(&misc->drain[1]), 1);
       misc->abort_flag = 0;
@@ -439,15 +471,24 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         ++seg;
         const int begin = p.kv_begin ? p.kv_begin[seq] : 0;
+        int ahead = t_lo;  // next tile of this segment to bring into L2
         for (int t = t_lo; t < t_hi; ++t, ++g) {
           if (g < pre_issued) continue;
           const int64_t row = tile_row(seq, begin, t);
           if (g >= kStages) {
-            prefetch_tile(row);
-            ok = BoundedWait(bar(&misc->kv_empty[g % kStages]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
+            if (ahead < t) ahead = t;
+            for (; ahead < t_hi && ahead < t + kPrefetchAhead; ++ahead) {
+              prefetch_tile(ahead == t ? row : tile_row(seq, begin, ahead));
+            }
+            TRACE(g, 0);
+            for (int c = 0; c < kGroups && ok; ++c) {
+              ok = BoundedSpin(bar(&misc->kv_empty[g % kStages][c]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
+              if (ok) issue_group(row, g, c);
+            }
             if (!ok) break;
+          } else {
+            issue_tile(row, g);
           }
-          issue_tile(row, g);
         }
       }
       if (!ok) {
@@ -464,7 +505,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (last < 0) continue;
           const uint32_t parity = (last / kStages) & 1;
           const uint64_t t0 = ptx::GlobalTimerNs();
-          for (int k = 0; k < 3; ++k) {
+          for (int k = 0; k < kGroups; ++k) {
             while (!ptx::MbarTryWait(bar(&misc->kv_full[s][k]), parity)) {
               if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
             }
@@ -519,15 +560,19 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t d = tmem_u + kTmemColS + kTile * buf;
             // Twelve k-steps per slab group, each group as soon as its slabs have landed (compile-time
             // offsets; a runtime offset costs the uniform-datapath issue rate).
-            IssueQkGroup<0>(q_desc, kdesc, d);
+            IssueQkGroup<0, 2>(q_desc, kdesc, d);
             ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][1]), kv_parity, misc, p.status, 26));
             if (!ok) break;
             ptx::TcFenceAfterSync();
-            IssueQkGroup<3>(q_desc, kdesc, d);
+            IssueQkGroup<2, 2>(q_desc, kdesc, d);
             ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][2]), kv_parity, misc, p.status, 27));
             if (!ok) break;
             ptx::TcFenceAfterSync();
-            IssueQkGroup<6>(q_desc, kdesc, d);
+            IssueQkGroup<4, 2>(q_desc, kdesc, d);
+            ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][3]), kv_parity, misc, p.status, 28));
+            if (!ok) break;
+            ptx::TcFenceAfterSync();
+            IssueQkGroup<6, 3>(q_desc, kdesc, d);
             if (ptx::ElectOne()) {
               ptx::TcCommit(bar(&misc->s_full[buf]));
               if (i == n - 1) ptx::TcCommit(bar(&misc->q_empty));  // Q buffer free for the next segment
@@ -552,16 +597,16 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint64_t vdesc = DescAt(v_desc0, stage_off);
             const int first_pv = __shfl_sync(0xffffffffu, i == 0 ? 1 : 0, 0);
 #pragma unroll
-            for (int ks = 0; ks < kTile / 16; ++ks) {
+            for (int tm = 0; tm < 4; ++tm) {  // accumulator by accumulator: slabs 2tm, 2tm + 1 are done with after it
 #pragma unroll
-              for (int tm = 0; tm < 4; ++tm) {
+              for (int ks = 0; ks < kTile / 16; ++ks) {
                 const uint64_t a = DescAt(vdesc, 2 * tm * kSlabBytes + ks * 2048);
                 const uint64_t b = DescAt(pdesc, ks * 32);
                 const uint32_t acc = (first_pv != 0 && ks == 0) ? 0u : 1u;
                 if (ptx::ElectOne()) ptx::MmaF16SS(tmem_u + 64 * tm, a, b, kIdescPv, acc);
               }
+              if (ptx::ElectOne()) ptx::TcCommit(bar(&misc->kv_empty[stage][tm]));
             }
-            if (ptx::ElectOne()) ptx::TcCommit(bar(&misc->kv_empty[stage]));
             TRACE(g, 6);
           }
           if (ok && ptx::ElectOne()) ptx::TcCommit(bar(&misc->o_full));
@@ -584,8 +629,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ======================= softmax + epilogue warps ============================================
     const int tid = threadIdx.x;                 // 0..127
     const bool row_ok = lane < 16;               // M=64 accumulators use lanes 0..15 of each 32-lane quarter
-    const bool upper = lane >= 16;               // takes tokens 32..63 of row (lane - 16) in the softmax
-    const int head = warp * 16 + (lane & 15);
+    const int head = warp * 16 + (lane & 15);    // the row this lane writes (m, l) for in the epilogue
+    // In the softmax a thread holds 16 scores of each of two rows: quad q = lane / 4 has rows q and q + 8 of
+    // this warp's sixteen, thread lane % 4 of the quad the token pairs 8i + 2(lane % 4), i = 0..7.
+    const int quad_row = lane >> 2;
+    const int quad_col = (lane & 3) * 2;
+    const int head0 = warp * 16 + quad_row;      // and head0 + 8
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     SegmentWalker walk(p.kv_len, p.batch, start_seq, start_tile, my_tiles);
     int seq, t_lo, t_hi, seq_tiles, seq_len;
@@ -595,8 +644,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool first_segment_of_cta = true;
 
     while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
-      float m_run = -INFINITY;  // reference maximum, log2 domain (s * scale * log2e)
-      float l_run = 0.0f;
+      float m_run[2] = {-INFINITY, -INFINITY};  // reference maxima of the two rows, log2 domain (s * scale * log2e)
+      float l_run[2] = {0.0f, 0.0f};
       const int n = t_hi - t_lo;
       for (int i = 0; i < n && ok; ++i, ++g) {
         const int buf = g & 1;
@@ -607,71 +656,84 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) break;
         ptx::TcFenceAfterSync();
         if (tid == 0) TRACE(g, 3);
-        uint32_t sr[kTile];
-#pragma unroll
-        for (int part = 0; part < kTile / 32; ++part) {
-          ptx::TmemLd32(tmem + lane_base + kTmemColS + kTile * buf + 32 * part,
-                        *reinterpret_cast<uint32_t(*)[32]>(&sr[32 * part]));
-        }
+        static_assert(kTile == 64, "one 16x256b.x8 load covers the 64 columns of a tile");
+        uint32_t sr[32];
+        ptx::TmemLd16x256bX8(tmem + lane_base + kTmemColS + kTile * buf, sr);
         ptx::TmemWaitLd();
         ptx::TcFenceBeforeSync();
-        ptx::MbarArrive(bar(&misc->s_empty[buf]));
+        __syncwarp();
+        if (lane == 0) ptx::MbarArrive(bar(&misc->s_empty[buf]));  // one arrival per warp
 
-        // Lanes 0-15 of a warp hold the 64 scores of their row (an M=64 accumulator occupies lanes 0-15
-        // of each 32-lane quarter). Lane t+16 takes over tokens 32-63 of lane t's row, so all 128 threads
-        // work: x[j] is token tok_base + j of row `head`.
-        static_assert(kTile == 64, "the lane split below assumes 64-token tiles");
-        const int tok_base = upper ? 32 : 0;
-        float x[32];
+        // x[r][2k + e] = score of row head0 + 8r, token 8k + quad_col + e.
+        float x[2][16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const uint32_t from_pair = __shfl_sync(0xffffffffu, sr[32 + j], lane & 15);
-          x[j] = __uint_as_float(upper ? from_pair : sr[j]);
+        for (int k = 0; k < 8; ++k) {
+          x[0][2 * k] = __uint_as_float(sr[4 * k]);
+          x[0][2 * k + 1] = __uint_as_float(sr[4 * k + 1]);
+          x[1][2 * k] = __uint_as_float(sr[4 * k + 2]);
+          x[1][2 * k + 1] = __uint_as_float(sr[4 * k + 3]);
         }
-        // Raw maximum first (the scale is positive), then one FFMA + one EX2 per element.
-        float raw_max = -INFINITY;
-        if (valid == kTile) {
+        if (valid < kTile) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) raw_max = fmaxf(raw_max, x[j]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (tok_base + j >= valid) x[j] = -INFINITY;  // masked out of the maximum and of P
-            raw_max = fmaxf(raw_max, x[j]);
+          for (int j = 0; j < 16; ++j) {
+            if (8 * (j >> 1) + quad_col + (j & 1) >= valid) {  // masked out of the maximum and of P
+              x[0][j] = -INFINITY;
+              x[1][j] = -INFINITY;
+            }
           }
         }
-        raw_max = fmaxf(raw_max, __shfl_xor_sync(0xffffffffu, raw_max, 16));
-        const float tile_max = raw_max * p.scale_log2;
-        float factor = 1.0f;
-        bool rescale = false;
-        if (m_run == -INFINITY) {
-          m_run = tile_max;  // first tile of the segment: nothing accumulated yet
-        } else if (tile_max > m_run + kRescaleThreshold) {
-          factor = exp2f(m_run - tile_max);
-          m_run = tile_max;
-          rescale = true;
-        }
-        if (!upper) misc->factor[head] = factor;
-        const float neg_m = -m_run;
-        float sum = 0.0f;
-        uint32_t packed[16];
+        // Raw maxima first (the scale is positive), then one FFMA + one EX2 per element.
+        float raw_max[2];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = ptx::Ex2Approx(fmaf(x[2 * j], p.scale_log2, neg_m));
-          const float p1 = ptx::Ex2Approx(fmaf(x[2 * j + 1], p.scale_log2, neg_m));
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          packed[j] = *reinterpret_cast<const uint32_t*>(&pb);
-          sum += p0 + p1;  // the denominator (and lse) keep the unrounded fp32 weights
+        for (int r = 0; r < 2; ++r) {  // a tree, not a chain: one warp per scheduler pays every dependent latency
+          float t[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t[j] = fmaxf(x[r][2 * j], x[r][2 * j + 1]);
+          raw_max[r] = fmaxf(fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3])), fmaxf(fmaxf(t[4], t[5]), fmaxf(t[6], t[7])));
         }
-        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-        l_run = l_run * factor + sum;
+        bool rescale = false;
+        float neg_m[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          raw_max[r] = fmaxf(raw_max[r], __shfl_xor_sync(0xffffffffu, raw_max[r], 1));
+          raw_max[r] = fmaxf(raw_max[r], __shfl_xor_sync(0xffffffffu, raw_max[r], 2));
+          const float tile_max = raw_max[r] * p.scale_log2;
+          // The reference maximum moves only when the tile's exceeds it by the threshold (always on a segment's
+          // first tile, where m_run is -inf and nothing has been accumulated). No branch: a factor of
+          // exp2(0) = 1 costs one more EX2, a divergent branch costs more.
+          const bool moves = tile_max > m_run[r] + kRescaleThreshold;
+          const float m_new = moves ? tile_max : m_run[r];
+          const float factor = i == 0 ? 1.0f : ptx::Ex2Approx(m_run[r] - m_new);
+          m_run[r] = m_new;
+          rescale |= moves && i > 0;
+          if ((lane & 3) == 0) misc->factor[head0 + 8 * r] = factor;
+          l_run[r] *= factor;
+          neg_m[r] = -m_run[r];
+        }
+        uint32_t packed[2][8];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          float part[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float p0 = ptx::Ex2Approx(fmaf(x[r][2 * k], p.scale_log2, neg_m[r]));
+            const float p1 = ptx::Ex2Approx(fmaf(x[r][2 * k + 1], p.scale_log2, neg_m[r]));
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            packed[r][k] = *reinterpret_cast<const uint32_t*>(&pb);
+            part[k] = p0 + p1;  // the denominator (and lse) keep the unrounded fp32 weights
+          }
+          float sum = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          l_run[r] += sum;
+        }
 
         const bool any_rescale = ptx::NamedBarrierOr(1, kSoftmaxThreads, rescale);
         if (any_rescale) {
           // Rare path: scale the accumulated O^T columns (heads) by their factors. PV of the previous
           // tile must have drained first; its commit is the arrival on that tile's kv_empty.
           const int gp = g - 1;
-          ok = BoundedWait(bar(&misc->kv_empty[gp % kStages]), (gp / kStages) & 1, misc, p.status, 31);
+          ok = BoundedWait(bar(&misc->kv_empty[gp % kStages][kGroups - 1]), (gp / kStages) & 1, misc, p.status, 31);
           if (!ok) break;
           ptx::TcFenceAfterSync();
 #pragma unroll 1
@@ -692,15 +754,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         unsigned char* stage_ptr = smem + kOffKv + stage * kStageBytes;
         {
-          // Row `head` of P (64 bf16 = 8 chunks of 16 bytes, this thread's half = 4 chunks) over the
-          // stage's rope slab, which QK has finished with; chunks swizzled by the row index as the
-          // 128-byte pattern prescribes.
-          unsigned char* prow = stage_ptr + 8 * kSlabBytes + head * 128;
-          const int c0 = upper ? 4 : 0;
+          // P over the stage's rope slab, which QK has finished with: row = head, 64 bf16 = 8 chunks of 16
+          // bytes, chunks swizzled by the row index as the 128-byte pattern prescribes. This thread's pair of
+          // tokens of chunk k is 4 bytes at quad_col * 2; a quad completes the chunk, and the eight quads of a
+          // warp land in eight different chunk positions, so a store instruction touches each bank once.
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            *reinterpret_cast<int4*>(prow + (((c0 + c) ^ (head & 7)) << 4)) =
-                make_int4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          for (int r = 0; r < 2; ++r) {
+            // Row base (128-byte aligned) + quad_col * 2 < 16 leaves bits 4-6 free, so the swizzled chunk offset
+            // (k ^ quad_row) << 4 is one XOR with a constant on a value prepared once.
+            const uint32_t prow = ptx::SmemAddr(stage_ptr + 8 * kSlabBytes + (head0 + 8 * r) * 128 + quad_col * 2) ^
+                                  static_cast<uint32_t>(quad_row << 4);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ptx::StShared32(prow ^ static_cast<uint32_t>(k << 4), packed[r][k]);
           }
         }
         if (valid < kTile) {
@@ -716,7 +781,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::FenceProxyAsyncShared();
         if (any_rescale) ptx::NamedBarrier(2, kSoftmaxThreads);  // factors are read before the next tile rewrites them
         if (tid == 0) TRACE(g, 4);
-        ptx::MbarArrive(bar(&misc->p_full[stage]));
+        __syncwarp();
+        if (lane == 0) ptx::MbarArrive(bar(&misc->p_full[stage]));
       }
       if (!ok) break;
 
@@ -729,17 +795,22 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool to_user_partial = whole && p.user_o != nullptr;
       const bool to_ws = !whole;
       const int slot = cta * 2 + (first_segment_of_cta ? 0 : 1);
-      const float m_nat = m_run * 0.6931471805599453f;
+      // Lane j < 16 writes row j of this warp's sixteen: its (m, l) sit in quad j % 8, entry j / 8.
+      const int from = 4 * (lane & 7);
+      const float m_lo = __shfl_sync(0xffffffffu, m_run[0], from), m_hi = __shfl_sync(0xffffffffu, m_run[1], from);
+      const float l_lo = __shfl_sync(0xffffffffu, l_run[0], from), l_hi = __shfl_sync(0xffffffffu, l_run[1], from);
+      const float l_row = (lane & 8) ? l_hi : l_lo;
+      const float m_nat = ((lane & 8) ? m_hi : m_lo) * 0.6931471805599453f;
       if (row_ok) {
-        misc->inv_l[head] = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        misc->inv_l[head] = l_row > 0.0f ? 1.0f / l_row : 0.0f;
         if (to_ws) {
           p.ws_m[head * p.n_slots + slot] = m_nat;
-          p.ws_l[head * p.n_slots + slot] = l_run;
+          p.ws_l[head * p.n_slots + slot] = l_row;
         } else if (to_user_partial) {
           p.user_m[static_cast<int64_t>(seq) * kHeads + head] = m_nat;
-          p.user_l[static_cast<int64_t>(seq) * kHeads + head] = l_run;
+          p.user_l[static_cast<int64_t>(seq) * kHeads + head] = l_row;
         } else if (p.lse != nullptr) {
-          p.lse[static_cast<int64_t>(seq) * kHeads + head] = m_nat + logf(l_run);
+          p.lse[static_cast<int64_t>(seq) * kHeads + head] = m_nat + logf(l_row);
         }
       }
       ptx::NamedBarrier(1, kSoftmaxThreads);
@@ -769,7 +840,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       ptx::TcFenceBeforeSync();
-      ptx::MbarArrive(bar(&misc->o_empty));
+      __syncwarp();
+      if (lane == 0) ptx::MbarArrive(bar(&misc->o_empty));
       if (tid == 0) TRACE(63, 3 + 2 * (seg & 1));
       first_segment_of_cta = false;
       ++seg;

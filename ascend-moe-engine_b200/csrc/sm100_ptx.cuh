@@ -98,6 +98,31 @@ __device__ __forceinline__ void TmaPrefetchL2_2D(const CUtensorMap* map, int32_t
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 
+// L2 eviction-priority descriptors for the cache-hinted forms below.
+__device__ __forceinline__ uint64_t L2PolicyEvictLast() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ uint64_t L2PolicyEvictFirst() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void TmaPrefetchL2_2DHint(const CUtensorMap* map, int32_t x, int32_t y, uint64_t policy) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile.L2::cache_hint [%0, {%1, %2}], %3;" ::"l"(map), "r"(x),
+               "r"(y), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ void TmaLoad2DHint(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar,
+                                              uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, "
+      "%3}], [%4], %5;" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ void TmaLoad3D(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
                                           uint32_t bar) {
   asm volatile(
@@ -180,6 +205,34 @@ __device__ __forceinline__ void TmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
+// 16 lanes x 64 columns spread over the whole warp (shape 16x256b, eight repetitions): thread t receives, for
+// each group i of eight columns, r[4i], r[4i+1] = lane t/4, columns 8i + 2(t%4) and the next, and r[4i+2],
+// r[4i+3] = lane t/4 + 8, same columns. An M=64 accumulator keeps its rows in lanes 0-15 of each 32-lane
+// quarter, so this form hands every thread of a warp an equal share of them.
+__device__ __forceinline__ void TmemLd16x256bX8(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// The same shape over 32 columns (four repetitions): r[4i..4i+3] as above for i = 0..3.
+__device__ __forceinline__ void TmemLd16x256bX4(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
 __device__ __forceinline__ void TmemSt32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -213,6 +266,10 @@ __device__ __forceinline__ bool NamedBarrierOr(uint32_t id, uint32_t threads, bo
       : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(threads)
       : "memory");
   return out != 0;
+}
+
+__device__ __forceinline__ void StShared32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float Ex2Approx(float x) {
