@@ -68,6 +68,10 @@ class DecodeArgs(Structure):
         ("workspace_bytes", c_size_t),
         ("variant", c_int32),
         ("max_ctas", c_int32),
+        ("new_latent", c_void_p),
+        ("new_latent_stride", c_int64),
+        ("new_rope", c_void_p),
+        ("new_rope_stride", c_int64),
     ]
 
 
@@ -318,8 +322,10 @@ def decode_workspace_bytes(batch: int, heads: int = HEADS, max_ctas: int = 0) ->
 
 def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: float, out=None, lse=None,
                kv_begin=None, partial=None, workspace=None, variant: int = DECODE_AUTO, max_ctas: int = 0,
-               status=None, stream=None) -> None:
-    """q bf16 [B, H, 576]; out bf16 [B, H, 512]; lse fp32 [B, H]; partial = (o fp32 [B,H,512], m, l)."""
+               status=None, stream=None, new_rows=None) -> None:
+    """q bf16 [B, H, 576]; out bf16 [B, H, 512]; lse fp32 [B, H]; partial = (o fp32 [B,H,512], m, l).
+    new_rows = (latent bf16 [B, 512], rope bf16 [B, 64]): the append fused into the launch, each sequence's
+    new row written at its position kv_len - 1 before the attention reads it."""
     args = DecodeArgs()
     args.q = _ptr(q)
     args.q_seq_stride = q.stride(0)
@@ -341,6 +347,10 @@ def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: f
     args.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     args.variant = variant
     args.max_ctas = max_ctas
+    if new_rows is not None:
+        new_latent, new_rope = new_rows
+        args.new_latent, args.new_latent_stride = _ptr(new_latent), new_latent.stride(0)
+        args.new_rope, args.new_rope_stride = _ptr(new_rope), new_rope.stride(0)
     check(lib.b200kv_mla_decode(ctypes.byref(args), _stream_handle(stream), _ptr(status)))
 
 

@@ -74,7 +74,7 @@ using namespace b200kv;
 
 extern "C" const char* b200kv_last_error(void) { return g_error; }
 
-extern "C" int32_t b200kv_abi_version(void) { return 1; }
+extern "C" int32_t b200kv_abi_version(void) { return 2; }
 
 extern "C" size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas) {
   if (batch <= 0 || heads <= 0) return 0;
@@ -116,6 +116,10 @@ extern "C" int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* strea
     return B200KV_ERR_INVALID;
   }
   const bool use_tc = a.variant == B200KV_DECODE_TCGEN05 || (a.variant == B200KV_DECODE_AUTO && tc_ok);
+  if ((a.new_latent != nullptr || a.new_rope != nullptr) && !use_tc) {
+    SetLastError("decode: the fused append runs in the tcgen05 kernel only");
+    return B200KV_ERR_INVALID;
+  }
   const int32_t sms = CurrentDeviceSmCount();
   const int32_t ctas = a.max_ctas > 0 ? a.max_ctas : sms;
   const size_t need = use_tc ? TcWorkspaceBytes(ctas) : (SimtSplitCount(a.batch, sms) > 1 ? SimtWorkspaceBytes(a.batch, a.heads, sms) : 0);

@@ -65,7 +65,7 @@ constexpr float kRescaleThreshold = 8.0f;               // log2 units: rescale O
 constexpr int kOffQ = 0;
 constexpr int kOffKv = kOffQ + kQBytes;
 constexpr int kOffMisc = kOffKv + kStages * kStageBytes;
-constexpr int kMiscBytes = 1024;
+constexpr int kMiscBytes = 4096;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + slack for the manual 1024-byte alignment
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 
@@ -91,6 +91,10 @@ struct Misc {
   int32_t n_tiles;
   float factor[kHeads];
   float inv_l[kHeads];
+  // Fused append: the sequence's new row (512 latent + 64 rope bf16) on its way from the caller's buffer to
+  // the pool, and the barrier its bulk load completes on.
+  alignas(16) unsigned char new_row[(kLatent + kRope) * 2];
+  uint64_t new_row_full;
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc does not fit its reservation");
 
@@ -103,6 +107,15 @@ struct TcParams {
   const int32_t* kv_len;
   const int32_t* kv_begin;
   int64_t pool_rows;
+  // Fused append (null = none): the new rows, and the pool once more as plain pointers to write them through.
+  const char* new_latent;
+  const char* new_rope;
+  int64_t new_latent_bytes;  // row strides in bytes
+  int64_t new_rope_bytes;
+  char* pool_latent;
+  char* pool_rope;
+  int64_t pool_latent_bytes;
+  int64_t pool_rope_bytes;
   int32_t batch;
   int32_t block_size;
   float scale_log2;  // scale * log2(e)
@@ -317,6 +330,29 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
     for (int c = 0; c < kGroups; ++c) issue_group(row, g, c);
   };
+  // Fused append, first half: the new row of `seq` starts towards shared memory.
+  auto new_row_fetch = [&](int seq) {
+    const uint32_t full = bar(&misc->new_row_full);
+    ptx::MbarArriveExpectTx(full, (kLatent + kRope) * 2);
+    ptx::BulkLoad(ptx::SmemAddr(misc->new_row), p.new_latent + seq * p.new_latent_bytes, kLatent * 2, full);
+    ptx::BulkLoad(ptx::SmemAddr(misc->new_row) + kLatent * 2, p.new_rope + seq * p.new_rope_bytes, kRope * 2, full);
+  };
+  // Second half, just before the load of the tile that holds the row: shared memory -> pool row with plain
+  // stores (72 x 16 bytes, one thread), made visible to the TMA load that follows. `parity` counts this CTA's
+  // appends.
+  auto new_row_store = [&](int64_t row, uint32_t parity) -> bool {
+    if (!BoundedWait(bar(&misc->new_row_full), parity, misc, p.status, 12)) return false;
+    const int4* src = reinterpret_cast<const int4*>(misc->new_row);
+    int4* latent_dst = reinterpret_cast<int4*>(p.pool_latent + row * p.pool_latent_bytes);
+    int4* rope_dst = reinterpret_cast<int4*>(p.pool_rope + row * p.pool_rope_bytes);
+#pragma unroll 8
+    for (int i = 0; i < kLatent / 8; ++i) latent_dst[i] = src[i];
+#pragma unroll
+    for (int i = 0; i < kRope / 8; ++i) rope_dst[i] = src[kLatent / 8 + i];
+    __threadfence();
+    ptx::FenceProxyAsync();
+    return true;
+  };
   // Q of one sequence: nine 64-column slabs of 64 head rows.
   auto issue_q = [&](int seq) {
     const uint32_t qbar = bar(&misc->q_full);
@@ -342,6 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::MbarInit(bar(&misc->s_full[s]), 1);
         ptx::MbarInit(bar(&misc->s_empty[s]), kSoftmaxWarps);
       }
+      ptx::MbarInit(bar(&misc->new_row_full), 1);
       ptx::MbarInit(bar(&misc->q_full), 1);
       ptx::MbarInit(bar(&misc->q_empty), 1);
       ptx::MbarInit(bar(&misc->o_full), 1);
@@ -430,7 +467,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (hi > lo && start_seq < p.batch) {
         issue_q(start_seq);
         const int begin = p.kv_begin ? p.kv_begin[start_seq] : 0;
-        const int t_end = min(start_seq_tiles, start_tile + static_cast<int>(hi - lo));
+        // A tile that a fused append still has to write into is left to the main loop.
+        const int t_end = min(start_seq_tiles - (p.new_latent != nullptr ? 1 : 0), start_tile + static_cast<int>(hi - lo));
         for (int t = start_tile; t < t_end && pre_issued < kStages; ++t, ++pre_issued) {
           issue_tile(tile_row(start_seq, begin, t), pre_issued);
         }
@@ -461,6 +499,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       int g = 0;  // tiles issued
       bool ok = true;
       int seg = 0;
+      uint32_t n_appended = 0;
+      bool fetch_pending = false;  // a new row's bulk load is in flight towards shared memory
       while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
         // Q of this segment's sequence, once the previous segment's last QK has finished reading the
         // buffer (the first segment's Q went out before the setup barrier).
@@ -471,10 +511,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         ++seg;
         const int begin = p.kv_begin ? p.kv_begin[seq] : 0;
+        const bool appends = p.new_latent != nullptr && t_hi == seq_tiles;  // this segment holds the sequence's end
+        if (appends) {
+          new_row_fetch(seq);
+          fetch_pending = true;
+        }
         int ahead = t_lo;  // next tile of this segment to bring into L2
         for (int t = t_lo; t < t_hi; ++t, ++g) {
           if (g < pre_issued) continue;
           const int64_t row = tile_row(seq, begin, t);
+          if (appends && t == seq_tiles - 1) {
+            ok = new_row_store(row + (seq_len - 1 - t * kTile), n_appended & 1);
+            if (!ok) break;
+            ++n_appended;
+            fetch_pending = false;
+          }
           if (g >= kStages) {
             if (ahead < t) ahead = t;
             for (; ahead < t_hi && ahead < t + kPrefetchAhead; ++ahead) {
@@ -489,6 +540,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           } else {
             issue_tile(row, g);
           }
+        }
+      }
+      if (!ok && fetch_pending) {
+        const uint64_t t0 = ptx::GlobalTimerNs();
+        while (!ptx::MbarTryWait(bar(&misc->new_row_full), n_appended & 1)) {
+          if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
         }
       }
       if (!ok) {
@@ -1201,6 +1258,20 @@ bool TcSupports(const b200kv_decode_args& a) {
 }
 
 int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status) {
+  if (a.new_latent != nullptr || a.new_rope != nullptr) {
+    if (a.new_latent == nullptr || a.new_rope == nullptr) {
+      SetLastError("decode: a fused append needs both new_latent and new_rope");
+      return B200KV_ERR_NULLPTR;
+    }
+    if (a.kv_begin != nullptr || a.new_latent_stride < kLatent || a.new_latent_stride % 8 != 0 ||
+        a.new_rope_stride < kRope || a.new_rope_stride % 8 != 0 ||
+        ((reinterpret_cast<uintptr_t>(a.new_latent) | reinterpret_cast<uintptr_t>(a.new_rope)) & 15u) != 0) {
+      SetLastError("decode: the fused append works without kv_begin, from 16-byte aligned rows whose strides are "
+                   "multiples of 8 elements (strides %lld / %lld)",
+                   static_cast<long long>(a.new_latent_stride), static_cast<long long>(a.new_rope_stride));
+      return B200KV_ERR_INVALID;
+    }
+  }
   static thread_local int configured_device = -1;
   int device = 0;
   if (int32_t rc = CheckCuda(cudaGetDevice(&device), "cudaGetDevice")) return rc;
@@ -1228,6 +1299,14 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.kv_len = a.kv_len;
   p.kv_begin = a.kv_begin;
   p.pool_rows = a.pool.pool_rows;
+  p.new_latent = static_cast<const char*>(a.new_latent);
+  p.new_rope = static_cast<const char*>(a.new_rope);
+  p.new_latent_bytes = a.new_latent_stride * 2;
+  p.new_rope_bytes = a.new_rope_stride * 2;
+  p.pool_latent = static_cast<char*>(a.pool.latent);
+  p.pool_rope = static_cast<char*>(a.pool.rope);
+  p.pool_latent_bytes = a.pool.latent_row_stride * 2;
+  p.pool_rope_bytes = a.pool.rope_row_stride * 2;
   p.batch = a.batch;
   p.block_size = a.block_size;
   p.scale_log2 = a.scale * 1.4426950408889634f;

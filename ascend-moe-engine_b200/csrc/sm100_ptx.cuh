@@ -123,6 +123,16 @@ __device__ __forceinline__ void TmaLoad2DHint(uint32_t dst, const CUtensorMap* m
       : "memory");
 }
 
+// Untiled bulk copy, global -> this CTA's shared memory (both 16-byte aligned, a multiple of 16 bytes),
+// completion on an mbarrier.
+__device__ __forceinline__ void BulkLoad(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// Orders this thread's earlier generic-proxy accesses (global or shared) before later async-proxy ones.
+__device__ __forceinline__ void FenceProxyAsync() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 __device__ __forceinline__ void TmaLoad3D(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
                                           uint32_t bar) {
   asm volatile(

@@ -245,21 +245,25 @@ class Workload:
                       variant=variant, status=self.status, stream=stream)
         self.launches += 3  # append, decode, finalize
 
-    def step_resident(self, variant, events=None):
+    def step_resident(self, variant, events=None, fused=False):
+        """43 layers of append + attention. fused: the append rides in the attention launch (the decode kernel
+        writes each sequence's new row before it reads that tile) instead of a launch of its own."""
         torch = self.torch
         for layer in range(LAYERS):
-            self.kv.append(self.views[layer], self.new_rows[layer][:, :LATENT], self.new_rows[layer][:, LATENT:],
-                           self.slots, status=self.status)
+            new = self.new_rows[layer]
+            if not fused:
+                self.kv.append(self.views[layer], new[:, :LATENT], new[:, LATENT:], self.slots, status=self.status)
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
             self.kv.mla_decode(self.q[layer], self.views[layer], self.table, self.kv_len, BLOCK, SCALE,
-                               out=self.out[layer], workspace=self.ws, variant=variant, status=self.status)
+                               out=self.out[layer], workspace=self.ws, variant=variant, status=self.status,
+                               new_rows=(new[:, :LATENT], new[:, LATENT:]) if fused else None)
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
-            self.launches += 3
+            self.launches += 2 if fused else 3
 
 
 def check_against_oracle(torch, b200kv, wl: Workload, variant) -> float:
@@ -446,8 +450,18 @@ def run_b200_arm(args):
     # step is captured once in a CUDA graph and replayed: the timed region holds kernels only.
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
+    fused = args.variant != "simt" and not args.separate_append
+    if fused:
+        # The fused append must leave the pool as the append kernel does: one layer, bit for bit.
+        wl.pool[0].index_fill_(0, wl.slots.long(), 0)
+        new0 = wl.new_rows[0]
+        b200kv.mla_decode(wl.q[0], wl.views[0], wl.table, wl.kv_len, BLOCK, SCALE, out=wl.out[0], workspace=wl.ws,
+                          variant=variant, status=wl.status, new_rows=(new0[:, :LATENT], new0[:, LATENT:]))
+        torch.cuda.synchronize()
+        if not torch.equal(wl.pool[0][wl.slots.long()].view(torch.int16), new0.view(torch.int16)):
+            raise RuntimeError("fused append: the pool rows differ from the appended rows")
     with torch.cuda.stream(side):
-        wl.step_resident(variant)
+        wl.step_resident(variant, fused=fused)
         attention_only()
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
@@ -459,15 +473,15 @@ def run_b200_arm(args):
             self.fn()
 
     if args.no_graph:
-        g_step, g_attn = Eager(lambda: wl.step_resident(variant)), Eager(attention_only)
+        g_step, g_attn = Eager(lambda: wl.step_resident(variant, fused=fused)), Eager(attention_only)
     else:
         g_step = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_step):
-            wl.step_resident(variant)
+            wl.step_resident(variant, fused=fused)
         g_attn = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_attn):
             attention_only()
-    launches_per_step = LAYERS * 3  # append, decode, finalize/merge per layer
+    launches_per_step = LAYERS * (2 if fused else 3)  # (append,) decode, finalize/merge per layer
 
     # ---- device-resident timing (value) ----
     for _ in range(args.warmup):
@@ -538,9 +552,11 @@ def run_b200_arm(args):
                 compute.wait_event(in_ready[s])
                 if out_free[s] is not None:
                     compute.wait_event(out_free[s])
-                wl.kv.append(wl.views[layer], d_new[s][:, :LATENT], d_new[s][:, LATENT:], d_slots, status=wl.status)
+                if not fused:
+                    wl.kv.append(wl.views[layer], d_new[s][:, :LATENT], d_new[s][:, LATENT:], d_slots, status=wl.status)
                 wl.kv.mla_decode(d_q[s], wl.views[layer], wl.table, wl.kv_len, BLOCK, SCALE, out=d_out[s],
-                                 workspace=wl.ws, variant=variant, status=wl.status)
+                                 workspace=wl.ws, variant=variant, status=wl.status,
+                                 new_rows=(d_new[s][:, :LATENT], d_new[s][:, LATENT:]) if fused else None)
                 in_free[s] = torch.cuda.Event()
                 in_free[s].record(compute)
                 out_ready[s] = torch.cuda.Event()
@@ -601,7 +617,8 @@ def run_b200_arm(args):
             "config": {"workload": "configs[1]: B=32 x ctx 4096 per GPU, 43 layers, block 64, seeded permuted "
                                    "block tables, latent KV ~ N(0,1) bf16, 64 heads x 576",
                        "l2": "inputs larger than L2 (151 MB per layer, 6.49 GB pool walked layer by layer)",
-                       "launch": "one CUDA graph replay per step (43 x append + decode + finalize)",
+                       "launch": "one CUDA graph replay per step (43 x decode with the append fused in + finalize)"
+                                 if fused else "one CUDA graph replay per step (43 x append + decode + finalize)",
                        "decode_variant": args.variant, "self_check_max_abs_err": err,
                        "parallelism": f"sequence-partitioned x{world} (no collective)"},
             "roofline": {"kernel": "MlaDecodeTcKernel + MlaFinalizeKernel" if args.variant != "simt"
@@ -800,6 +817,8 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-move", action="store_true")
+    ap.add_argument("--separate-append", action="store_true",
+                    help="append as a launch of its own before each attention launch (default: fused into it)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="longctx only: merge the shards over peer memory (default) or with an NCCL all-gather")
     ap.add_argument("--workload", default="batched", choices=["batched", "ragged", "longctx"],

@@ -128,6 +128,19 @@ typedef struct b200kv_decode_args {
   size_t workspace_bytes;
   int32_t variant;
   int32_t max_ctas; /* 0 = one CTA per SM of the current device                     */
+  /*
+   * Append fused into the attention launch (tensor-core kernel, kv_begin null; both null = none): the new row
+   * of sequence b, new_latent[b] (512 bf16) and new_rope[b] (64 bf16), row strides in elements (multiples of
+   * 8), is written to the pool at the sequence's last position kv_len[b] - 1, through the block table, by the
+   * CTA that attends over that position, before it reads the tile. The result equals b200kv_append with
+   * slot_mapping[b] = block_table[b][(kv_len[b]-1) / block_size] * block_size + (kv_len[b]-1) % block_size
+   * followed by the attention: the two stages the reference plans back to back
+   * (src/pipeline/pipeline.cpp:226-249) as one launch. Sequences with kv_len 0 append nothing.
+   */
+  const void* new_latent;
+  int64_t new_latent_stride;
+  const void* new_rope;
+  int64_t new_rope_stride;
 } b200kv_decode_args;
 
 size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas);

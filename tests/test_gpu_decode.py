@@ -243,3 +243,89 @@ def test_random_batches_and_grid_sizes_match_the_reference(seed):
             out, lse = run_decode(q, pool, table, kv_len, bs, 1.0 / 24.0, b200kv.DECODE_TCGEN05, max_ctas=max_ctas)
             scenarios.check_attention(out, lse, ref_out, ref_lse,
                                       what=f"seed {seed} case {case} lens {kv_len.tolist()} ctas {max_ctas}")
+
+
+def _fused_append_case(kv_len, bs, blocks, seed_scale, max_ctas, two_caches=False):
+    """Pool + new rows; returns (device result, oracle result) of append-then-attend."""
+    from gpu_util import from_dev_bf16, status_ok, to_dev_bf16, to_dev_i32
+
+    B = len(kv_len)
+    table = scenarios.fragmented_tables(kv_len, bs, blocks)
+    pool = kvo.make_pool(blocks * bs)
+    q = kvo.make_q(B, scale=seed_scale)
+    new_rows = kvo.make_pool(B)[:, :576].copy()  # any bf16 rows will do; stream 1, other count
+    new_rows[:, ::7] ^= 0x0040                    # and differ from what the pool holds at those rows
+    last = kv_len.astype(np.int64) - 1
+    live = kv_len > 0
+    slots = np.full(B, -1, dtype=np.int32)
+    slots[live] = (table[np.arange(B)[live], last[live] // bs].astype(np.int64) * bs + last[live] % bs).astype(np.int32)
+    want_pool = pool.copy()
+    assert kvo.append(want_pool, np.ascontiguousarray(new_rows[live, :512]), np.ascontiguousarray(new_rows[live, 512:]),
+                      slots[live]) == 0
+    ref_out, ref_lse = scenarios.ref_attention_f64(q, want_pool, table, kv_len, bs, 1.0 / 24.0)
+
+    if two_caches:
+        lat = to_dev_bf16(np.ascontiguousarray(pool[:, :512]))
+        rope = to_dev_bf16(np.ascontiguousarray(pool[:, 512:]))
+        view = b200kv.pool_view(lat, rope)
+    else:
+        dev_pool = to_dev_bf16(pool)
+        view = b200kv.pool_view(dev_pool)
+    new_lat = to_dev_bf16(np.ascontiguousarray(new_rows[:, :512]))
+    new_rope = to_dev_bf16(np.ascontiguousarray(new_rows[:, 512:]))
+    dq = to_dev_bf16(q)
+    out = torch.full((B, 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+    lse = torch.full((B, 64), float("nan"), dtype=torch.float32, device="cuda")
+    ws = torch.empty(b200kv.decode_workspace_bytes(B, 64, max_ctas), dtype=torch.uint8, device="cuda")
+    status = b200kv.new_status()
+    b200kv.mla_decode(dq, view, to_dev_i32(table), to_dev_i32(kv_len), bs, 1.0 / 24.0, out=out, lse=lse, workspace=ws,
+                      variant=b200kv.DECODE_TCGEN05, max_ctas=max_ctas, status=status, new_rows=(new_lat, new_rope))
+    status_ok(status)
+    if two_caches:
+        got_pool = np.concatenate([from_dev_bf16(lat), from_dev_bf16(rope)], axis=1)
+    else:
+        got_pool = from_dev_bf16(dev_pool)
+    return got_pool, want_pool, from_dev_bf16(out), lse.cpu().numpy(), ref_out, ref_lse
+
+
+@pytest.mark.parametrize("max_ctas", [0, 5, 1])
+def test_append_fused_into_the_attention_launch(max_ctas):
+    """The decode launch writes each sequence's new row at position kv_len - 1 and attends over it: the pool
+    equals the oracle's append bit for bit, the attention matches the reference on the appended pool. Lengths
+    put the new row at the start, in the middle and at the end of a tile and of a block, in one-tile and
+    one-token sequences, and leave an empty sequence alone."""
+    bs = 64
+    kv_len = np.array([4097, 1, 64, 65, 0, 128, 129, 1000, 63, 2048, 2], dtype=np.int32)
+    blocks = int(sum(scenarios.blocks_for(int(n), bs) for n in kv_len)) + 5
+    got_pool, want_pool, out, lse, ref_out, ref_lse = _fused_append_case(kv_len, bs, blocks, 4.0 / 24.0, max_ctas)
+    assert np.array_equal(got_pool, want_pool)
+    scenarios.check_attention(out, lse, ref_out, ref_lse, what=f"fused append max_ctas={max_ctas}")
+    assert (out[kv_len == 0] == 0).all()
+
+
+def test_append_fused_with_the_reference_layout_of_two_caches():
+    bs = 128
+    kv_len = np.array([129, 128, 700, 1], dtype=np.int32)
+    blocks = int(sum(scenarios.blocks_for(int(n), bs) for n in kv_len)) + 2
+    got_pool, want_pool, out, lse, ref_out, ref_lse = _fused_append_case(kv_len, bs, blocks, 1.0 / 24.0, 0, two_caches=True)
+    assert np.array_equal(got_pool, want_pool)
+    scenarios.check_attention(out, lse, ref_out, ref_lse, what="fused append, two caches")
+
+
+def test_append_fused_is_refused_where_it_cannot_run():
+    from gpu_util import to_dev_bf16, to_dev_i32
+
+    bs, kv_len = 64, np.array([10], dtype=np.int32)
+    table = scenarios.build_tables(kv_len, bs, 2)
+    pool = to_dev_bf16(kvo.make_pool(2 * bs))
+    q = to_dev_bf16(kvo.make_q(1))
+    out = torch.empty((1, 64, 512), dtype=torch.bfloat16, device="cuda")
+    rows = to_dev_bf16(kvo.make_pool(1))
+    ws = torch.empty(b200kv.decode_workspace_bytes(1, 64, 0), dtype=torch.uint8, device="cuda")
+    with pytest.raises(b200kv.B200KVError):  # the CUDA-core kernel has no fused append
+        b200kv.mla_decode(q, b200kv.pool_view(pool), to_dev_i32(table), to_dev_i32(kv_len), bs, 1 / 24, out=out,
+                          workspace=ws, variant=b200kv.DECODE_SIMT, new_rows=(rows[:, :512], rows[:, 512:]))
+    with pytest.raises(b200kv.B200KVError):  # nor a KV-range shard
+        b200kv.mla_decode(q, b200kv.pool_view(pool), to_dev_i32(table), to_dev_i32(kv_len), bs, 1 / 24, out=out,
+                          workspace=ws, variant=b200kv.DECODE_TCGEN05, kv_begin=to_dev_i32(np.zeros(1)),
+                          new_rows=(rows[:, :512], rows[:, 512:]))
