@@ -72,6 +72,7 @@ class DecodeArgs(Structure):
         ("new_latent_stride", c_int64),
         ("new_rope", c_void_p),
         ("new_rope_stride", c_int64),
+        ("flags", ctypes.c_uint32),
     ]
 
 
@@ -322,10 +323,11 @@ def decode_workspace_bytes(batch: int, heads: int = HEADS, max_ctas: int = 0) ->
 
 def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: float, out=None, lse=None,
                kv_begin=None, partial=None, workspace=None, variant: int = DECODE_AUTO, max_ctas: int = 0,
-               status=None, stream=None, new_rows=None) -> None:
+               status=None, stream=None, new_rows=None, stable_tables: bool = False) -> None:
     """q bf16 [B, H, 576]; out bf16 [B, H, 512]; lse fp32 [B, H]; partial = (o fp32 [B,H,512], m, l).
     new_rows = (latent bf16 [B, 512], rope bf16 [B, 64]): the append fused into the launch, each sequence's
-    new row written at its position kv_len - 1 before the attention reads it."""
+    new row written at its position kv_len - 1 before the attention reads it. stable_tables: the block table
+    and the lengths were not written by the kernel just before this call on the stream (B200KV_DECODE_STABLE_TABLES)."""
     args = DecodeArgs()
     args.q = _ptr(q)
     args.q_seq_stride = q.stride(0)
@@ -347,6 +349,7 @@ def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: f
     args.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     args.variant = variant
     args.max_ctas = max_ctas
+    args.flags = 1 if stable_tables else 0
     if new_rows is not None:
         new_latent, new_rope = new_rows
         args.new_latent, args.new_latent_stride = _ptr(new_latent), new_latent.stride(0)

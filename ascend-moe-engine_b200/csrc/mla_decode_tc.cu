@@ -118,6 +118,7 @@ struct TcParams {
   int64_t pool_rope_bytes;
   int32_t batch;
   int32_t block_size;
+  int32_t stable_tables;  // lengths and block table may be read before the stream dependency wait
   float scale_log2;  // scale * log2(e)
   __nv_bfloat16* out;
   float* lse;
@@ -395,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // Up to here nothing read memory that an earlier kernel in the stream may still be writing, so under
     // a programmatic dependent launch the lines above overlap that kernel's tail. From here on the
     // lengths, the block table, Q and the pool are read.
-    GridDependencyWait();
+    if (p.stable_tables == 0) GridDependencyWait();
     // This CTA's run of the flat tile list (see CostCut): totals first, then the tile at which the run
     // starts and the tile at which the next CTA's run starts.
     // Per-lane and per-chunk quantities are 32-bit (a sequence has at most 2^25 tiles, a chunk of 32 at most
@@ -465,13 +466,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       misc->start_tile = start_tile;
       misc->n_tiles = static_cast<int>(hi - lo);
       if (hi > lo && start_seq < p.batch) {
-        issue_q(start_seq);
         const int begin = p.kv_begin ? p.kv_begin[start_seq] : 0;
         // A tile that a fused append still has to write into is left to the main loop.
         const int t_end = min(start_seq_tiles - (p.new_latent != nullptr ? 1 : 0), start_tile + static_cast<int>(hi - lo));
-        for (int t = start_tile; t < t_end && pre_issued < kStages; ++t, ++pre_issued) {
-          issue_tile(tile_row(start_seq, begin, t), pre_issued);
-        }
+        static_assert(kStages == 2, "the first tiles' rows are looked up before the dependency wait, two of them");
+        const int n_first = max(0, min(kStages, t_end - start_tile));
+        const int64_t row0 = n_first > 0 ? tile_row(start_seq, begin, start_tile) : 0;
+        const int64_t row1 = n_first > 1 ? tile_row(start_seq, begin, start_tile + 1) : 0;
+        if (p.stable_tables != 0) GridDependencyWait();  // Q and the pool are the preceding kernels' to write
+        issue_q(start_seq);
+        if (n_first > 0) issue_tile(row0, 0);
+        if (n_first > 1) issue_tile(row1, 1);
+        pre_issued = n_first;
+      } else if (p.stable_tables != 0) {
+        GridDependencyWait();
       }
     }
     __syncwarp();
@@ -1299,6 +1307,7 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.kv_len = a.kv_len;
   p.kv_begin = a.kv_begin;
   p.pool_rows = a.pool.pool_rows;
+  p.stable_tables = (a.flags & B200KV_DECODE_STABLE_TABLES) != 0 ? 1 : 0;
   p.new_latent = static_cast<const char*>(a.new_latent);
   p.new_rope = static_cast<const char*>(a.new_rope);
   p.new_latent_bytes = a.new_latent_stride * 2;

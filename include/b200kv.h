@@ -141,7 +141,16 @@ typedef struct b200kv_decode_args {
   int64_t new_latent_stride;
   const void* new_rope;
   int64_t new_rope_stride;
+  /*
+   * B200KV_DECODE_STABLE_TABLES: block_table, kv_len and kv_begin were not written by the kernel that precedes
+   * this call on the stream (the engine uploads them once per step, before the first layer:
+   * src/pipeline/pipeline.cpp:515-519). The decode kernel is launched so that it may start while that kernel
+   * drains; with this flag it finds its slice of the work and the rows of its first tiles before it waits for
+   * that kernel, and only then reads Q, the new rows and the pool. Without it everything is read after the wait.
+   */
+  uint32_t flags;
 } b200kv_decode_args;
+#define B200KV_DECODE_STABLE_TABLES 1u
 
 size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas);
 int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* stream, b200kv_status_word* status);

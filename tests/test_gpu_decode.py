@@ -329,3 +329,36 @@ def test_append_fused_is_refused_where_it_cannot_run():
         b200kv.mla_decode(q, b200kv.pool_view(pool), to_dev_i32(table), to_dev_i32(kv_len), bs, 1 / 24, out=out,
                           workspace=ws, variant=b200kv.DECODE_TCGEN05, kv_begin=to_dev_i32(np.zeros(1)),
                           new_rows=(rows[:, :512], rows[:, 512:]))
+
+
+def test_stable_tables_flag_changes_nothing_but_the_order_of_reads():
+    """With B200KV_DECODE_STABLE_TABLES the kernel looks up its slice and first rows before it waits for the
+    preceding kernel; behind a kernel that writes Q (as the projection before attention does) the results are
+    the same, bit for bit."""
+    from gpu_util import from_dev_bf16, status_ok, to_dev_bf16, to_dev_i32
+
+    bs = 64
+    kv_len = scenarios.ragged_lengths(9, 1, 3000)
+    blocks = int(sum(scenarios.blocks_for(int(n), bs) for n in kv_len)) + 3
+    table = scenarios.fragmented_tables(kv_len, bs, blocks)
+    pool = to_dev_bf16(kvo.make_pool(blocks * bs))
+    q_src = to_dev_bf16(kvo.make_q(len(kv_len), scale=2.0 / 24.0))
+    tbl, lens = to_dev_i32(table), to_dev_i32(kv_len)
+    ws = torch.empty(b200kv.decode_workspace_bytes(len(kv_len), 64, 0), dtype=torch.uint8, device="cuda")
+    status = b200kv.new_status()
+    results = []
+    for stable in (False, True):
+        q = torch.zeros_like(q_src)
+        out = torch.full((len(kv_len), 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+        lse = torch.full((len(kv_len), 64), float("nan"), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        q.copy_(q_src)  # a kernel on the same stream writes Q just before the launch
+        b200kv.mla_decode(q, b200kv.pool_view(pool), tbl, lens, bs, 1.0 / 24.0, out=out, lse=lse, workspace=ws,
+                          variant=b200kv.DECODE_TCGEN05, status=status, stable_tables=stable)
+        status_ok(status)
+        results.append((from_dev_bf16(out), lse.cpu().numpy()))
+    assert np.array_equal(results[0][0], results[1][0])
+    assert np.array_equal(results[0][1], results[1][1])
+    ref_out, ref_lse = scenarios.ref_attention_f64(kvo.make_q(len(kv_len), scale=2.0 / 24.0), kvo.make_pool(blocks * bs),
+                                                   table, kv_len, bs, 1.0 / 24.0)
+    scenarios.check_attention(results[1][0], results[1][1], ref_out, ref_lse, what="stable tables")
