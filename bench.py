@@ -38,7 +38,7 @@ METRIC = "decode attn tokens/s/GPU at B=32x4K ctx (43 layers: KV append + paged 
 
 ATTN_BYTES_PER_LAUNCH = BATCH * CONTEXT * ROW * 2 + BATCH * HEADS * ROW * 2 + BATCH * HEADS * LATENT * 2
 # DRAM bytes of one decode launch from the committed ncu capture (dram__bytes_read.sum + dram__bytes_write.sum).
-NCU_DRAM_BYTES_PER_LAUNCH = 153_840_000 + 5_730_000
+NCU_DRAM_BYTES_PER_LAUNCH = 153_830_000 + 4_910_000
 ATTN_FLOPS_PER_LAUNCH = BATCH * CONTEXT * HEADS * (ROW + LATENT) * 2
 
 
@@ -629,8 +629,8 @@ def run_b200_arm(args):
                          "frac": achieved / hbm_peak, "peak_kind": peak_kind,
                          "traffic": NCU_DRAM_BYTES_PER_LAUNCH if args.variant != "simt" else None,
                          "traffic_source": "ncu capture of MlaDecodeTcKernel at this workload's shape "
-                                           "(profiles/mla_decode_tc_b32x4k_2layers.md): DRAM read 153.84 MB "
-                                           "+ write 5.73 MB per launch",
+                                           "(profiles/mla_decode_tc_b32x4k_2layers.md): DRAM read 153.83 MB "
+                                           "+ write 4.91 MB per launch",
                          "algorithmic_bytes_per_launch": ATTN_BYTES_PER_LAUNCH, "us_per_launch": attn_ms * 1e3,
                          "tflops": ATTN_FLOPS_PER_LAUNCH / (attn_ms * 1e-3) * 1e-12,
                          "frac_of_measured_bf16_peak": ATTN_FLOPS_PER_LAUNCH / (attn_ms * 1e-3) * 1e-12 / tflops_peak},
