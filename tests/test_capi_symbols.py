@@ -46,3 +46,25 @@ def test_host_side_argument_refusals():
     rc = b200kv.lib.b200kv_append(ctypes.byref(view), 0x3000, 512, 0x4000, 64, 0x5000, 1, None, None)
     assert rc == b200kv.ERR_INVALID and "multiples of 8" in b200kv.last_error()
     assert b200kv.lib.b200kv_mla_decode(None, None, None) == b200kv.ERR_NULLPTR
+
+
+def test_ctypes_structures_match_the_header_layout(tmp_path):
+    """The binding's ctypes structures and include/b200kv.h describe the same bytes: a C program compiled
+    against the header prints each struct's size and the offset of its last field."""
+    import subprocess
+
+    import b200kv
+
+    cases = [("b200kv_pool_view", "pool_rows", b200kv.PoolView), ("b200kv_decode_args", "flags", b200kv.DecodeArgs),
+             ("b200kv_producer_args", "rstd_out", b200kv.ProducerArgs)]
+    lines = "".join(f'  printf("%zu %zu\\n", sizeof({c}), offsetof({c}, {f}));\n' for c, f, _ in cases)
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stddef.h>\n#include <stdio.h>\n#include "b200kv.h"\nint main(void) {\n' + lines +
+                   "  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c11", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    for (c_name, field, py), line in zip(cases, out):
+        size, last = (int(x) for x in line.split())
+        assert ctypes.sizeof(py) == size, c_name
+        assert getattr(py, field).offset == last, (c_name, field)
