@@ -288,7 +288,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto bar = [&](const uint64_t* b) { return ptx::SmemAddr(b); };
 
   // ---- setup ----------------------------------------------------------------------------------
-  GridDependencyTrigger();  // the finalize kernel may be scheduled as SMs free up
+  // The finalize kernel may be scheduled as SMs free up. It reads the lengths before it waits for this kernel, so
+  // unless the caller vouches for them (B200KV_DECODE_STABLE_TABLES) it is let go only once this kernel's own
+  // wait for the preceding kernel has returned (below).
+  if (p.stable_tables != 0) GridDependencyTrigger();
   if (threadIdx.x == 0) TRACE(63, 0);
 
   // One tile's nine TMA loads (eight latent slabs, one rope slab) into stage g % kStages.
@@ -489,6 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::TmemRelinquish();
   }
   GridDependencyWait();  // every thread, before it reads anything of the caller's
+  if (p.stable_tables == 0) GridDependencyTrigger();
   ptx::TcFenceBeforeSync();
   __syncthreads();
   ptx::TcFenceAfterSync();
