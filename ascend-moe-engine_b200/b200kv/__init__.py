@@ -11,8 +11,7 @@ import os
 from ctypes import POINTER, Structure, c_char_p, c_double, c_float, c_int32, c_int64, c_size_t, c_uint64, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# B200KV_LIB points at an alternative build of the same library (instrumented builds).
-LIB_PATH = os.environ.get("B200KV_LIB") or os.path.join(_HERE, "libb200kv.so")
+LIB_PATH = os.path.join(_HERE, "libb200kv.so")
 
 LATENT_DIM = 512
 ROPE_DIM = 64

@@ -34,7 +34,11 @@ extern "C" aclTensor* aclCreateTensor(const int64_t* view_dims, uint64_t view_di
     t->strides.assign(view_dims_num, 1);
     for (int64_t i = static_cast<int64_t>(view_dims_num) - 2; i >= 0; --i) t->strides[i] = t->strides[i + 1] * t->dims[i + 1];
   }
-  if (storage_dims != nullptr) t->storage_dims.assign(storage_dims, storage_dims + storage_dims_num);
+  if (storage_dims != nullptr) {
+    t->storage_dims.assign(storage_dims, storage_dims + storage_dims_num);
+  } else {
+    t->storage_dims = t->dims;  // a tensor described without a storage shape is dense over its view
+  }
   t->offset = storage_offset;
   t->dtype = dtype;
   t->format = format;
@@ -45,23 +49,29 @@ extern "C" aclnnStatus aclDestroyTensor(const aclTensor* tensor) {
   delete tensor;
   return 0;
 }
+// The three shape getters hand the caller a copy it owns and releases with delete[]: the reference wraps each
+// result in std::unique_ptr<int64_t[]> (src/memory/static_arena.cpp:181-188, src/core/matmul_contract.cpp:16-23).
+namespace {
+aclnnStatus CopyOut(const std::vector<int64_t>& values, int64_t** out, uint64_t* count) {
+  int64_t* copy = new (std::nothrow) int64_t[values.size() > 0 ? values.size() : 1];
+  if (copy == nullptr) return kErrNull;
+  if (!values.empty()) std::memcpy(copy, values.data(), values.size() * sizeof(int64_t));
+  *out = copy;
+  *count = values.size();
+  return 0;
+}
+}  // namespace
 extern "C" aclnnStatus aclGetViewShape(const aclTensor* t, int64_t** dims, uint64_t* count) {
   if (t == nullptr || dims == nullptr || count == nullptr) return kErrNull;
-  *dims = const_cast<int64_t*>(t->dims.data());
-  *count = t->dims.size();
-  return 0;
+  return CopyOut(t->dims, dims, count);
 }
 extern "C" aclnnStatus aclGetStorageShape(const aclTensor* t, int64_t** dims, uint64_t* count) {
   if (t == nullptr || dims == nullptr || count == nullptr) return kErrNull;
-  *dims = const_cast<int64_t*>(t->storage_dims.data());
-  *count = t->storage_dims.size();
-  return 0;
+  return CopyOut(t->storage_dims, dims, count);
 }
 extern "C" aclnnStatus aclGetViewStrides(const aclTensor* t, int64_t** strides, uint64_t* count) {
   if (t == nullptr || strides == nullptr || count == nullptr) return kErrNull;
-  *strides = const_cast<int64_t*>(t->strides.data());
-  *count = t->strides.size();
-  return 0;
+  return CopyOut(t->strides, strides, count);
 }
 extern "C" aclnnStatus aclGetDataType(const aclTensor* t, aclDataType* dtype) {
   if (t == nullptr || dtype == nullptr) return kErrNull;

@@ -70,6 +70,33 @@ __global__ void FillNormalKernel(__nv_bfloat16* dst, int64_t count, unsigned lon
 }  // namespace
 }  // namespace b200kv
 
+namespace b200kv {
+
+// The argument refusals every decode entry point shares (pointers, sizes, strides, variant).
+int32_t ValidateDecodeArgs(const b200kv_decode_args& a, const char* who) {
+  if (int32_t rc = ValidatePoolView(&a.pool)) return rc;
+  if (a.batch == 0) return B200KV_OK;
+  const bool want_partial = a.partial_o != nullptr || a.partial_m != nullptr || a.partial_l != nullptr;
+  if (a.q == nullptr || a.block_table == nullptr || a.kv_len == nullptr ||
+      (want_partial && (a.partial_o == nullptr || a.partial_m == nullptr || a.partial_l == nullptr)) ||
+      (!want_partial && a.out == nullptr)) {
+    SetLastError("%s: q, block_table, kv_len and either out or all three partial_* buffers must be non-null", who);
+    return B200KV_ERR_NULLPTR;
+  }
+  if (a.batch < 0 || a.heads <= 0 || a.block_size <= 0 || a.max_blocks <= 0 || a.pool.pool_rows % a.block_size != 0 ||
+      !(a.scale > 0.0f) || a.q_head_stride < B200KV_LATENT_DIM + B200KV_ROPE_DIM || a.q_head_stride % 2 != 0 ||
+      a.q_seq_stride % 2 != 0 || (a.batch > 1 && a.q_seq_stride < 0) || (reinterpret_cast<uintptr_t>(a.q) & 3u) != 0 ||
+      (a.variant != B200KV_DECODE_AUTO && a.variant != B200KV_DECODE_SIMT && a.variant != B200KV_DECODE_TCGEN05)) {
+    SetLastError("%s refused: batch %d heads %d block_size %d max_blocks %lld scale %g q strides %lld/%lld variant %d",
+                 who, a.batch, a.heads, a.block_size, static_cast<long long>(a.max_blocks), static_cast<double>(a.scale),
+                 static_cast<long long>(a.q_seq_stride), static_cast<long long>(a.q_head_stride), a.variant);
+    return B200KV_ERR_INVALID;
+  }
+  return B200KV_OK;
+}
+
+}  // namespace b200kv
+
 using namespace b200kv;
 
 extern "C" const char* b200kv_last_error(void) { return g_error; }
@@ -91,24 +118,8 @@ extern "C" int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* strea
     return B200KV_ERR_NULLPTR;
   }
   const b200kv_decode_args& a = *args;
-  if (int32_t rc = ValidatePoolView(&a.pool)) return rc;
+  if (int32_t rc = ValidateDecodeArgs(a, "decode")) return rc;
   if (a.batch == 0) return B200KV_OK;
-  const bool want_partial = a.partial_o != nullptr || a.partial_m != nullptr || a.partial_l != nullptr;
-  if (a.q == nullptr || a.block_table == nullptr || a.kv_len == nullptr ||
-      (want_partial && (a.partial_o == nullptr || a.partial_m == nullptr || a.partial_l == nullptr)) ||
-      (!want_partial && a.out == nullptr)) {
-    SetLastError("decode: q, block_table, kv_len and either out or all three partial_* buffers must be non-null");
-    return B200KV_ERR_NULLPTR;
-  }
-  if (a.batch < 0 || a.heads <= 0 || a.block_size <= 0 || a.max_blocks <= 0 || a.pool.pool_rows % a.block_size != 0 ||
-      !(a.scale > 0.0f) || a.q_head_stride < B200KV_LATENT_DIM + B200KV_ROPE_DIM || a.q_head_stride % 2 != 0 ||
-      a.q_seq_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(a.q) & 3u) != 0 ||
-      (a.variant != B200KV_DECODE_AUTO && a.variant != B200KV_DECODE_SIMT && a.variant != B200KV_DECODE_TCGEN05)) {
-    SetLastError("decode refused: batch %d heads %d block_size %d max_blocks %lld scale %g q strides %lld/%lld variant %d",
-                 a.batch, a.heads, a.block_size, static_cast<long long>(a.max_blocks), static_cast<double>(a.scale),
-                 static_cast<long long>(a.q_seq_stride), static_cast<long long>(a.q_head_stride), a.variant);
-    return B200KV_ERR_INVALID;
-  }
   const bool tc_ok = TcSupports(a);
   if (a.variant == B200KV_DECODE_TCGEN05 && !tc_ok) {
     SetLastError("decode: the tcgen05 kernel needs 64 heads, block_size %% 64 == 0, 16-byte aligned q with strides "

@@ -193,7 +193,9 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 4)
         }
         const int64_t j = row - out_row_offsets[lo];
         if (j >= 0 && j < kv_len[lo]) {
-          const int64_t block = block_table[static_cast<int64_t>(lo) * max_blocks + j / block_size];
+          // The lengths live on the device, so only the kernel can see a length that runs past the table's row.
+          const int64_t column = j / block_size;
+          const int64_t block = column < max_blocks ? block_table[static_cast<int64_t>(lo) * max_blocks + column] : -1;
           const int64_t src_row = block * block_size + j % block_size;
           if (block < 0 || src_row >= pool.pool_rows) {
             RecordError(status, B200KV_DEV_BAD_BLOCK, lo, static_cast<int32_t>(j / block_size),

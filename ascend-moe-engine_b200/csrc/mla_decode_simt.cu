@@ -102,7 +102,10 @@ __global__ void __launch_bounds__(kThreads, 1) MlaDecodeSimtKernel(SimtParams p)
       int4 v = make_int4(0, 0, 0, 0);
       if (j < valid) {
         const int tok = begin + tok0 + j;
-        const int64_t block = p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
+        // A length beyond the table's row (the lengths are device data) must not index past it.
+        const int64_t column = tok / p.block_size;
+        const int64_t block =
+            (tok >= 0 && column < p.max_blocks) ? p.block_table[static_cast<int64_t>(b) * p.max_blocks + column] : -1;
         const int64_t row = block * p.block_size + tok % p.block_size;
         if (block < 0 || row >= p.pool.pool_rows) {
           RecordError(p.status, B200KV_DEV_BAD_BLOCK, b, tok / p.block_size, static_cast<int32_t>(block));

@@ -27,7 +27,6 @@
 // word, raises a CTA-wide abort flag, waits (bounded) for its own TMA loads, frees TMEM and returns.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -43,12 +42,9 @@ constexpr int kLatent = B200KV_LATENT_DIM;
 constexpr int kRope = B200KV_ROPE_DIM;
 constexpr int kTile = 64;      // tokens per tile / KV stage
 constexpr int kStages = 2;
-#ifndef B200KV_PF
-#define B200KV_PF 1
-#endif
 // Tiles on their way into L2 ahead of the one being loaded. One is the best measured (a 43-layer step of
 // 32 x 4096 tokens: none 2.25 ms, one 2.07, two 2.17, three 2.20), with or without L2 eviction hints.
-constexpr int kPrefetchAhead = B200KV_PF;
+constexpr int kPrefetchAhead = 1;
 constexpr int kGroups = 4;                              // slab groups of a stage: slabs 2c, 2c+1 (and 8 with the last)
 constexpr int kSlabBytes = kTile * 128;                 // one 64-column slab of a tile: kTile rows x 128 B
 constexpr int kStageBytes = 9 * kSlabBytes;             // 73,728
@@ -133,14 +129,7 @@ struct TcParams {
   float* ws_m;  // [G*2][64]
   float* ws_l;
   int32_t* status;
-  long long* trace;  // debug builds only: [cta][tile][8] clock64 stamps, or null
 };
-
-#ifdef B200KV_TRACE
-#define TRACE(tile, slot) do { if (p.trace != nullptr && (tile) < 64) p.trace[(static_cast<long long>(blockIdx.x) * 64 + (tile)) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(tile, slot) do { } while (0)
-#endif
 
 __device__ __forceinline__ int TilesOf(int len) { return (len + kTile - 1) / kTile; }
 
@@ -292,14 +281,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   // unless the caller vouches for them (B200KV_DECODE_STABLE_TABLES) it is let go only once this kernel's own
   // wait for the preceding kernel has returned (below).
   if (p.stable_tables != 0) GridDependencyTrigger();
-  if (threadIdx.x == 0) TRACE(63, 0);
 
   // One tile's nine TMA loads (eight latent slabs, one rope slab) into stage g % kStages.
   // A prefetched tile should stay in L2 until its load (one or two tile periods later), and is dead after it.
   const uint64_t keep_policy = ptx::L2PolicyEvictLast();
   const uint64_t drop_policy = ptx::L2PolicyEvictFirst();
-  // Pool row at which tile t of a sequence starts, through the block table.
-  auto tile_row = [&](int seq, int begin, int t) -> int64_t {
+  // Pool row at which tile t of a sequence starts, through the block table; -1 (after recording it) when the
+  // table entry is missing or points outside the pool.
+  auto tile_row_checked = [&](int seq, int begin, int t) -> int64_t {
     const int tok = begin + t * kTile;
     const int64_t table_col = tok / p.block_size;
     const int64_t block =
@@ -307,9 +296,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     int64_t row = block * p.block_size + tok % p.block_size;
     if (block < 0 || row + kTile > p.pool_rows) {
       RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, tok / p.block_size, static_cast<int32_t>(block));
-      row = 0;  // keep the pipeline moving on addressable memory; the status word tells the host
+      row = -1;
     }
     return row;
+  };
+  // For loads: a bad entry reads row 0 instead, which keeps the pipeline moving on addressable memory (the
+  // status word tells the host that the result is void). Nothing is ever written through a bad entry.
+  auto tile_row = [&](int seq, int begin, int t) -> int64_t {
+    const int64_t row = tile_row_checked(seq, begin, t);
+    return row < 0 ? 0 : row;
   };
   // A tile that has no free stage yet is brought into L2 meanwhile: with two stages a tile's load can only
   // start when the tile two before it has been consumed, and from L2 it lands sooner than from DRAM. TMA
@@ -330,7 +325,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (c == kGroups - 1) ptx::TmaLoad2DHint(dst + 8 * kSlabBytes, &rope_map, 0, static_cast<int32_t>(row), full, drop_policy);
   };
   auto issue_tile = [&](int64_t row, int g) {
-    TRACE(g, 0);
 #pragma unroll
     for (int c = 0; c < kGroups; ++c) issue_group(row, g, c);
   };
@@ -346,6 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // appends.
   auto new_row_store = [&](int64_t row, uint32_t parity) -> bool {
     if (!BoundedWait(bar(&misc->new_row_full), parity, misc, p.status, 12)) return false;
+    if (row < 0) return true;  // bad table entry: the fetched row is consumed (parities stay in step), not stored
     const int4* src = reinterpret_cast<const int4*>(misc->new_row);
     int4* latent_dst = reinterpret_cast<int4*>(p.pool_latent + row * p.pool_latent_bytes);
     int4* rope_dst = reinterpret_cast<int4*>(p.pool_rope + row * p.pool_rope_bytes);
@@ -497,7 +492,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::TcFenceAfterSync();
 
-  if (threadIdx.x == 0) TRACE(63, 1);
   const uint32_t tmem = misc->tmem_base;
   const int start_seq = misc->start_seq;
   const int start_tile = misc->start_tile;
@@ -531,9 +525,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         int ahead = t_lo;  // next tile of this segment to bring into L2
         for (int t = t_lo; t < t_hi; ++t, ++g) {
           if (g < pre_issued) continue;
-          const int64_t row = tile_row(seq, begin, t);
+          const int64_t checked_row = tile_row_checked(seq, begin, t);
+          const int64_t row = checked_row < 0 ? 0 : checked_row;
           if (appends && t == seq_tiles - 1) {
-            ok = new_row_store(row + (seq_len - 1 - t * kTile), n_appended & 1);
+            ok = new_row_store(checked_row < 0 ? -1 : checked_row + (seq_len - 1 - t * kTile), n_appended & 1);
             if (!ok) break;
             ++n_appended;
             fetch_pending = false;
@@ -543,7 +538,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (; ahead < t_hi && ahead < t + kPrefetchAhead; ++ahead) {
               prefetch_tile(ahead == t ? row : tile_row(seq, begin, ahead));
             }
-            TRACE(g, 0);
             for (int c = 0; c < kGroups && ok; ++c) {
               ok = BoundedSpin(bar(&misc->kv_empty[g % kStages][c]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
               if (ok) issue_group(row, g, c);
@@ -624,7 +618,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if (!ok) break;
             ptx::TcFenceAfterSync();
-            TRACE(g, 1);
             const uint64_t kdesc = DescAt(k_desc0, stage * kStageBytes);
             const uint32_t d = tmem_u + kTmemColS + kTile * buf;
             // Twelve k-steps per slab group, each group as soon as its slabs have landed (compile-time
@@ -646,7 +639,6 @@ __global__ void __launch_bounds__(kThreads, 1)
               ptx::TcCommit(bar(&misc->s_full[buf]));
               if (i == n - 1) ptx::TcCommit(bar(&misc->q_empty));  // Q buffer free for the next segment
             }
-            TRACE(g, 2);
           }
         } else {
           if (seg > 0) {
@@ -660,7 +652,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                             BoundedWait(bar(&misc->p_full[stage]), (g / kStages) & 1, misc, p.status, 21));
             if (!ok) break;
             ptx::TcFenceAfterSync();
-            TRACE(g, 5);
             const uint32_t stage_off = stage * kStageBytes;
             const uint64_t pdesc = DescAt(k_desc0, stage_off + 8 * kSlabBytes);  // K-major: row = head, 32 B per k-step
             const uint64_t vdesc = DescAt(v_desc0, stage_off);
@@ -676,7 +667,6 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
               if (ptx::ElectOne()) ptx::TcCommit(bar(&misc->kv_empty[stage][tm]));
             }
-            TRACE(g, 6);
           }
           if (ok && ptx::ElectOne()) ptx::TcCommit(bar(&misc->o_full));
         }
@@ -724,7 +714,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = BoundedWait(bar(&misc->s_full[buf]), (g >> 1) & 1, misc, p.status, 30);
         if (!ok) break;
         ptx::TcFenceAfterSync();
-        if (tid == 0) TRACE(g, 3);
         static_assert(kTile == 64, "one 16x256b.x8 load covers the 64 columns of a tile");
         uint32_t sr[32];
         ptx::TmemLd16x256bX8(tmem + lane_base + kTmemColS + kTile * buf, sr);
@@ -849,7 +838,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         ptx::FenceProxyAsyncShared();
         if (any_rescale) ptx::NamedBarrier(2, kSoftmaxThreads);  // factors are read before the next tile rewrites them
-        if (tid == 0) TRACE(g, 4);
         __syncwarp();
         if (lane == 0) ptx::MbarArrive(bar(&misc->p_full[stage]));
       }
@@ -859,7 +847,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = BoundedWait(bar(&misc->o_full), seg & 1, misc, p.status, 32);
       if (!ok) break;
       ptx::TcFenceAfterSync();
-      if (tid == 0) TRACE(63, 2 + 2 * (seg & 1));
       const bool whole = (t_lo == 0 && t_hi == seq_tiles);
       const bool to_user_partial = whole && p.user_o != nullptr;
       const bool to_ws = !whole;
@@ -911,7 +898,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::TcFenceBeforeSync();
       __syncwarp();
       if (lane == 0) ptx::MbarArrive(bar(&misc->o_empty));
-      if (tid == 0) TRACE(63, 3 + 2 * (seg & 1));
       first_segment_of_cta = false;
       ++seg;
     }
@@ -920,7 +906,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ---- teardown ---------------------------------------------------------------------------------
   ptx::TcFenceBeforeSync();
   __syncthreads();
-  if (threadIdx.x == 0) TRACE(63, 6);
   if (warp == 5) {
     ptx::TcFenceAfterSync();
     ptx::TmemDealloc(tmem, kTmemCols);
@@ -1213,10 +1198,30 @@ int32_t GetRowMap(const void* base, int64_t stride, int64_t rows, int32_t width,
 
 // Query view [batch][64 heads][576] bf16 with element strides (q_seq_stride, q_head_stride, 1);
 // box = 64 columns x 64 heads of one sequence, 128-byte swizzle.
+struct QKey {
+  const void* base;
+  int64_t head_stride;
+  int64_t seq_stride;  // the effective one: a batch of one has none of its own
+  int32_t batch;
+  bool operator==(const QKey& o) const {
+    return base == o.base && head_stride == o.head_stride && seq_stride == o.seq_stride && batch == o.batch;
+  }
+};
+struct QKeyHash {
+  size_t operator()(const QKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h ^= static_cast<size_t>(k.head_stride) * 0x9E3779B97F4A7C15ull;
+    h ^= static_cast<size_t>(k.seq_stride) * 0xC2B2AE3D27D4EB4Full;
+    return h ^ (static_cast<size_t>(k.batch) * 0x165667B19E3779F9ull);
+  }
+};
+
 int32_t GetQMap(const void* base, int64_t head_stride, int64_t seq_stride, int32_t batch, CUtensorMap* out) {
   static std::mutex mu;
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{base, head_stride * 131 + seq_stride, batch, -1};
+  static std::unordered_map<QKey, CUtensorMap, QKeyHash> cache;
+  // A batch of one has no meaningful sequence stride; any multiple of 16 bytes that covers a sequence will do.
+  const int64_t seq_stride_eff = batch > 1 ? seq_stride : static_cast<int64_t>(kHeads) * head_stride;
+  const QKey key{base, head_stride, seq_stride_eff, batch};
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
@@ -1230,8 +1235,6 @@ int32_t GetQMap(const void* base, int64_t head_stride, int64_t seq_stride, int32
     SetLastError("cuTensorMapEncodeTiled could not be resolved from the CUDA driver");
     return B200KV_ERR_RUNTIME;
   }
-  // A batch of one has no meaningful sequence stride; any multiple of 16 bytes that covers a sequence will do.
-  const int64_t seq_stride_eff = batch > 1 ? seq_stride : static_cast<int64_t>(kHeads) * head_stride;
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kLatent + kRope), kHeads, static_cast<cuuint64_t>(batch)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_stride) * 2, static_cast<cuuint64_t>(seq_stride_eff) * 2};
   const cuuint32_t box[3] = {64, kHeads, 1};
@@ -1256,8 +1259,6 @@ int32_t GetQMap(const void* base, int64_t head_stride, int64_t seq_stride, int32
 }
 
 }  // namespace
-
-long long* g_trace = nullptr;  // set by the debug hook below; null in normal use
 
 size_t TcWorkspaceBytes(int32_t n_ctas) {
   return static_cast<size_t>(n_ctas) * 2 * kHeads * (kLatent + 2) * sizeof(float);
@@ -1335,16 +1336,12 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.ws_m = ws + slots * kHeads * kLatent;
   p.ws_l = p.ws_m + slots * kHeads;
   p.status = status;
-  p.trace = g_trace;
 
   if (int32_t rc = CheckCuda(LaunchOverlapped(MlaDecodeTcKernel, dim3(n_ctas), dim3(kThreads), kSmemBytes, stream,
                                               latent_map, rope_map, q_map, p),
                              "tcgen05 decode launch")) {
     return rc;
   }
-#ifdef B200KV_TRACE
-  if (getenv("B200KV_SKIP_FINALIZE") != nullptr) return B200KV_OK;  // instrumented builds only: timing breakdown
-#endif
   const int64_t rows = static_cast<int64_t>(a.batch) * kHeads;
   // Few rows (a handful of long sequences): four or sixteen warps per row, so that the merge still fills the GPU.
   if (rows < 256) {
@@ -1366,7 +1363,3 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
 }
 
 }  // namespace b200kv
-
-// Debug hook (not declared in the public header): device buffer of [ctas][64][8] clock64 stamps that a
-// library built with -DB200KV_TRACE fills per tile.
-extern "C" void b200kv_debug_set_trace(long long* device_buffer) { b200kv::g_trace = device_buffer; }

@@ -7,9 +7,12 @@
 // this variant carries its own, a fixed array in the library's device image, so the caller passes only
 // inputs and outputs. The array is part of the loaded module: every GPU that loads the library holds
 // kStaticScratchBytes of it until the process exits.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b200kv {
+int32_t ValidateDecodeArgs(const b200kv_decode_args& a, const char* who);
 bool TcSupports(const b200kv_decode_args& a);
 size_t TcWorkspaceBytes(int32_t n_ctas);
 int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status);
@@ -28,7 +31,7 @@ constexpr size_t kStaticScratchBytes = static_cast<size_t>(kStaticMaxCtas) * 2 *
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_address[kMaxDevices] = {};  // per device, filled by the first call on that device
+std::atomic<void*> g_scratch_address[kMaxDevices];  // per device, filled by the first call on that device
 
 // Resolves the array's device address for the current device (once per device).
 int32_t ScratchForCurrentDevice(void** out) {
@@ -38,14 +41,15 @@ int32_t ScratchForCurrentDevice(void** out) {
     SetLastError("mla_decode_static: device ordinal %d outside [0, %d)", device, kMaxDevices);
     return B200KV_ERR_INVALID;
   }
-  if (g_scratch_address[device] == nullptr) {
-    void* ptr = nullptr;
+  void* ptr = g_scratch_address[device].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    // Threads that get here together each look the address up and store the same value.
     if (int32_t rc = CheckCuda(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)")) {
       return rc;
     }
-    g_scratch_address[device] = ptr;
+    g_scratch_address[device].store(ptr, std::memory_order_release);
   }
-  *out = g_scratch_address[device];
+  *out = ptr;
   return B200KV_OK;
 }
 
@@ -60,17 +64,11 @@ extern "C" int32_t b200kv_mla_decode_static(const b200kv_decode_args* args, void
     return B200KV_ERR_NULLPTR;
   }
   b200kv_decode_args a = *args;
-  if (int32_t rc = ValidatePoolView(&a.pool)) return rc;
+  a.variant = B200KV_DECODE_TCGEN05;  // the caller's choice is ignored: only the tensor-core kernel runs here
+  // The same refusals as b200kv_mla_decode, then the tensor-core kernel's own geometry.
+  if (int32_t rc = ValidateDecodeArgs(a, "mla_decode_static")) return rc;
   if (a.batch == 0) return B200KV_OK;
-  const bool want_partial = a.partial_o != nullptr || a.partial_m != nullptr || a.partial_l != nullptr;
-  if (a.q == nullptr || a.block_table == nullptr || a.kv_len == nullptr ||
-      (want_partial && (a.partial_o == nullptr || a.partial_m == nullptr || a.partial_l == nullptr)) ||
-      (!want_partial && a.out == nullptr)) {
-    SetLastError("mla_decode_static: q, block_table, kv_len and either out or all three partial_* must be non-null");
-    return B200KV_ERR_NULLPTR;
-  }
-  if (a.batch < 0 || a.block_size <= 0 || a.max_blocks <= 0 || a.pool.pool_rows % a.block_size != 0 ||
-      !(a.scale > 0.0f) || !TcSupports(a)) {
+  if (!TcSupports(a)) {
     SetLastError("mla_decode_static refused: it runs the tensor-core kernel only (64 heads, block_size %% 64 == 0, "
                  "16-byte aligned q with strides that are multiples of 8 elements); batch %d heads %d block_size %d",
                  a.batch, a.heads, a.block_size);
@@ -87,7 +85,6 @@ extern "C" int32_t b200kv_mla_decode_static(const b200kv_decode_args* args, void
   if (int32_t rc = ScratchForCurrentDevice(&scratch)) return rc;
   a.workspace = scratch;
   a.workspace_bytes = kStaticScratchBytes;
-  a.variant = B200KV_DECODE_TCGEN05;
   // Nothing in the scratch has to start at zero: every partial slot a launch reads was written by the
   // same launch's decode kernel first.
   return LaunchMlaDecodeTc(a, ctas, static_cast<cudaStream_t>(stream), status);

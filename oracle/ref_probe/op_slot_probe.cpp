@@ -8,7 +8,12 @@
 // (src/core/device_ops.cpp:96-262). This driver does exactly that with the reference's classes, with the
 // argument lists of stages 8 and 9 of the reference's Build (src/pipeline/pipeline.cpp:226-248) and the
 // descriptor shapes of StaticArenaManager::CreateDescriptors (src/memory/static_arena_manager.cpp:480-497,
-// 567-588), but linked against libb200kv.so instead of the vendor's operator library. The Python test
+// 567-588), but linked against libb200kv.so instead of the vendor's operator library. Memory and descriptors
+// come from the reference's StaticMemoryArena (src/memory/static_arena.cpp): the four KV spans are reserved,
+// one Commit allocates them, the descriptors and the key / value lists are made by CreateTensor /
+// CreateTensorList / CreateIntArray in CreateDescriptors' order (the list copies go through the operator
+// library's shape getters, whose results the arena owns and deletes), the workspace by NoteWorkspace /
+// CommitWorkspace, and the arena is sealed before the step. The Python test
 // writes the inputs, runs this binary on the GPU and checks its outputs against the oracle.
 //
 //   op_slot_probe <input file> <output file>
@@ -32,6 +37,7 @@
 #include "moe/core/device_ops.hpp"
 #include "moe/core/error.hpp"
 #include "moe/core/op_table.hpp"
+#include "moe/memory/static_arena.hpp"
 
 using namespace ascend_moe;
 
@@ -44,15 +50,6 @@ constexpr int32_t kInt32 = 3;   // ACL_INT32
 constexpr int32_t kFloat = 0;   // ACL_FLOAT
 // Positions of the repointed tensors in the operators' argument lists (include/moe/pipeline/pipeline.hpp:177-184).
 constexpr size_t kScatterKeyCache = 1, kScatterValueCache = 4, kFiaKeyList = 1, kFiaValueList = 2, kFiaKeyRope = 25;
-
-aclTensor* Tensor(const std::vector<int64_t>& dims, int32_t dtype, void* data) {
-  std::vector<int64_t> strides(dims.size(), 1);
-  for (int64_t i = static_cast<int64_t>(dims.size()) - 2; i >= 0; --i) strides[i] = strides[i + 1] * dims[i + 1];
-  aclTensor* t = aclCreateTensor(dims.data(), dims.size(), static_cast<aclDataType>(dtype), strides.data(), 0,
-                                 ACL_FORMAT_ND, dims.data(), dims.size(), data);
-  if (t == nullptr) throw Dsv4Error("aclCreateTensor returned null");
-  return t;
-}
 
 template <typename T>
 std::vector<T> ReadArray(std::ifstream& in, size_t count) {
@@ -79,19 +76,34 @@ int Run(const std::string& in_path, const std::string& out_path) {
   OpTable table;
   DeviceStream stream = device.CreateStream();
 
-  // Device buffers. One allocation per role, all layers of a pool contiguous (layer-major, as
-  // src/memory/static_arena_manager.cpp:315-318 lays them out).
+  // The KV spans as the reference lays them out: two layer-major caches, the block table and the slot
+  // (src/memory/static_arena_manager.cpp:298-300, 315-318), plus the step's activations, all carved from the
+  // reference's arena with ONE device allocation.
+  StaticMemoryArena arena(device);
   const size_t latent_layer = static_cast<size_t>(rows) * kLatent * 2, rope_layer = static_cast<size_t>(rows) * kRope * 2;
-  auto* latent_pool = static_cast<uint8_t*>(device.DeviceMalloc(latent_layer * layers));
-  auto* rope_pool = static_cast<uint8_t*>(device.DeviceMalloc(rope_layer * layers));
-  auto* new_latent = static_cast<uint8_t*>(device.DeviceMalloc(kLatent * 2));
-  auto* new_rope = static_cast<uint8_t*>(device.DeviceMalloc(kRope * 2));
-  auto* q_latent = static_cast<uint8_t*>(device.DeviceMalloc(static_cast<size_t>(heads) * kLatent * 2));
-  auto* q_rope = static_cast<uint8_t*>(device.DeviceMalloc(static_cast<size_t>(heads) * kRope * 2));
-  auto* attn_out = static_cast<uint8_t*>(device.DeviceMalloc(static_cast<size_t>(heads) * kLatent * 2));
-  auto* lse = static_cast<uint8_t*>(device.DeviceMalloc(static_cast<size_t>(heads) * 4));
-  auto* slot_dev = static_cast<uint8_t*>(device.DeviceMalloc(4));
-  auto* table_dev = static_cast<uint8_t*>(device.DeviceMalloc(static_cast<size_t>(blocks) * 4));
+  const ArenaHandle h_table = arena.Reserve("kv.block_table", static_cast<size_t>(blocks) * 4);
+  const ArenaHandle h_slot = arena.Reserve("kv.slot_mapping", 4);
+  const ArenaHandle h_latent = arena.Reserve("kv.latent_cache", latent_layer * layers);
+  const ArenaHandle h_rope = arena.Reserve("kv.rope_cache", rope_layer * layers);
+  const ArenaHandle h_new_latent = arena.Reserve("attn.kv_latent_normed", kLatent * 2);
+  const ArenaHandle h_new_rope = arena.Reserve("attn.k_rope", kRope * 2);
+  const ArenaHandle h_q_latent = arena.Reserve("attn.q_latent", static_cast<size_t>(heads) * kLatent * 2);
+  const ArenaHandle h_q_rope = arena.Reserve("attn.q_rope", static_cast<size_t>(heads) * kRope * 2);
+  const ArenaHandle h_out = arena.Reserve("attn.out", static_cast<size_t>(heads) * kLatent * 2);
+  const ArenaHandle h_lse = arena.Reserve("attn.lse", static_cast<size_t>(heads) * 4);
+  const uint64_t allocations_before = device.DeviceAllocationCount();
+  arena.Commit();
+  if (device.DeviceAllocationCount() != allocations_before + 1) throw Dsv4Error("Commit made more than one allocation");
+  auto* latent_pool = arena.AddressAs<uint8_t>(h_latent);
+  auto* rope_pool = arena.AddressAs<uint8_t>(h_rope);
+  auto* new_latent = arena.AddressAs<uint8_t>(h_new_latent);
+  auto* new_rope = arena.AddressAs<uint8_t>(h_new_rope);
+  auto* q_latent = arena.AddressAs<uint8_t>(h_q_latent);
+  auto* q_rope = arena.AddressAs<uint8_t>(h_q_rope);
+  auto* attn_out = arena.AddressAs<uint8_t>(h_out);
+  auto* lse = arena.AddressAs<uint8_t>(h_lse);
+  auto* slot_dev = arena.AddressAs<uint8_t>(h_slot);
+  auto* table_dev = arena.AddressAs<uint8_t>(h_table);
 
   struct LayerInput {
     std::vector<uint16_t> latent, rope, new_latent, new_rope, q_latent, q_rope;
@@ -111,27 +123,41 @@ int Run(const std::string& in_path, const std::string& out_path) {
   const std::vector<int32_t> block_table = ReadArray<int32_t>(in, static_cast<size_t>(blocks));
   device.MemcpySync(table_dev, blocks * 4, block_table.data(), blocks * 4, MemcpyKind::kHostToDevice);
 
-  // Descriptors with the reference's shapes.
-  aclTensor* t_kv_latent = Tensor({1, kLatent}, kBf16, new_latent);
-  aclTensor* t_k_rope = Tensor({1, 1, kRope}, kBf16, new_rope);
-  aclTensor* t_latent_cache = Tensor({blocks, block_size, 1, kLatent}, kBf16, latent_pool);
-  aclTensor* t_rope_cache = Tensor({blocks, block_size, 1, kRope}, kBf16, rope_pool);
-  aclTensor* t_slot = Tensor({1}, kInt32, slot_dev);
-  aclTensor* t_q_latent = Tensor({1, heads, kLatent}, kBf16, q_latent);
-  aclTensor* t_q_rope = Tensor({1, heads, kRope}, kBf16, q_rope);
-  aclTensor* t_key = Tensor({blocks, block_size, 1, kLatent}, kBf16, latent_pool);
-  aclTensor* t_value = Tensor({blocks, block_size, 1, kLatent}, kBf16, latent_pool);
-  aclTensor* t_key_rope = Tensor({blocks, block_size, 1, kRope}, kBf16, rope_pool);
-  aclTensor* t_block_table = Tensor({1, blocks}, kInt32, table_dev);
-  aclTensor* t_out = Tensor({1, heads, kLatent}, kBf16, attn_out);
-  aclTensor* t_lse = Tensor({1, heads, 1}, kFloat, lse);
-  const aclTensor* key_items[1] = {t_key};
-  const aclTensor* value_items[1] = {t_value};
-  aclTensorList* key_list = aclCreateTensorList(key_items, 1);
-  aclTensorList* value_list = aclCreateTensorList(value_items, 1);
-  const int64_t one = 1;
-  aclIntArray* seq_q = aclCreateIntArray(&one, 1);
-  aclIntArray* seq_kv = aclCreateIntArray(&context, 1);
+  // Descriptors with the reference's shapes and labels, in the order of CreateDescriptors
+  // (src/memory/static_arena_manager.cpp:480-497, 567-588).
+  aclTensor* t_q_latent = arena.CreateTensor("q_latent", {1, heads, kLatent}, kBf16, q_latent);
+  aclTensor* t_q_rope = arena.CreateTensor("q_rope", {1, heads, kRope}, kBf16, q_rope);
+  aclTensor* t_kv_latent = arena.CreateTensor("kv_latent_normed", {1, kLatent}, kBf16, new_latent);
+  aclTensor* t_k_rope = arena.CreateTensor("k_rope", {1, 1, kRope}, kBf16, new_rope);
+  aclTensor* t_out = arena.CreateTensor("attn_out", {1, heads, kLatent}, kBf16, attn_out);
+  aclTensor* t_lse = arena.CreateTensor("attn_lse", {1, heads, 1}, kFloat, lse);
+  aclTensor* t_latent_cache = arena.CreateTensor("kv_latent_cache", {blocks, block_size, 1, kLatent}, kBf16, latent_pool);
+  aclTensor* t_rope_cache = arena.CreateTensor("kv_rope_cache", {blocks, block_size, 1, kRope}, kBf16, rope_pool);
+  aclTensor* t_key_rope = arena.CreateTensor("key_rope_cache_view", {blocks, block_size, 1, kRope}, kBf16, rope_pool);
+  aclTensorList* key_list = arena.CreateTensorList("fia_key_list", {t_latent_cache});
+  aclTensorList* value_list = arena.CreateTensorList("fia_value_list", {t_latent_cache});
+  aclTensor* t_block_table = arena.CreateTensor("block_table", {1, blocks}, kInt32, table_dev);
+  aclTensor* t_slot = arena.CreateTensor("slot_mapping", {1}, kInt32, slot_dev);
+  aclIntArray* seq_q = arena.CreateIntArray("actual_seq_q", {1});
+  aclIntArray* seq_kv = arena.CreateIntArray("actual_seq_kv", {context});
+  // The getters' results belong to the caller (the arena's list copies above released theirs with delete[]);
+  // once more here, directly, for all three.
+  {
+    int64_t* raw = nullptr;
+    uint64_t n = 0;
+    if (aclGetViewShape(t_latent_cache, &raw, &n) != 0 || n != 4 || raw[0] != blocks || raw[3] != kLatent) {
+      throw Dsv4Error("aclGetViewShape disagrees with the descriptor");
+    }
+    delete[] raw;
+    if (aclGetViewStrides(t_latent_cache, &raw, &n) != 0 || n != 4 || raw[3] != 1 || raw[0] != block_size * kLatent) {
+      throw Dsv4Error("aclGetViewStrides disagrees with the descriptor");
+    }
+    delete[] raw;
+    if (aclGetStorageShape(t_latent_cache, &raw, &n) != 0 || n != 4 || raw[1] != block_size) {
+      throw Dsv4Error("aclGetStorageShape disagrees with the descriptor");
+    }
+    delete[] raw;
+  }
 
   // Plan once (stages 8 and 9 of the reference's Build), keep the executors.
   char cache_mode[] = "Norm";
@@ -149,8 +175,21 @@ int Run(const std::string& in_path, const std::string& out_path) {
       nullptr, heads, static_cast<double>(scale), int64_t{65536}, int64_t{0}, layout, int64_t{1}, int64_t{3},
       int64_t{0}, block_size, int64_t{0}, false, int64_t{0}, int64_t{0}, int64_t{0}, int64_t{0}, t_out, t_lse);
   attention.Adopt(OpId::kFusedInferAttentionScoreV5, "attention", workspace_bytes, executor);
-  const uint64_t shared_workspace = std::max<uint64_t>(scatter.workspace_size(), attention.workspace_size());
-  void* workspace = shared_workspace > 0 ? device.DeviceMalloc(shared_workspace) : nullptr;
+  // One shared workspace at the planned high-water mark, then the latch: from here on the arena refuses
+  // every reservation, descriptor and allocation (src/memory/static_arena.cpp:270-304).
+  arena.NoteWorkspace(scatter.workspace_size());
+  arena.NoteWorkspace(attention.workspace_size());
+  arena.CommitWorkspace();
+  arena.Seal();
+  void* workspace = arena.workspace();
+  bool refused = false;
+  try {
+    arena.CreateTensor("late", {1}, kInt32, slot_dev);
+  } catch (const Dsv4Error&) {
+    refused = true;
+  }
+  if (!refused) throw Dsv4Error("a sealed arena built a descriptor");
+  const uint64_t allocations_sealed = device.DeviceAllocationCount();
 
   // One decode step: the slot goes to the device once (src/pipeline/pipeline.cpp:515-519), then per layer
   // the address swaps and the two launches.
@@ -172,6 +211,8 @@ int Run(const std::string& in_path, const std::string& out_path) {
     scatter.Launch(table, workspace, stream);
     attention.Launch(table, workspace, stream);
     device.SynchronizeStream(stream);
+    // Zero allocations inside the layer loop, as the reference asserts per step (src/pipeline/pipeline.cpp:502-503).
+    if (device.DeviceAllocationCount() != allocations_sealed) throw Dsv4Error("the layer loop allocated device memory");
     outs[l].resize(static_cast<size_t>(heads) * kLatent);
     device.MemcpySync(outs[l].data(), outs[l].size() * 2, attn_out, outs[l].size() * 2, MemcpyKind::kDeviceToHost);
     rows_back[l].resize(kLatent + kRope);
@@ -192,7 +233,8 @@ int Run(const std::string& in_path, const std::string& out_path) {
   attention.Reset();
   device.DestroyStream(stream);
   std::cout << "op_slot_probe: " << layers << " layers, context " << context << ", backend " << device.backend_name()
-            << ", device allocations " << device.DeviceAllocationCount() << "\n";
+            << ", device allocations " << device.DeviceAllocationCount() << ", arena bytes " << arena.arena_bytes()
+            << ", descriptors " << arena.descriptors().size() << "\n";
   return 0;
 }
 
