@@ -1,27 +1,29 @@
 // Split-KV absorbed-MLA decode attention on tcgen05 tensor cores (sm_100a), 64 heads x (512+64).
 //
 // Work partition. A sequence of L tokens is ceil(L/64) tiles. The tiles of all sequences form one flat
-// list; CTA c of G takes the contiguous range [c*T/G, (c+1)*T/G). A CTA therefore walks a few
-// "segments" (a tile range inside one sequence). A segment that covers its whole sequence writes the
-// result directly; otherwise it writes an un-normalised partial (m, l, O) to the workspace and the
-// finalize kernel merges the parts with a log-sum-exp reduction. Only the first and the last segment
-// of a CTA can be partial, so the workspace holds two partial slots per CTA.
+// list, which is cut into G contiguous runs by cost (CostCut below: a tile costs 2, entering another sequence
+// in mid-run 3 more), one run per CTA. A CTA therefore walks a few "segments" (a tile range inside one
+// sequence). A segment that covers its whole sequence writes the result directly; otherwise it writes an
+// un-normalised partial (m, l, O) to the workspace and the finalize kernel merges the parts with a
+// log-sum-exp reduction. Only the first and the last segment of a CTA can be partial, so the workspace holds
+// two partial slots per CTA.
 //
 // Per tile of 64 tokens (one KV stage of 73,728 bytes: nine 64-column slabs, TMA-loaded, 128-byte
-// swizzled):
+// swizzled, never multicast):
 //   S[64 heads x 64 tok]  = Q[64 x 576] . K_tile^T            36 MMAs M=64  N=64 K=16 (K-major A, B)
 //   P = exp2(S*scale*log2e - m)  (softmax warps, fp32 -> bf16, written over the stage's rope slab,
 //                                 which QK has finished with)
 //   O^T[512 x 64 heads]  += V_tile^T[512 x 64] . P^T[64 x 64]  16 MMAs M=128 N=64 K=16 (MN-major A)
 // V is the first 512 columns of the same shared-memory tile that served as K: a tile is read from HBM
 // once. O^T lives in TMEM (4 accumulators of 128 lanes x 64 columns), S double-buffered beside it.
-// Measured on B200: one tcgen05.mma costs max(45, N/2) cycles whatever M is, so the tile is 64 tokens
-// (N = 64 costs the same as N = 32) and PV runs transposed to use M = 128.
+// Measured on B200: one tcgen05.mma costs max(N/2, operand bytes/128, about 32) cycles whatever M is, so
+// the tile is 64 tokens (N = 64 costs the same as N = 32) and PV runs transposed to use M = 128.
 //
-// Warp roles: warps 0-3 softmax + epilogue (TMEM lanes 32w..32w+31), warp 4 TMA producer, warp 5 MMA
-// issuer and TMEM owner. The issuer polls: PV of tile i goes out as soon as P is ready, QK of tile i+1
-// as soon as its stage has landed, whichever comes first, so the tensor pipe works on the next tile's
-// scores while the softmax warps handle this one. Shared memory holds Q (72 KB) and two KV stages.
+// Warp roles (224 threads): warps 0-3 softmax + epilogue (TMEM lanes 32w..32w+31); warp 4 TMA producer, its
+// lanes sharing out a tile's loads (one thread issues a cp.async.bulk.tensor only every 170 cycles or so);
+// warp 5 issues every QK and owns the TMEM allocation, warp 6 issues every PV: two independent instruction
+// streams into the tensor pipe. Shared memory holds Q (72 KB) and two KV stages, each filled and given back
+// in four slab groups.
 //
 // Every wait is bounded: when a wait runs out the kernel records B200KV_DEV_TIMEOUT in the status
 // word, raises a CTA-wide abort flag, waits (bounded) for its own TMA loads, frees TMEM and returns.
@@ -42,9 +44,6 @@ constexpr int kLatent = B200KV_LATENT_DIM;
 constexpr int kRope = B200KV_ROPE_DIM;
 constexpr int kTile = 64;      // tokens per tile / KV stage
 constexpr int kStages = 2;
-// Tiles on their way into L2 ahead of the one being loaded. One is the best measured (a 43-layer step of
-// 32 x 4096 tokens: none 2.25 ms, one 2.07, two 2.17, three 2.20), with or without L2 eviction hints.
-constexpr int kPrefetchAhead = 1;
 constexpr int kGroups = 4;                              // slab groups of a stage: slabs 2c, 2c+1 (and 8 with the last)
 constexpr int kSlabBytes = kTile * 128;                 // one 64-column slab of a tile: kTile rows x 128 B
 constexpr int kStageBytes = 9 * kSlabBytes;             // 73,728
@@ -121,12 +120,14 @@ struct TcParams {
   float* user_o;  // caller's partial buffers (shard mode) or null
   float* user_m;
   float* user_l;
-  // Partials, head-major: [64 heads][2G slots][512] and [64][2G]. The merge of one head reads that head's
-  // row of many slots: head-major puts them side by side (slot-major put them 2^17 bytes apart, which the L2
-  // serves badly, and made the (m, l) reads of a warp 32 separate lines).
+  // Partials, one slot per (CTA, first / later segment): [2G slots][16 head quads][512 dv][4 heads] fp32, and
+  // (m, l) as [2G][64]. A thread of the epilogue owns one dv (a TMEM lane) and reads its heads as consecutive
+  // registers: four heads make a 16-byte store, and the 32 lanes of a warp (32 consecutive dv) write 512
+  // contiguous bytes per instruction. The merge kernel reads the same lines the same way, lanes along dv,
+  // which is also the order of the output rows: nothing has to be turned round.
   float* ws_o;
   int32_t n_slots;  // 2G
-  float* ws_m;  // [G*2][64]
+  float* ws_m;  // [2G][64]
   float* ws_l;
   int32_t* status;
 };
@@ -195,11 +196,18 @@ struct CostCut {
     if (((a | b) >> 32) == 0) return static_cast<long long>(static_cast<uint32_t>(a) / static_cast<uint32_t>(b));
     return a / b;
   }
-  __device__ long long CtaOf(long long x, long long s) const { return Div((2 * x + 3 * s) * n_ctas, cost_total); }
+  static constexpr long long kTileCost = 2;   // one tile of 64 tokens
+  static constexpr long long kCrossCost = 3;  // entering another sequence in mid-run
+  __device__ static long long Pos(long long x, long long s) { return kTileCost * x + kCrossCost * s; }
+  __device__ static long long Total(long long tiles, long long nonempty) {
+    return kTileCost * tiles + kCrossCost * (nonempty > 0 ? nonempty - 1 : 0);
+  }
+  __device__ long long CtaOf(long long x, long long s) const { return Div(Pos(x, s) * n_ctas, cost_total); }
   __device__ long long FirstPos(long long c) const { return Div(c * cost_total + n_ctas - 1, n_ctas); }
   // First tile of a sequence (first tile `first`, ordinal s) at or after cost position k.
   __device__ long long FirstTileAt(long long k, long long first, long long s) const {
-    const long long x = (k - 3 * s + 1) >> 1;  // ceil((k - 3s) / 2), also right for negative values
+    static_assert(kTileCost == 2, "the ceiling below divides by the tile cost with a shift");
+    const long long x = (k - kCrossCost * s + 1) >> 1;  // ceil((k - cross * s) / 2), also right for negative values
     return x > first ? x : first;
   }
 };
@@ -283,8 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (p.stable_tables != 0) GridDependencyTrigger();
 
   // One tile's nine TMA loads (eight latent slabs, one rope slab) into stage g % kStages.
-  // A prefetched tile should stay in L2 until its load (one or two tile periods later), and is dead after it.
-  const uint64_t keep_policy = ptx::L2PolicyEvictLast();
+  // A tile is dead in L2 once it has been loaded.
   const uint64_t drop_policy = ptx::L2PolicyEvictFirst();
   // Pool row at which tile t of a sequence starts, through the block table; -1 (after recording it) when the
   // table entry is missing or points outside the pool.
@@ -306,14 +313,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int64_t row = tile_row_checked(seq, begin, t);
     return row < 0 ? 0 : row;
   };
-  // A tile that has no free stage yet is brought into L2 meanwhile: with two stages a tile's load can only
-  // start when the tile two before it has been consumed, and from L2 it lands sooner than from DRAM. TMA
-  // prefetches; plain prefetch.global.L2 instructions from the producer warp's lanes were slower than none.
-  auto prefetch_tile = [&](int64_t row) {
-#pragma unroll
-    for (int c = 0; c < 8; ++c) ptx::TmaPrefetchL2_2DHint(&latent_map, 64 * c, static_cast<int32_t>(row), keep_policy);
-    ptx::TmaPrefetchL2_2DHint(&rope_map, 0, static_cast<int32_t>(row), keep_policy);
-  };
   // Group c of a tile into stage g % kStages: slabs 2c and 2c + 1, and the rope slab with the last group.
   auto issue_group = [&](int64_t row, int g, int c) {
     const int stage = g % kStages;
@@ -324,9 +323,24 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::TmaLoad2DHint(dst + (2 * c + 1) * kSlabBytes, &latent_map, 128 * c + 64, static_cast<int32_t>(row), full, drop_policy);
     if (c == kGroups - 1) ptx::TmaLoad2DHint(dst + 8 * kSlabBytes, &rope_map, 0, static_cast<int32_t>(row), full, drop_policy);
   };
-  auto issue_tile = [&](int64_t row, int g) {
-#pragma unroll
-    for (int c = 0; c < kGroups; ++c) issue_group(row, g, c);
+  // The producer warp spreads a tile's TMA instructions over its lanes: one thread needs some 170 cycles per
+  // cp.async.bulk.tensor, so nine loads and nine prefetches issued by one thread take a whole tile period.
+  // Lane s < 9 owns slab s (its group: slabs 0-1, 2-3, 4-5, 6-8) and lanes 0, 2, 4, 6 announce their group's bytes;
+  // the barrier counts one arrival, so a phase cannot complete before its announcement, whichever lane's
+  // instruction comes first. (Bringing the next tile into L2 with TMA prefetches from further lanes, which paid
+  // while one thread issued everything, now only takes TMA slots from the loads: 43.0 us per launch with, 42.4
+  // without.)
+  const int my_group = lane < 6 ? (lane >> 1) : 3;
+  auto issue_slab = [&](int64_t row, int g) {  // lanes 0 .. 8
+    const int stage = g % kStages;
+    const uint32_t dst = kv_addr + stage * kStageBytes + lane * kSlabBytes;
+    const uint32_t full = bar(&misc->kv_full[stage][my_group]);
+    if (lane < 8 && (lane & 1) == 0) ptx::MbarArriveExpectTx(full, (my_group == kGroups - 1 ? 3 : 2) * kSlabBytes);
+    if (lane < 8) {
+      ptx::TmaLoad2DHint(dst, &latent_map, 64 * lane, static_cast<int32_t>(row), full, drop_policy);
+    } else {
+      ptx::TmaLoad2DHint(dst, &rope_map, 0, static_cast<int32_t>(row), full, drop_policy);
+    }
   };
   // Fused append, first half: the new row of `seq` starts towards shared memory.
   auto new_row_fetch = [&](int seq) {
@@ -353,11 +367,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     return true;
   };
   // Q of one sequence: nine 64-column slabs of 64 head rows.
-  auto issue_q = [&](int seq) {
+  auto issue_q = [&](int seq) {  // lanes 0 .. 8, one slab each
     const uint32_t qbar = bar(&misc->q_full);
-    ptx::MbarArriveExpectTx(qbar, kQBytes);
-#pragma unroll
-    for (int c = 0; c < 9; ++c) ptx::TmaLoad3D(q_addr + c * kQSlabBytes, &q_map, 64 * c, 0, seq, qbar);
+    if (lane == 0) ptx::MbarArriveExpectTx(qbar, kQBytes);
+    ptx::TmaLoad3D(q_addr + lane * kQSlabBytes, &q_map, 64 * lane, 0, seq, qbar);
   };
 
   int pre_issued = 0;  // tiles the producer put in flight before the CTA-wide setup barrier
@@ -413,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       total += t;
       nonempty += ne;
     }
-    const CostCut cut{2 * total + 3 * (nonempty > 0 ? nonempty - 1 : 0), n_ctas};
+    const CostCut cut{CostCut::Total(total, nonempty), n_ctas};
     // One pass over the sequences finds both the first tile at or after this CTA's first cost position
     // (flat index `lo`, its sequence, that sequence's first flat index and tile count) and the first tile
     // at or after the next CTA's (`hi`); either is `total` when no tile is left.
@@ -437,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         const long long s = before_s + incl_s - 1;                      // ordinal of this lane's sequence, if not empty
-        const long long last_pos = 2 * (before + incl - 1) + 3 * s;     // cost position of its last tile
+        const long long last_pos = CostCut::Pos(before + incl - 1, s);     // cost position of its last tile
         const unsigned hit_lo = __ballot_sync(0xffffffffu, mine > 0 && last_pos >= k_lo);
         const unsigned hit_hi = __ballot_sync(0xffffffffu, mine > 0 && last_pos >= k_hi);
         if (!have_lo && hit_lo != 0) {
@@ -463,22 +476,25 @@ __global__ void __launch_bounds__(kThreads, 1)
       misc->start_seq = start_seq;
       misc->start_tile = start_tile;
       misc->n_tiles = static_cast<int>(hi - lo);
-      if (hi > lo && start_seq < p.batch) {
-        const int begin = p.kv_begin ? p.kv_begin[start_seq] : 0;
-        // A tile that a fused append still has to write into is left to the main loop.
-        const int t_end = min(start_seq_tiles - (p.new_latent != nullptr ? 1 : 0), start_tile + static_cast<int>(hi - lo));
-        static_assert(kStages == 2, "the first tiles' rows are looked up before the dependency wait, two of them");
-        const int n_first = max(0, min(kStages, t_end - start_tile));
-        const int64_t row0 = n_first > 0 ? tile_row(start_seq, begin, start_tile) : 0;
-        const int64_t row1 = n_first > 1 ? tile_row(start_seq, begin, start_tile + 1) : 0;
-        if (p.stable_tables != 0) GridDependencyWait();  // Q and the pool are the preceding kernels' to write
+    }
+    // Everything below is the same in every lane (the values above came out of shuffles); lanes 0 .. 8 issue.
+    if (hi > lo && start_seq < p.batch) {
+      const int begin = p.kv_begin ? p.kv_begin[start_seq] : 0;
+      // A tile that a fused append still has to write into is left to the main loop.
+      const int t_end = min(start_seq_tiles - (p.new_latent != nullptr ? 1 : 0), start_tile + static_cast<int>(hi - lo));
+      static_assert(kStages == 2, "the first tiles' rows are looked up before the dependency wait, two of them");
+      const int n_first = max(0, min(kStages, t_end - start_tile));
+      const int64_t row0 = n_first > 0 ? tile_row(start_seq, begin, start_tile) : 0;
+      const int64_t row1 = n_first > 1 ? tile_row(start_seq, begin, start_tile + 1) : 0;
+      if (p.stable_tables != 0) GridDependencyWait();  // Q and the pool are the preceding kernels' to write
+      if (lane < 9) {
         issue_q(start_seq);
-        if (n_first > 0) issue_tile(row0, 0);
-        if (n_first > 1) issue_tile(row1, 1);
-        pre_issued = n_first;
-      } else if (p.stable_tables != 0) {
-        GridDependencyWait();
+        if (n_first > 0) issue_slab(row0, 0);
+        if (n_first > 1) issue_slab(row1, 1);
       }
+      pre_issued = n_first;
+    } else if (p.stable_tables != 0) {
+      GridDependencyWait();
     }
     __syncwarp();
   }
@@ -499,7 +515,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == 4) {
     // ======================= TMA producer =======================================================
-    if (lane == 0) {
+    // All lanes walk the segments together; what a lane issues depends on its number (see issue_slab).
+    {
       SegmentWalker walk(p.kv_len, p.batch, start_seq, start_tile, my_tiles);
       int seq, t_lo, t_hi, seq_tiles, seq_len;
       int g = 0;  // tiles issued
@@ -507,55 +524,79 @@ __global__ void __launch_bounds__(kThreads, 1)
       int seg = 0;
       uint32_t n_appended = 0;
       bool fetch_pending = false;  // a new row's bulk load is in flight towards shared memory
+      const bool loader = lane < 9;
       while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
         // Q of this segment's sequence, once the previous segment's last QK has finished reading the
         // buffer (the first segment's Q went out before the setup barrier).
         if (seg > 0) {
-          ok = BoundedWait(bar(&misc->q_empty), (seg - 1) & 1, misc, p.status, 11);
+          ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_empty), (seg - 1) & 1, misc, p.status, 11));
           if (!ok) break;
-          issue_q(seq);
+          if (loader) issue_q(seq);
         }
         ++seg;
         const int begin = p.kv_begin ? p.kv_begin[seq] : 0;
         const bool appends = p.new_latent != nullptr && t_hi == seq_tiles;  // this segment holds the sequence's end
         if (appends) {
-          new_row_fetch(seq);
+          if (lane == 0) new_row_fetch(seq);
           fetch_pending = true;
         }
-        int ahead = t_lo;  // next tile of this segment to bring into L2
         for (int t = t_lo; t < t_hi; ++t, ++g) {
           if (g < pre_issued) continue;
           const int64_t checked_row = tile_row_checked(seq, begin, t);
           const int64_t row = checked_row < 0 ? 0 : checked_row;
           if (appends && t == seq_tiles - 1) {
-            ok = new_row_store(checked_row < 0 ? -1 : checked_row + (seq_len - 1 - t * kTile), n_appended & 1);
-            if (!ok) break;
+            // The tile that receives the new row: one lane writes the row and then issues the tile's loads itself,
+            // so that its stores, its fences and its loads are one thread's program order.
+            if (lane == 0) {
+              ok = new_row_store(checked_row < 0 ? -1 : checked_row + (seq_len - 1 - t * kTile), n_appended & 1);
+              for (int c = 0; c < kGroups && ok; ++c) {
+                if (g >= kStages) {
+                  ok = BoundedSpin(bar(&misc->kv_empty[g % kStages][c]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
+                }
+                if (ok) issue_group(row, g, c);
+              }
+            }
             ++n_appended;
             fetch_pending = false;
-          }
-          if (g >= kStages) {
-            if (ahead < t) ahead = t;
-            for (; ahead < t_hi && ahead < t + kPrefetchAhead; ++ahead) {
-              prefetch_tile(ahead == t ? row : tile_row(seq, begin, ahead));
-            }
-            for (int c = 0; c < kGroups && ok; ++c) {
-              ok = BoundedSpin(bar(&misc->kv_empty[g % kStages][c]), ((g / kStages) & 1) ^ 1, misc, p.status, 10);
-              if (ok) issue_group(row, g, c);
-            }
-            if (!ok) break;
+          } else if (g < kStages) {
+            if (loader) issue_slab(row, g);
           } else {
-            issue_tile(row, g);
+            // The warp polls together and a lane issues its slab inside the loop, the moment its group has been
+            // given back: PV releases a stage group by group, and lanes that left a spin loop of their own would
+            // wait for each other at the loop's end before any of them issued.
+            const uint32_t empty = bar(&misc->kv_empty[g % kStages][my_group]);
+            const uint32_t parity = ((g / kStages) & 1) ^ 1;
+            bool done = !loader;
+            uint64_t start = 0;
+            for (uint32_t it = 0;; ++it) {
+              if (!done && ptx::MbarTestWait(empty, parity)) {
+                issue_slab(row, g);
+                done = true;
+              }
+              if (__all_sync(0xffffffffu, done)) break;
+              if ((it & 1023u) == 1023u) {
+                const uint64_t now = ptx::GlobalTimerNs();
+                if (start == 0) start = now;
+                if (Aborting(misc) || now - start > 1000000000ull) {
+                  if (!Aborting(misc) && lane == 0) RaiseTimeout(misc, p.status, 10, parity);
+                  ok = false;
+                  break;
+                }
+              }
+            }
           }
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
         }
       }
-      if (!ok && fetch_pending) {
+      if (lane == 0 && !ok && fetch_pending) {
         const uint64_t t0 = ptx::GlobalTimerNs();
         while (!ptx::MbarTryWait(bar(&misc->new_row_full), n_appended & 1)) {
           if (ptx::GlobalTimerNs() - t0 > 200000000ull) break;
         }
       }
-      if (!ok) {
-        // Aborting: let the loads this thread issued land before the CTA exits. A stage whose load
+      if (lane == 0 && !ok) {
+        // Aborting: let the loads this warp issued land before the CTA exits. A stage whose load
         // was issued at count i (the last one for that stage) completes phase (i / kStages) & 1.
         for (int s = 0; s < kStages; ++s) {
           int last = -1;
@@ -575,6 +616,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      __syncwarp();
     }
   } else if (warp == 5 || warp == 6) {
     // ======================= MMA issuers =========================================================
@@ -860,8 +902,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (row_ok) {
         misc->inv_l[head] = l_row > 0.0f ? 1.0f / l_row : 0.0f;
         if (to_ws) {
-          p.ws_m[head * p.n_slots + slot] = m_nat;
-          p.ws_l[head * p.n_slots + slot] = l_row;
+          p.ws_m[slot * kHeads + head] = m_nat;
+          p.ws_l[slot * kHeads + head] = l_row;
         } else if (to_user_partial) {
           p.user_m[static_cast<int64_t>(seq) * kHeads + head] = m_nat;
           p.user_l[static_cast<int64_t>(seq) * kHeads + head] = l_row;
@@ -870,27 +912,42 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       ptx::NamedBarrier(1, kSoftmaxThreads);
+      if (to_ws) {
+        // The usual case (a sequence cut over several CTAs). Both halves of an accumulator are read before the
+        // one wait; store j of a warp is the 512 contiguous bytes of head quad j, dv 32 w .. 32 w + 31.
+        uint4* slot_base = reinterpret_cast<uint4*>(p.ws_o) + static_cast<int64_t>(slot) * (kLatent * kHeads / 4);
 #pragma unroll 1
-      for (int tm = 0; tm < 4; ++tm) {
-        const int dv = 128 * tm + warp * 32 + lane;
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t o[32];
-          ptx::TmemLd32(tmem + lane_base + 64 * tm + 32 * half, o);
+        for (int tm = 0; tm < 4; ++tm) {
+          const int dv = 128 * tm + warp * 32 + lane;
+          uint32_t lo[32], hi[32];
+          ptx::TmemLd32(tmem + lane_base + 64 * tm, lo);
+          ptx::TmemLd32(tmem + lane_base + 64 * tm + 32, hi);
           ptx::TmemWaitLd();
-          if (to_ws) {
-            float* dst = p.ws_o + (static_cast<int64_t>(32 * half) * p.n_slots + slot) * kLatent + dv;
+          uint4* dst = slot_base + dv;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) dst[static_cast<int64_t>(j) * p.n_slots * kLatent] = __uint_as_float(o[j]);
-          } else if (to_user_partial) {
-            float* dst = p.user_o + (static_cast<int64_t>(seq) * kHeads + 32 * half) * kLatent + dv;
+          for (int j = 0; j < 8; ++j) dst[j * kLatent] = make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) dst[j * kLatent] = __uint_as_float(o[j]);
-          } else {
-            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(seq) * kHeads + 32 * half) * kLatent + dv;
+          for (int j = 0; j < 8; ++j) dst[(8 + j) * kLatent] = make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
+        }
+      } else {
+#pragma unroll 1
+        for (int tm = 0; tm < 4; ++tm) {
+          const int dv = 128 * tm + warp * 32 + lane;
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            uint32_t o[32];
+            ptx::TmemLd32(tmem + lane_base + 64 * tm + 32 * half, o);
+            ptx::TmemWaitLd();
+            if (to_user_partial) {
+              float* dst = p.user_o + (static_cast<int64_t>(seq) * kHeads + 32 * half) * kLatent + dv;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              dst[j * kLatent] = __float2bfloat16_rn(__uint_as_float(o[j]) * misc->inv_l[32 * half + j]);
+              for (int j = 0; j < 32; ++j) dst[j * kLatent] = __uint_as_float(o[j]);
+            } else {
+              __nv_bfloat16* dst = p.out + (static_cast<int64_t>(seq) * kHeads + 32 * half) * kLatent + dv;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                dst[j * kLatent] = __float2bfloat16_rn(__uint_as_float(o[j]) * misc->inv_l[32 * half + j]);
+              }
             }
           }
         }
@@ -913,35 +970,50 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // Merges the partial segments of every sequence that straddles CTAs, and writes the result of empty
-// sequences. One warp per (sequence, head); grid-wide, so the partials (a few tens of MB, mostly still
-// in L2) are pulled by every SM at once. Recomputes the flat partition arithmetic of the decode
-// kernel: sequence b owns tiles [P_b, P_b + n_b) of T; CTA c owns [c*T/G, (c+1)*T/G).
-// Loads are arranged in two independent waves instead of a chain per part: the lengths (before the
-// decode kernel has finished), then every part's (m, l), one part per lane, together with the parts' rows,
-// up to eight (sixteen when four warps share a row) parts in flight.
-template <int kColSplit>
-__global__ void __launch_bounds__(256)
+// sequences. A CTA takes one sequence, one quad of heads and a range of the 512 output columns; a thread owns
+// one column (dv) of the four heads, as the decode kernel's epilogue left them: 16 bytes per part, a warp's
+// loads 512 contiguous bytes, and its output stores runs of 32 consecutive values of a row.
+//
+// Where a sequence's parts lie follows from the lengths alone (the decode kernel's cut of the tile list,
+// CostCut), so that arithmetic runs before the wait for the decode kernel. Then, per chunk of parts, the data
+// loads of the chunk's first parts are issued, one warp per part group works out the weights of its eight parts
+// for the quad's four heads (lane = part x head; the maxima and sums are shuffles) and leaves them in shared
+// memory, and every thread accumulates weight x data.
+// kGroups = 1: 128 threads, 256 columns per CTA in two passes, every thread walks all parts (batches, where a
+// sequence has a handful of parts: 32 CTAs per sequence). kGroups = 8: 256 threads, 32 columns per CTA, a
+// chunk is 64 parts of which each warp takes eight, summed through shared memory at the end (a few long
+// sequences with a hundred parts each: 256 CTAs per sequence).
+// The kernel needs a few hundred bytes of shared memory, so its CTAs fit beside a resident decode CTA.
+template <int kGroups>
+__global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2)
     MlaFinalizeKernel(TcParams p, int32_t n_ctas) {
-  // kColSplit warps (1, 4 or 16) share a row, each taking 512 / kColSplit of its columns: with few rows (one
-  // long sequence has 64) that is what fills the GPU, and a lane then holds so little of a part that 16 or
-  // 32 parts can be in flight at once.
-  static_assert(kColSplit == 1 || kColSplit == 2 || kColSplit == 4 || kColSplit == 16,
-                "a lane holds 16, 8, 4 or 1 floats of a row");
-  constexpr int kFloats = 16 / kColSplit;                                  // floats per lane and part
-  constexpr int kBatch = kColSplit <= 2 ? 8 : (kColSplit == 4 ? 16 : 32);  // parts in flight
-  const int lane = threadIdx.x & 31;
-  const int64_t warp_id = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t row = warp_id / kColSplit;
-  const int quarter = static_cast<int>(warp_id % kColSplit);
-  const bool in_range = row < static_cast<int64_t>(p.batch) * kHeads;  // the last CTA may have spare warps
-  const int b = in_range ? static_cast<int>(row / kHeads) : p.batch - 1;
-  const int h = static_cast<int>(row % kHeads);
-  // Where the sequence's parts lie follows from the lengths alone (the decode kernel's cut of the tile list,
-  // CostCut). All warps of a CTA work on the same sequence (a CTA covers at most eight consecutive rows and a
-  // sequence has 64), so the first warp works it out once for all of them: this arithmetic, not memory, is
-  // what the kernel spends its time on otherwise.
+  constexpr int kThreadsF = kGroups == 1 ? 128 : 256;
+  constexpr int kGroupThreads = kThreadsF / kGroups;   // 128 or 32: columns a group covers per pass
+  constexpr int kPasses = kGroups == 1 ? 2 : 1;
+  constexpr int kDv = kGroupThreads * kPasses;         // 256 or 32 output columns per CTA
+  constexpr int kChunk = 8 * kGroups;                  // parts per chunk: 8 per group
+  constexpr int kSub = 4;                              // parts whose data a thread has in flight
+  constexpr int kDvChunks = kLatent / kDv;             // 2 or 16
+  constexpr int kQuads = kHeads / 4;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int b = blockIdx.x / (kQuads * kDvChunks);
+  const int hq = (blockIdx.x / kDvChunks) % kQuads;    // heads 4 hq .. 4 hq + 3
+  const int dv0 = (blockIdx.x % kDvChunks) * kDv;
+  const int group = tid / kGroupThreads;
+  const int tl = tid % kGroupThreads;
+
   __shared__ long long shared_meta[8];
-  if (threadIdx.x < 32) {
+  __shared__ int s_slot[kChunk];
+  __shared__ __align__(16) float s_w[kChunk][4];
+  __shared__ float s_gmax[kGroups][4], s_gsum[kGroups][4];
+  __shared__ __align__(16) float s_carry[4];
+  __shared__ float s_big[4], s_sum[4];
+  __shared__ __align__(16) float4 s_red[kGroups > 1 ? kGroups * kGroupThreads : 1];
+
+  if (tid < 32) {
     long long before = 0, total = 0, before_s = 0, nonempty = 0;
     for (int i = lane; i < p.batch; i += 32) {
       const long long t = TilesOf(p.kv_len[i]);
@@ -961,7 +1033,7 @@ __global__ void __launch_bounds__(256)
     }
     if (lane == 0) {
       const long long tiles = TilesOf(p.kv_len[b]);
-      const CostCut c{2 * total + 3 * (nonempty > 0 ? nonempty - 1 : 0), n_ctas};
+      const CostCut c{CostCut::Total(total, nonempty), n_ctas};
       shared_meta[0] = total;
       shared_meta[1] = nonempty;
       shared_meta[2] = before;
@@ -973,150 +1045,178 @@ __global__ void __launch_bounds__(256)
       shared_meta[6] = tiles > 0 ? c.CtaOf(before + tiles - 1, before_s) : -1;
       shared_meta[7] = before > 0 && tiles > 0 ? c.CtaOf(before - 1, before_s - 1) : -1;
     }
+    if (lane < 4) {
+      s_big[lane] = -INFINITY;
+      s_sum[lane] = 0.0f;
+    }
   }
   __syncthreads();
-  if (!in_range) return;
   const long long total = shared_meta[0], nonempty = shared_meta[1], before = shared_meta[2], before_s = shared_meta[3];
   const long long mine = shared_meta[4];
-  const long long c_first = shared_meta[5], c_last = shared_meta[6], c_prev = shared_meta[7];
+  const int cf = static_cast<int>(shared_meta[5]), cl = static_cast<int>(shared_meta[6]), cp = static_cast<int>(shared_meta[7]);
   const bool want_partial = p.user_o != nullptr;
-  const CostCut cut{2 * total + 3 * (nonempty > 0 ? nonempty - 1 : 0), n_ctas};
-  // Slot of CTA c's part of this sequence, or -1: the CTA holds a part if its first tile inside the
-  // sequence lies before the next CTA's run.
-  // When every CTA's share of the cost is at least 5 units it holds at least one tile (consecutive tiles
-  // are at most 5 units apart), so every CTA from c_first to c_last holds a part and no division is needed.
-  const bool dense = cut.cost_total >= 5 * cut.n_ctas;
-  auto slot_of = [&](long long c) {
-    if (c > c_last) return -1;
+  const CostCut cut{CostCut::Total(total, nonempty), n_ctas};
+  // Slot of CTA c's part of this sequence, or -1: the CTA holds a part if its first tile inside the sequence
+  // lies before the next CTA's run. When every CTA's share of the cost is at least 5 units it holds at least
+  // one tile (consecutive tiles are at most 5 units apart), so every CTA from the first to the last holds a
+  // part and no division is needed.
+  const bool dense = cut.cost_total >= (CostCut::kTileCost + CostCut::kCrossCost) * cut.n_ctas;
+  auto slot_of = [&](int c) {
+    if (c > cl) return -1;
     if (!dense) {
       const long long x = cut.FirstTileAt(cut.FirstPos(c), before, before_s);
-      if (x >= before + mine || 2 * x + 3 * before_s >= cut.FirstPos(c + 1)) return -1;
+      if (x >= before + mine || CostCut::Pos(x, before_s) >= cut.FirstPos(c + 1)) return -1;
     }
-    return static_cast<int>(c * 2 + (c > c_prev ? 0 : 1));
+    return c * 2 + (c > cp ? 0 : 1);
   };
-  int slot = slot_of(c_first + lane);
-  // 32-bit copies for the part loop below (CTA numbers and slots are small; the loop runs once per part and
-  // its instruction count, not memory, is what bounds this kernel when a sequence has a hundred parts).
-  const int cf = static_cast<int>(c_first), cl = static_cast<int>(c_last), cp = static_cast<int>(c_prev);
-  const int n_slots = p.n_slots;
-  const float* head_rows = p.ws_o + static_cast<int64_t>(h) * n_slots * kLatent;
   // All of the above came from the lengths, which were stable before the decode kernel ran; the partials
   // below are what that kernel wrote, so they wait for its completion.
   GridDependencyTrigger();
   GridDependencyWait();
+  if (mine > 0 && cf == cl) return;  // written directly by the decode kernel
 
-  float big = -INFINITY, sum_l = 0.0f;
-  float acc[kFloats];
+  float acc[kPasses][4];
 #pragma unroll
-  for (int i = 0; i < kFloats; ++i) acc[i] = 0.0f;
-  // Lane `lane` of warp `quarter` holds floats [4 * (col4 + lane + 32 i), +4) of a row for i < kFloats / 4, or
-  // the single float col1 + lane when sixteen warps share the row.
-  const int col4 = kColSplit <= 4 ? quarter * (128 / kColSplit) : 0;
-  const int col1 = quarter * 32;
+  for (int q = 0; q < kPasses; ++q) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[q][i] = 0.0f;
+  }
+  // float4 index of this thread's column of the quad in pass q of slot s: (s * 16 + hq) * 512 + dv
+  const float4* ws4 = reinterpret_cast<const float4*>(p.ws_o);
+  const int dv_first = dv0 + tl;
 
-  if (mine > 0 && c_first == c_last) return;  // written directly by the decode kernel
-  for (int c0 = cf; c0 <= cl; c0 += 32) {
-    // One wave of loads per chunk of 32 parts: lane k asks for the (m, l) of CTA c0 + k's part while the
-    // rows of the chunk's first parts are requested as well; where a part lies follows from
-    // arithmetic, so nothing here waits for an earlier load.
-    if (c0 != cf) slot = slot_of(c0 + lane);
-    float m = -INFINITY, l = 0.0f;
-    if (slot >= 0) {
-      l = p.ws_l[h * n_slots + slot];
-      m = p.ws_m[h * n_slots + slot];
-    }
-    const int left = cl - c0 + 1;
-    const int n_here = left < 32 ? left : 32;
-    float w = 0.0f;
-    for (int k0 = 0; k0 < n_here; k0 += kBatch) {
-      float v[kBatch][kFloats];
-      int slot_k[kBatch];
+  for (int c0 = cf; c0 <= cl && mine > 0; c0 += kChunk) {
+    if (c0 != cf) __syncthreads();  // the previous chunk's weights and slots have been used
+    if (tid < kChunk) s_slot[tid] = slot_of(c0 + tid);
+    __syncthreads();
+    // This thread's parts of the chunk: 8 consecutive ones per group, four at a time.
+    float4 data[kSub][kPasses];
+    auto load_sub = [&](int sub) {
 #pragma unroll
-      for (int k = 0; k < kBatch; ++k) {
-        if (dense) {  // every CTA of the range holds a part: its slot is arithmetic, no shuffle
-          const int c = c0 + k0 + k;
-          slot_k[k] = k0 + k < n_here ? 2 * c + (c > cp ? 0 : 1) : -1;
-        } else {
-          slot_k[k] = __shfl_sync(0xffffffffu, slot, (k0 + k) & 31);
-          if (k0 + k >= n_here) slot_k[k] = -1;
-        }
-        const float* rowp = head_rows + (slot_k[k] < 0 ? 0 : slot_k[k]) * kLatent;
-        if constexpr (kFloats == 1) {
-          v[k][0] = slot_k[k] >= 0 ? rowp[col1 + lane] : 0.0f;
-        } else {
+      for (int k = 0; k < kSub; ++k) {
+        const int slot = s_slot[group * 8 + sub * kSub + k];
 #pragma unroll
-          for (int i = 0; i < kFloats / 4; ++i) {
-            const float4 t = slot_k[k] >= 0 ? reinterpret_cast<const float4*>(rowp)[col4 + lane + 32 * i]
-                                            : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            v[k][4 * i] = t.x;
-            v[k][4 * i + 1] = t.y;
-            v[k][4 * i + 2] = t.z;
-            v[k][4 * i + 3] = t.w;
-          }
+        for (int q = 0; q < kPasses; ++q) {
+          data[k][q] = slot >= 0 ? ws4[(static_cast<int64_t>(slot) * kQuads + hq) * kLatent + dv_first + kGroupThreads * q]
+                                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
       }
-      if (k0 == 0) {
-        // The chunk's weights (this is where m and l are first needed).
-        if (!(l > 0.0f)) m = -INFINITY;
-        float chunk_max = m;
+    };
+    load_sub(0);
+    // ---- weights of the chunk: warp g of the first kGroups warps takes parts 8 g .. 8 g + 7, lane = (part, head) ----
+    float m_mine = -INFINITY, l_mine = 0.0f;
+    if (warp < kGroups) {
+      const int slot = s_slot[warp * 8 + (lane >> 2)];
+      if (slot >= 0) {
+        l_mine = p.ws_l[slot * kHeads + 4 * hq + (lane & 3)];
+        m_mine = p.ws_m[slot * kHeads + 4 * hq + (lane & 3)];
+      }
+      if (!(l_mine > 0.0f)) m_mine = -INFINITY;
+      float gmax = m_mine;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, off));
-        const float new_big = fmaxf(big, chunk_max);
-        // Rescale what earlier chunks accumulated (only sequences cut over more than 32 CTAs).
-        const float carry = (big == -INFINITY || new_big == -INFINITY) ? 0.0f : expf(big - new_big);
-        big = new_big;
-        sum_l *= carry;
+      for (int off = 4; off < 32; off <<= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, off));
+      if (lane < 4) s_gmax[warp][lane] = gmax;
+    }
+    if constexpr (kGroups > 1) __syncthreads(); else __syncwarp();
+    if (warp < kGroups) {
+      const int i = lane & 3;
+      const float old_big = s_big[i];
+      float new_big = old_big;
 #pragma unroll
-        for (int i = 0; i < kFloats; ++i) acc[i] *= carry;
-        w = (l > 0.0f && big != -INFINITY) ? expf(m - big) : 0.0f;
-        float lw = l * w;
+      for (int g = 0; g < kGroups; ++g) new_big = fmaxf(new_big, s_gmax[g][i]);
+      const float w = (l_mine > 0.0f && new_big != -INFINITY) ? expf(m_mine - new_big) : 0.0f;
+      s_w[warp * 8 + (lane >> 2)][i] = w;
+      float gsum = l_mine * w;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, off);
-        sum_l += lw;
+      for (int off = 4; off < 32; off <<= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, off);
+      if (lane < 4) s_gsum[warp][lane] = gsum;
+      if constexpr (kGroups > 1) {
+        // every warp has read s_big before warp 0 replaces it
+        asm volatile("bar.sync 1, %0;" ::"r"(kGroups * 32) : "memory");
+      } else {
+        __syncwarp();
+      }
+      if (warp == 0 && lane < 4) {
+        // Rescale what earlier chunks accumulated (only sequences cut over more parts than a chunk holds).
+        const float carry = (old_big == -INFINITY || new_big == -INFINITY) ? 0.0f : expf(old_big - new_big);
+        float sum = s_sum[i] * carry;
+#pragma unroll
+        for (int g = 0; g < kGroups; ++g) sum += s_gsum[g][i];
+        s_sum[i] = sum;
+        s_big[i] = new_big;
+        s_carry[i] = carry;
+      }
+    }
+    __syncthreads();
+    // ---- data of the chunk ----
+    if (c0 != cf) {
+      const float4 cr = *reinterpret_cast<const float4*>(s_carry);
+#pragma unroll
+      for (int q = 0; q < kPasses; ++q) {
+        acc[q][0] *= cr.x;
+        acc[q][1] *= cr.y;
+        acc[q][2] *= cr.z;
+        acc[q][3] *= cr.w;
+      }
+    }
+#pragma unroll
+    for (int sub = 0; sub < 8 / kSub; ++sub) {
+      if (sub > 0) {
+        if (s_slot[group * 8 + sub * kSub] < 0 && dense) break;  // dense: parts are consecutive, the rest is absent
+        load_sub(sub);
       }
 #pragma unroll
-      for (int k = 0; k < kBatch; ++k) {
-        // An empty part's row may hold anything (its weight is zero, but 0 x NaN is not): select, no branch.
-        const float from_lane = __shfl_sync(0xffffffffu, w, (k0 + k) & 31);
-        const float wk = slot_k[k] >= 0 ? from_lane : 0.0f;
+      for (int k = 0; k < kSub; ++k) {
+        // An absent part has weight zero and zero data; a present one with l = 0 may hold anything (0 x NaN is
+        // not 0), so its data is dropped with its weight.
+        const float4 w = *reinterpret_cast<const float4*>(s_w[group * 8 + sub * kSub + k]);
 #pragma unroll
-        for (int i = 0; i < kFloats; ++i) acc[i] = fmaf(wk != 0.0f ? v[k][i] : 0.0f, wk, acc[i]);
+        for (int q = 0; q < kPasses; ++q) {
+          acc[q][0] = fmaf(w.x != 0.0f ? data[k][q].x : 0.0f, w.x, acc[q][0]);
+          acc[q][1] = fmaf(w.y != 0.0f ? data[k][q].y : 0.0f, w.y, acc[q][1]);
+          acc[q][2] = fmaf(w.z != 0.0f ? data[k][q].z : 0.0f, w.z, acc[q][2]);
+          acc[q][3] = fmaf(w.w != 0.0f ? data[k][q].w : 0.0f, w.w, acc[q][3]);
+        }
       }
     }
   }
-  if (want_partial) {
-    float* dst = p.user_o + row * kLatent;
-    if constexpr (kFloats == 1) {
-      dst[col1 + lane] = acc[0];
-    } else {
+  if constexpr (kGroups > 1) {
+    s_red[group * kGroupThreads + tl] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+    __syncthreads();
+    if (group != 0) return;
 #pragma unroll
-      for (int i = 0; i < kFloats / 4; ++i) {
-        reinterpret_cast<float4*>(dst)[col4 + lane + 32 * i] =
-            make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+    for (int g = 1; g < kGroups; ++g) {
+      const float4 v = s_red[g * kGroupThreads + tl];
+      acc[0][0] += v.x;
+      acc[0][1] += v.y;
+      acc[0][2] += v.z;
+      acc[0][3] += v.w;
+    }
+  }
+  const int64_t row0 = static_cast<int64_t>(b) * kHeads + 4 * hq;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float sum = s_sum[i];
+    const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+#pragma unroll
+    for (int q = 0; q < kPasses; ++q) {
+      const int64_t at = (row0 + i) * kLatent + dv_first + kGroupThreads * q;
+      if (want_partial) {
+        p.user_o[at] = acc[q][i];
+      } else {
+        p.out[at] = __float2bfloat16_rn(acc[q][i] * inv);
       }
     }
-    if (lane == 0 && quarter == 0) {
-      p.user_m[row] = big;
-      p.user_l[row] = sum_l;
-    }
-    return;
   }
-  const float inv = sum_l > 0.0f ? 1.0f / sum_l : 0.0f;
-  __nv_bfloat16* dst = p.out + row * kLatent;
-  if constexpr (kFloats == 1) {
-    dst[col1 + lane] = __float2bfloat16_rn(acc[0] * inv);
-  } else {
-#pragma unroll
-    for (int i = 0; i < kFloats / 4; ++i) {
-      const __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[4 * i] * inv, acc[4 * i + 1] * inv);
-      const __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc[4 * i + 2] * inv, acc[4 * i + 3] * inv);
-      uint2 packed;
-      packed.x = *reinterpret_cast<const uint32_t*>(&lo2);
-      packed.y = *reinterpret_cast<const uint32_t*>(&hi2);
-      reinterpret_cast<uint2*>(dst)[col4 + lane + 32 * i] = packed;
+  if (dv0 == 0 && tid < 4) {
+    const float sum = s_sum[tid];
+    if (want_partial) {
+      p.user_m[row0 + tid] = s_big[tid];
+      p.user_l[row0 + tid] = sum;
+    } else if (p.lse != nullptr) {
+      p.lse[row0 + tid] = sum > 0.0f ? s_big[tid] + logf(sum) : -INFINITY;
     }
   }
-  if (lane == 0 && quarter == 0 && p.lse) p.lse[row] = sum_l > 0.0f ? big + logf(sum_l) : -INFINITY;
 }
 
 // ---- tensor maps ----------------------------------------------------------------------------------
@@ -1342,22 +1442,14 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
                              "tcgen05 decode launch")) {
     return rc;
   }
-  const int64_t rows = static_cast<int64_t>(a.batch) * kHeads;
-  // Few rows (a handful of long sequences): four or sixteen warps per row, so that the merge still fills the GPU.
-  if (rows < 256) {
-    return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<16>, dim3(static_cast<unsigned>((rows * 16 + 7) / 8)), dim3(256), 0,
+  // A handful of long sequences: 256 CTAs per sequence, the parts shared out among a CTA's eight warps, so that
+  // the merge still fills the GPU. Batches: 32 CTAs per sequence, every thread walking the sequence's few parts.
+  if (a.batch < 16) {
+    return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<8>, dim3(static_cast<unsigned>(a.batch) * 16 * (kLatent / 32)), dim3(256), 0,
                                       stream, p, n_ctas),
                      "decode finalize launch");
   }
-  if (rows < 1024) {
-    return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<4>, dim3(static_cast<unsigned>((rows * 4 + 7) / 8)), dim3(256), 0,
-                                      stream, p, n_ctas),
-                     "decode finalize launch");
-  }
-  // Many rows: two warps per row (109 registers against 254 for one warp per row, so twice the warps fit an
-  // SM) in CTAs of 128 threads, small enough to become resident beside the decode kernel's CTAs and have their
-  // arithmetic done when it finishes.
-  return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<2>, dim3(static_cast<unsigned>((rows * 2 + 3) / 4)), dim3(128), 0,
+  return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<1>, dim3(static_cast<unsigned>(a.batch) * 16 * (kLatent / 256)), dim3(128), 0,
                                     stream, p, n_ctas),
                    "decode finalize launch");
 }

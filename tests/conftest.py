@@ -26,3 +26,27 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Attention tolerance outcomes of the run: which comparisons also met the per-element bound."""
+    try:
+        import scenarios
+    except Exception:  # pragma: no cover
+        return
+    records = scenarios.TOLERANCE_RECORDS
+    if not records:
+        return
+    held = sum(1 for r in records if r["element_bound_excess"] <= 0.0)
+    terminalreporter.write_line(f"attention comparisons: {len(records)}; per-element bound 2e-3 + 1e-2*|ref| held in {held}")
+    for r in records:
+        if r["element_bound_excess"] > 0.0:
+            terminalreporter.write_line(
+                f"  per-element bound exceeded by {r['element_bound_excess']:.3e} (row bound margin "
+                f"{-r['row_bound_excess']:.3e}, max |ref| {r['max_abs_ref']:.3g}): {r['what']}")
+    path = os.environ.get("B200KV_TOLERANCE_REPORT")
+    if path:
+        import json
+
+        with open(path, "w") as f:
+            json.dump(records, f, indent=1)

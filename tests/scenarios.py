@@ -78,24 +78,43 @@ def ref_attention_f64(q_u16, pool_u16, table, kv_len, block_size, scale, kv_begi
     return out, lse
 
 
+# Every call of check_attention leaves a record here: (what, max abs err, worst excess over the row-max bound,
+# worst excess over the per-element bound). conftest.py prints them at the end of a run and writes them to the
+# file named by B200KV_TOLERANCE_REPORT, when that is set.
+TOLERANCE_RECORDS = []
+
+
 def check_attention(out_u16, lse, ref_out, ref_lse, abs_tol=2e-3, rel_tol=1e-2, lse_tol=1e-3, what="",
-                    strict_abs=False):
-    """The tolerance the path is held to (bf16 in, fp32 accumulate, bf16 out): every element satisfies
-    |got - ref| <= 2e-3 + 1e-2 * scale, where scale is the largest |ref| of the element's output row (an
-    output row is a softmax-weighted average of value rows, so its error is relative to the magnitude of
-    the values averaged, not to an element that happens to cancel); lse is within 1e-3. With strict_abs
-    (inputs drawn from the benchmark's distribution, outputs well below 0.2 in magnitude) the absolute
-    bound 2e-3 must hold alone."""
+                    strict_abs=False, elementwise=None):
+    """The tolerance the path is held to (bf16 in, fp32 accumulate, bf16 out), in three forms:
+
+    per element  |got - ref| <= 2e-3 + 1e-2 * |ref|            asserted with elementwise=True, and always
+                                                                implied by strict_abs
+    per row      |got - ref| <= 2e-3 + 1e-2 * max_row |ref|    always asserted: an output row is a softmax-weighted
+                                                                average of value rows, so its error is relative to
+                                                                the magnitude of the values averaged, not to an
+                                                                element of the row that happens to cancel
+    absolute     |got - ref| <= 2e-3                            strict_abs: inputs drawn from the benchmark's
+                                                                distribution (outputs well below 0.2 in magnitude)
+
+    lse is within 1e-3. elementwise=None measures the per-element form without asserting it (adversarial
+    inputs whose rows hold large values beside cancelling ones); the record says by how much it held or not."""
     got = kvo.bf16_to_f32(np.asarray(out_u16)).astype(np.float64)
     assert np.isfinite(got).all(), f"{what}: non-finite output"
     err = np.abs(got - ref_out)
     row_scale = np.abs(ref_out).max(axis=-1, keepdims=True) if err.size else 0.0
     bound = abs_tol + rel_tol * row_scale
     worst = float((err - bound).max()) if err.size else -1.0
+    worst_elem = float((err - (abs_tol + rel_tol * np.abs(ref_out))).max()) if err.size else -1.0
     max_abs = float(err.max()) if err.size else 0.0
+    TOLERANCE_RECORDS.append({"what": what, "max_abs_err": max_abs, "row_bound_excess": worst,
+                              "element_bound_excess": worst_elem, "strict_abs": bool(strict_abs),
+                              "max_abs_ref": float(np.abs(ref_out).max()) if err.size else 0.0})
     assert worst <= 0.0, f"{what}: |err| exceeds {abs_tol} + {rel_tol}*rowmax|ref| by {worst:.3e} (max abs err {max_abs:.3e})"
     if strict_abs:
         assert max_abs <= abs_tol, f"{what}: max abs err {max_abs:.3e} > {abs_tol}"
+    if elementwise:
+        assert worst_elem <= 0.0, f"{what}: |err| exceeds {abs_tol} + {rel_tol}*|ref| per element by {worst_elem:.3e}"
     if lse is not None:
         finite = np.isfinite(ref_lse)
         assert (np.isfinite(np.asarray(lse)) == finite).all(), f"{what}: lse finiteness differs"

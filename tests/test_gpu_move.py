@@ -113,6 +113,29 @@ def test_gather_reports_out_of_range_block():
     assert (from_dev_bf16(out_l)[:64] == kvo.make_pool(4 * bs)[64:128, :512]).all()
 
 
+def test_gather_length_beyond_the_table_row_is_reported_not_read():
+    """A device-side length that runs past the sequence's row of the block table: the rows the table covers are
+    gathered, the rest is recorded as a bad block; the next sequence's entries are not used in its place."""
+    bs = 64
+    pool_np = kvo.make_pool(8 * bs)
+    pool = to_dev_bf16(pool_np)
+    table = np.array([[1, 2], [3, 4]], dtype=np.int32)
+    kv_len = np.array([3 * bs, 10], dtype=np.int32)  # sequence 0 claims a third block its row does not have
+    total = int(kv_len.sum())
+    out_l = to_dev_bf16(np.full((total, 512), POISON, dtype=np.uint16))
+    out_r = to_dev_bf16(np.full((total, 64), POISON, dtype=np.uint16))
+    status = b200kv.new_status()
+    b200kv.gather(b200kv.pool_view(pool), to_dev_i32(table), to_dev_i32(kv_len), bs, out_l, out_r,
+                  to_dev_i64([0, 3 * bs]), total, status=status)
+    torch.cuda.synchronize()
+    st = status.cpu().tolist()
+    assert st[0] == b200kv.DEV_BAD_BLOCK and st[1] == 0 and st[2] == 2 and st[3] == -1, st
+    got = from_dev_bf16(out_l)
+    assert (got[: 2 * bs] == pool_np[bs: 3 * bs, :512]).all()
+    assert (got[2 * bs: 3 * bs] == POISON).all(), "rows beyond the table were written from somewhere"
+    assert (got[3 * bs:] == pool_np[3 * bs: 3 * bs + 10, :512]).all()
+
+
 def test_generator_on_device_matches_oracle_bits():
     n = 3_000_001
     dst = torch.empty(n, dtype=torch.bfloat16, device="cuda")

@@ -64,3 +64,20 @@ def test_static_scratch_entry_refuses_grids_beyond_its_array():
                                  out=out, max_ctas=33)
     assert err.value.code == b200kv.ERR_INVALID and "at most 32" in str(err.value)
     assert b200kv.lib.b200kv_mla_decode_static_scratch_bytes() == 32 * 2 * 64 * 514 * 4
+
+
+
+def test_static_scratch_entry_refuses_what_the_workspace_entry_refuses():
+    """Both entry points share their argument checks: a query whose head stride is shorter than a row (8
+    elements: a multiple of 8, so the tensor-core kernel's own alignment rule alone would let it through) is
+    refused as invalid before anything is launched."""
+    bs, kv_len, table, pool_np, q_np = _case(shift=0)
+    pool, q = to_dev_bf16(pool_np), to_dev_bf16(q_np)
+    out = torch.zeros((len(kv_len), 64, 512), dtype=torch.bfloat16, device="cuda")
+    narrow = q.as_strided((len(kv_len), 64, kvo.ROW), (64 * kvo.ROW, 8, 1))
+    for call in (b200kv.mla_decode_static,
+                 lambda *a, **k: b200kv.mla_decode(*a, workspace=torch.empty(
+                     b200kv.decode_workspace_bytes(len(kv_len)), dtype=torch.uint8, device="cuda"), **k)):
+        with pytest.raises(b200kv.B200KVError) as err:
+            call(narrow, b200kv.pool_view(pool), to_dev_i32(table), to_dev_i32(kv_len), bs, 1.0 / 24.0, out=out)
+        assert err.value.code == b200kv.ERR_INVALID
