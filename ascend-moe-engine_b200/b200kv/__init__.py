@@ -476,6 +476,8 @@ class KvCache(Structure):
         ("slot_mapping_handle", c_int64),
         ("latent_handle", c_int64),
         ("rope_handle", c_int64),
+        ("max_blocks_per_seq", c_int64),
+        ("seq_lens_handle", c_int64),
     ]
 
 
@@ -593,10 +595,46 @@ class Arena:
                                           ctypes.byref(cache)))
         return cache
 
+    def reserve_kv_cache_batched(self, num_blocks: int, block_size: int, layers: int, max_seqs: int,
+                                 max_blocks_per_seq: int, tokens_per_step: int) -> KvCache:
+        lib.b200kv_kv_cache_reserve_batched.restype = c_int32
+        lib.b200kv_kv_cache_reserve_batched.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                                        POINTER(KvCache)]
+        cache = KvCache()
+        check(lib.b200kv_kv_cache_reserve_batched(self._h, num_blocks, block_size, layers, max_seqs, max_blocks_per_seq,
+                                                  tokens_per_step, ctypes.byref(cache)))
+        return cache
+
+    def tensor(self, handle: int, shape, dtype):
+        """The committed span `handle` (or an address) as a torch tensor over the arena's memory, no copy."""
+        return device_tensor(self.address(handle), shape, dtype)
+
     def layer_view(self, cache: KvCache, layer: int) -> PoolView:
         view = PoolView()
         check(lib.b200kv_kv_cache_layer_view(self._h, ctypes.byref(cache), layer, ctypes.byref(view)))
         return view
+
+
+class _RawDeviceMemory:
+    """Memory someone else owns, described for torch through the CUDA array interface."""
+
+    def __init__(self, address: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 2}
+
+
+def device_tensor(address: int, shape, dtype):
+    """A torch tensor of `shape` and `dtype` over device memory at `address` that the caller keeps alive (an
+    arena span, an arena workspace). Nothing is allocated or copied."""
+    import math
+
+    import torch
+
+    count = math.prod(shape)
+    nbytes = count * torch.empty((), dtype=dtype).element_size()
+    if nbytes == 0:
+        return torch.empty(shape, dtype=dtype, device="cuda")
+    raw = torch.as_tensor(_RawDeviceMemory(address, nbytes), device="cuda")
+    return raw.view(dtype).view(*shape)
 
 
 def plan_reservation(max_context: int, block_size: int, layers: int = 43, max_seqs: int = 1,

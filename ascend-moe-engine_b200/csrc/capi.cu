@@ -101,7 +101,7 @@ using namespace b200kv;
 
 extern "C" const char* b200kv_last_error(void) { return g_error; }
 
-extern "C" int32_t b200kv_abi_version(void) { return 2; }
+extern "C" int32_t b200kv_abi_version(void) { return 3; }
 
 extern "C" size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas) {
   if (batch <= 0 || heads <= 0) return 0;

@@ -10,6 +10,7 @@
 // major layout, two co-indexed caches) and src/pipeline/pipeline.cpp:391-395 (per-layer base).
 #include <cuda_runtime.h>
 
+#include <climits>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -111,8 +112,8 @@ extern "C" int64_t b200kv_arena_reserve(b200kv_arena* arena, const char* name, s
     return -B200KV_ERR_NULLPTR;
   }
   if (align == 0) align = kArenaAlign;
-  if (arena->sealed) return -Refuse("the arena is sealed for decoding; Reserve would allocate inside the layer loop");
-  if (arena->base != nullptr) return -Refuse("Reserve after Commit: the arena's size is already fixed");
+  if (arena->sealed) return -Refuse("reserve refused: the arena has been sealed for the decode loop");
+  if (arena->base != nullptr) return -Refuse("reserve refused: the arena was committed and its size can no longer change");
   if (bytes == 0) return -Refuse("a reservation must not be empty");
   if ((align & (align - 1)) != 0) return -Refuse("a reservation's alignment must be a power of two");
   Span span{name, AlignUp(arena->cursor, align), bytes, align};
@@ -124,8 +125,8 @@ extern "C" int64_t b200kv_arena_reserve(b200kv_arena* arena, const char* name, s
 extern "C" int32_t b200kv_arena_commit(b200kv_arena* arena) {
   if (arena == nullptr) return B200KV_ERR_NULLPTR;
   if (arena->sealed) return Refuse("the arena is sealed; Commit refused");
-  if (arena->base != nullptr) return Refuse("the arena is already committed");
-  if (arena->spans.empty()) return Refuse("nothing was reserved");
+  if (arena->base != nullptr) return Refuse("commit refused: the arena has been committed before");
+  if (arena->spans.empty()) return Refuse("commit refused: the arena holds no reservation");
   arena->bytes = AlignUp(arena->cursor, kArenaAlign);
   arena->base = BackendAlloc(arena, arena->bytes);  // ONE allocation, zero-filled
   if (arena->base == nullptr) return B200KV_ERR_RUNTIME;
@@ -252,6 +253,49 @@ extern "C" int32_t b200kv_kv_cache_reserve(b200kv_arena* arena, int64_t max_cont
   out->latent_handle = b200kv_arena_reserve(arena, "kv.latent_cache", static_cast<size_t>(plan.latent_bytes), 0);
   out->rope_handle = b200kv_arena_reserve(arena, "kv.rope_cache", static_cast<size_t>(plan.rope_bytes), 0);
   if (out->block_table_handle < 0 || out->slot_mapping_handle < 0 || out->latent_handle < 0 || out->rope_handle < 0) {
+    return B200KV_ERR_INVALID;
+  }
+  out->max_blocks_per_seq = plan.blocks_per_layer;
+  out->seq_lens_handle = -1;
+  return B200KV_OK;
+}
+
+extern "C" int32_t b200kv_kv_cache_reserve_batched(b200kv_arena* arena, int64_t num_blocks, int64_t block_size,
+                                                   int64_t layers, int64_t max_seqs, int64_t max_blocks_per_seq,
+                                                   int64_t tokens_per_step, b200kv_kv_cache* out) {
+  if (arena == nullptr || out == nullptr) {
+    SetLastError("kv_cache_reserve_batched: null arena or out");
+    return B200KV_ERR_NULLPTR;
+  }
+  if (num_blocks <= 0 || block_size <= 0 || layers <= 0 || max_seqs <= 0 || max_blocks_per_seq <= 0 ||
+      tokens_per_step <= 0 || num_blocks * block_size > INT32_MAX) {
+    SetLastError("kv_cache_reserve_batched refused: blocks %lld x %lld rows, layers %lld, sequences %lld, blocks per "
+                 "sequence %lld, tokens per step %lld",
+                 static_cast<long long>(num_blocks), static_cast<long long>(block_size), static_cast<long long>(layers),
+                 static_cast<long long>(max_seqs), static_cast<long long>(max_blocks_per_seq),
+                 static_cast<long long>(tokens_per_step));
+    return B200KV_ERR_INVALID;
+  }
+  std::memset(out, 0, sizeof(*out));
+  b200kv_reservation& plan = out->geometry;
+  plan.blocks_per_layer = num_blocks;
+  plan.total_blocks = num_blocks * layers;
+  plan.latent_bytes = layers * num_blocks * block_size * B200KV_LATENT_DIM * 2;
+  plan.rope_bytes = layers * num_blocks * block_size * B200KV_ROPE_DIM * 2;
+  plan.block_table_bytes = max_seqs * max_blocks_per_seq * 4;
+  plan.slot_mapping_bytes = tokens_per_step * 4;
+  out->layers = layers;
+  out->block_size = block_size;
+  out->max_seqs = max_seqs;
+  out->max_blocks_per_seq = max_blocks_per_seq;
+  // The reference's four spans under its names and in its order, and the lengths beside the table.
+  out->block_table_handle = b200kv_arena_reserve(arena, "kv.block_table", static_cast<size_t>(plan.block_table_bytes), 0);
+  out->slot_mapping_handle = b200kv_arena_reserve(arena, "kv.slot_mapping", static_cast<size_t>(plan.slot_mapping_bytes), 0);
+  out->seq_lens_handle = b200kv_arena_reserve(arena, "kv.seq_lens", static_cast<size_t>(max_seqs) * 4, 0);
+  out->latent_handle = b200kv_arena_reserve(arena, "kv.latent_cache", static_cast<size_t>(plan.latent_bytes), 0);
+  out->rope_handle = b200kv_arena_reserve(arena, "kv.rope_cache", static_cast<size_t>(plan.rope_bytes), 0);
+  if (out->block_table_handle < 0 || out->slot_mapping_handle < 0 || out->seq_lens_handle < 0 || out->latent_handle < 0 ||
+      out->rope_handle < 0) {
     return B200KV_ERR_INVALID;
   }
   return B200KV_OK;

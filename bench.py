@@ -36,10 +36,24 @@ SCALE = 1.0 / 24.0      # 1/sqrt(576)
 SEED = 20251008
 METRIC = "decode attn tokens/s/GPU at B=32x4K ctx (43 layers: KV append + paged absorbed-MLA attention)"
 
+WORKLOAD_TEXT = ("configs[1]: B=32 x ctx 4096 per GPU, 43 layers, block 64, seeded permuted block tables, "
+                 "latent KV ~ N(0,1) bf16, 64 heads x 576")
+HBM_SPEC_GBS = 8000.0   # the nominal figure the goal is stated against; fractions are reported against both
+
 ATTN_BYTES_PER_LAUNCH = BATCH * CONTEXT * ROW * 2 + BATCH * HEADS * ROW * 2 + BATCH * HEADS * LATENT * 2
-# DRAM bytes of one decode launch from the committed ncu capture (dram__bytes_read.sum + dram__bytes_write.sum).
+# DRAM bytes of one attention launch (decode + finalize kernels) from the committed ncu capture of the 2-layer
+# case (dram__bytes_read.sum + dram__bytes_write.sum, profiles/mla_decode_tc_b32x4k_2layers.md). An annotation:
+# the achieved figure is computed from the algorithmic bytes above.
 NCU_DRAM_BYTES_PER_LAUNCH = 153_830_000 + 4_910_000
 ATTN_FLOPS_PER_LAUNCH = BATCH * CONTEXT * HEADS * (ROW + LATENT) * 2
+
+
+def host_threads() -> int:
+    """Host threads this process may use (torchrun exports OMP_NUM_THREADS=1, which is not the machine)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def measured_peaks():
@@ -113,7 +127,7 @@ def dist_env():
 
 
 # ---------------------------------------------------------------------------------------------------
-# CPU reference arm: the oracle (the reference's own operators are closed binaries)
+# CPU reference arm: the oracle port (the reference's own operators for this path are closed binaries)
 # ---------------------------------------------------------------------------------------------------
 class CpuSampler:
     """Times the oracle's append + attention on a bounded sample of the step: `layers` layers x `seqs`
@@ -125,6 +139,7 @@ class CpuSampler:
         import kvo
 
         self.np, self.kvo = np, kvo
+        kvo.lib().kvo_set_num_threads(host_threads())  # every host thread, whatever the launcher exported
         self.threads = int(kvo.lib().kvo_num_threads())
         self.blocks = CONTEXT // BLOCK
         self._data = {}
@@ -192,7 +207,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * BATCH / value,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "configs[1]: B=32 x ctx 4096, 43 layers, block 64, permuted block tables",
+        "config": {"workload": WORKLOAD_TEXT,
                    "arm": "CPU oracle port of the path (the reference's operators are closed CANN binaries); "
                           "each step is the bounded sample below"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": sampler.threads, "kind": "port",
@@ -207,7 +222,10 @@ def run_reference_arm(args):
 # B200 arm
 # ---------------------------------------------------------------------------------------------------
 class Workload:
-    """Device-resident state of configs[1] on one GPU."""
+    """Device-resident state of configs[1] on one GPU. Every buffer the path touches is carved from ONE device
+    allocation by the library's static arena, in the engine's order: reserve the KV spans (two layer-major caches,
+    block table, slots, lengths) and the step's activations, note the workspace, commit, seal; a layer's pool is
+    base + layer * bytes (b200kv_kv_cache_layer_view). torch only wraps the addresses."""
 
     def __init__(self, torch, b200kv, seed_offset: int = 0):
         import numpy as np
@@ -218,79 +236,93 @@ class Workload:
         blocks_per_seq = CONTEXT // BLOCK
         self.blocks = BATCH * blocks_per_seq
         rows = self.blocks * BLOCK
-        self.pool = torch.empty((LAYERS, rows, ROW), dtype=torch.bfloat16, device="cuda")
-        b200kv.fill_normal_bf16(self.pool, SEED + seed_offset, kvo.STREAM_KV)
+        arena = b200kv.Arena(b200kv.ARENA_DEVICE)
+        cache = arena.reserve_kv_cache_batched(self.blocks, BLOCK, LAYERS, BATCH, blocks_per_seq, BATCH)
+        h_q = arena.reserve("attn.q", LAYERS * BATCH * HEADS * ROW * 2)
+        h_new = arena.reserve("attn.new_rows", LAYERS * BATCH * ROW * 2)
+        h_out = arena.reserve("attn.out", LAYERS * BATCH * HEADS * LATENT * 2)
+        h_status = arena.reserve("attn.status", 16)
+        arena.note_workspace(b200kv.decode_workspace_bytes(BATCH, HEADS))
+        arena.commit()
+        arena.commit_workspace()
+        arena.seal()
+        if arena.allocations != 2:
+            raise RuntimeError(f"the arena made {arena.allocations} allocations (one for the spans, one workspace expected)")
+        self.arena, self.cache = arena, cache
+        bf16, i32 = torch.bfloat16, torch.int32
+        self.latent = arena.tensor(cache.latent_handle, (LAYERS, rows, LATENT), bf16)
+        self.rope = arena.tensor(cache.rope_handle, (LAYERS, rows, ROW - LATENT), bf16)
+        self.table = arena.tensor(cache.block_table_handle, (BATCH, blocks_per_seq), i32)
+        self.slots = arena.tensor(cache.slot_mapping_handle, (BATCH,), i32)
+        self.kv_len = arena.tensor(cache.seq_lens_handle, (BATCH,), i32)
+        self.q = arena.tensor(h_q, (LAYERS, BATCH, HEADS, ROW), bf16)
+        self.new_rows = arena.tensor(h_new, (LAYERS, BATCH, ROW), bf16)
+        self.out = arena.tensor(h_out, (LAYERS, BATCH, HEADS, LATENT), bf16)
+        self.status = arena.tensor(h_status, (4,), i32)
+        self.ws = b200kv.device_tensor(arena.workspace, (arena.workspace_bytes,), torch.uint8)
+        b200kv.fill_normal_bf16(self.latent, SEED + seed_offset, kvo.STREAM_KV)
+        b200kv.fill_normal_bf16(self.rope, SEED + seed_offset, kvo.STREAM_KV + 64)
         table = kvo.permutation(self.blocks, seed=SEED + seed_offset).reshape(BATCH, blocks_per_seq)
         self.table_np = table
-        self.table = torch.from_numpy(table).cuda()
-        self.kv_len = torch.full((BATCH,), CONTEXT, dtype=torch.int32, device="cuda")
+        self.table.copy_(torch.from_numpy(table).cuda())
+        self.kv_len.fill_(CONTEXT)
         slots = (table[:, -1].astype(np.int64) * BLOCK + (CONTEXT - 1) % BLOCK).astype(np.int32)
         self.slots_np = slots
-        self.slots = torch.from_numpy(slots).cuda()
-        self.q = torch.empty((LAYERS, BATCH, HEADS, ROW), dtype=torch.bfloat16, device="cuda")
+        self.slots.copy_(torch.from_numpy(slots).cuda())
         b200kv.fill_normal_bf16(self.q, SEED + seed_offset, kvo.STREAM_Q, 0, SCALE)
-        self.new_rows = torch.empty((LAYERS, BATCH, ROW), dtype=torch.bfloat16, device="cuda")
         b200kv.fill_normal_bf16(self.new_rows, SEED + seed_offset, kvo.STREAM_NEW)
-        self.out = torch.empty((LAYERS, BATCH, HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
-        self.ws = torch.empty(b200kv.decode_workspace_bytes(BATCH, HEADS), dtype=torch.uint8, device="cuda")
-        self.status = b200kv.new_status()
-        self.views = [b200kv.pool_view(self.pool[layer]) for layer in range(LAYERS)]
+        self.views = [arena.layer_view(cache, layer) for layer in range(LAYERS)]
         self.launches = 0
 
-    def layer(self, layer: int, q, new_rows, out, variant, stream=None):
-        kv = self.kv
-        kv.append(self.views[layer], new_rows[:, :LATENT], new_rows[:, LATENT:], self.slots, status=self.status,
-                  stream=stream)
-        kv.mla_decode(q, self.views[layer], self.table, self.kv_len, BLOCK, SCALE, out=out, workspace=self.ws,
-                      variant=variant, status=self.status, stream=stream)
-        self.launches += 3  # append, decode, finalize
+    def close(self):
+        self.torch.cuda.synchronize()
+        for name in ("latent", "rope", "table", "slots", "kv_len", "q", "new_rows", "out", "status", "ws"):
+            setattr(self, name, None)
+        self.arena.close()
 
-    def step_resident(self, variant, events=None, fused=False):
+    def step_resident(self, variant, fused=False):
         """43 layers of append + attention. fused: the append rides in the attention launch (the decode kernel
         writes each sequence's new row before it reads that tile) instead of a launch of its own."""
-        torch = self.torch
         for layer in range(LAYERS):
             new = self.new_rows[layer]
             if not fused:
                 self.kv.append(self.views[layer], new[:, :LATENT], new[:, LATENT:], self.slots, status=self.status)
-            if events is not None:
-                e0 = torch.cuda.Event(enable_timing=True)
-                e1 = torch.cuda.Event(enable_timing=True)
-                e0.record()
             self.kv.mla_decode(self.q[layer], self.views[layer], self.table, self.kv_len, BLOCK, SCALE,
                                out=self.out[layer], workspace=self.ws, variant=variant, status=self.status,
                                new_rows=(new[:, :LATENT], new[:, LATENT:]) if fused else None,
                                stable_tables=True)  # table and lengths are uploaded before the step
-            if events is not None:
-                e1.record()
-                events.append((e0, e1))
             self.launches += 2 if fused else 3
 
 
 def check_against_oracle(torch, b200kv, wl: Workload, variant) -> float:
-    """One sequence of one layer, copied back and recomputed by the oracle."""
+    """Two sequences of one layer, copied back and recomputed by the oracle (the GPU tests hold all 32)."""
     import numpy as np
 
     import kvo
 
-    layer, b = min(7, LAYERS - 1), 5
+    layer = min(7, LAYERS - 1)
     wl.step_resident(variant)
     torch.cuda.synchronize()
-    rows = (wl.table_np[b].astype(np.int64)[:, None] * BLOCK + np.arange(BLOCK)[None, :]).reshape(-1)
-    kv_rows = wl.pool[layer][torch.from_numpy(rows).cuda()].contiguous()
-    pool_np = kv_rows.view(torch.int16).cpu().numpy().view(np.uint16)
-    q_np = wl.q[layer, b].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)[None]
-    table = np.arange(CONTEXT // BLOCK, dtype=np.int32)[None]
-    want, _ = kvo.mla_decode(q_np, pool_np, table, np.array([CONTEXT], np.int32), BLOCK, SCALE, use_double=True)
-    got = wl.out[layer, b].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
-    err = float(np.abs(kvo.bf16_to_f32(got) - kvo.bf16_to_f32(want[0])).max())
-    if not err <= 2e-3:
-        raise RuntimeError(f"bench self-check failed: attention differs from the oracle by {err:.3e}")
-    # the appended row is in the pool, bit for bit
-    slot = int(wl.slots_np[b])
-    if not torch.equal(wl.pool[layer, slot].view(torch.int16), wl.new_rows[layer, b].view(torch.int16)):
-        raise RuntimeError("bench self-check failed: appended row not found in the pool")
-    return err
+    worst = 0.0
+    for b in (5, 31):
+        rows = (wl.table_np[b].astype(np.int64)[:, None] * BLOCK + np.arange(BLOCK)[None, :]).reshape(-1)
+        idx = torch.from_numpy(rows).cuda()
+        kv_rows = torch.cat([wl.latent[layer][idx], wl.rope[layer][idx]], dim=1).contiguous()
+        pool_np = kv_rows.view(torch.int16).cpu().numpy().view(np.uint16)
+        q_np = wl.q[layer, b].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)[None]
+        table = np.arange(CONTEXT // BLOCK, dtype=np.int32)[None]
+        want, _ = kvo.mla_decode(q_np, pool_np, table, np.array([CONTEXT], np.int32), BLOCK, SCALE, use_double=True)
+        got = wl.out[layer, b].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        err = float(np.abs(kvo.bf16_to_f32(got) - kvo.bf16_to_f32(want[0])).max())
+        if not err <= 2e-3:
+            raise RuntimeError(f"bench self-check failed: attention differs from the oracle by {err:.3e}")
+        worst = max(worst, err)
+        # the appended row is in the pool, bit for bit
+        slot = int(wl.slots_np[b])
+        got_row = torch.cat([wl.latent[layer, slot], wl.rope[layer, slot]])
+        if not torch.equal(got_row.view(torch.int16), wl.new_rows[layer, b].view(torch.int16)):
+            raise RuntimeError("bench self-check failed: appended row not found in the pool")
+    return worst
 
 
 def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph: bool = True):
@@ -421,6 +453,311 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
     return res
 
 
+def capture(torch, fn, warm: int = 1):
+    """Runs fn once on a side stream (lazy initialisations), then captures it in a CUDA graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(warm):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return graph
+
+
+def timed(torch, run, steps: int, barrier):
+    """Milliseconds for `steps` calls of run(), CUDA events on the current stream, a barrier on both sides."""
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1)
+
+
+def measure_e2e(torch, b200kv, wl, variant, fused, args, barrier):
+    """The step through the C ABI with HOST buffers: every layer's inputs (q and the new rows, one contiguous
+    pinned block and one copy per layer) come up from pinned memory and every layer's output goes back, on
+    three streams with four device buffers per direction, captured as one graph. Also measures the same copies
+    with no kernels between them: the floor the host link sets for this step at this rank count."""
+    n_buf = 4
+    in_elems = BATCH * HEADS * ROW + BATCH * ROW
+    out_elems = BATCH * HEADS * LATENT
+    bf16 = torch.bfloat16
+    h_in = torch.empty((LAYERS, in_elems), dtype=bf16).pin_memory()
+    h_out = torch.empty((LAYERS, out_elems), dtype=bf16).pin_memory()
+    h_slots = torch.from_numpy(wl.slots_np).pin_memory()
+    h_in[:, :BATCH * HEADS * ROW].copy_(wl.q.reshape(LAYERS, -1).cpu())
+    h_in[:, BATCH * HEADS * ROW:].copy_(wl.new_rows.reshape(LAYERS, -1).cpu())
+    d_in = [torch.empty(in_elems, dtype=bf16, device="cuda") for _ in range(n_buf)]
+    d_out = [torch.empty((BATCH, HEADS, LATENT), dtype=bf16, device="cuda") for _ in range(n_buf)]
+    d_slots = torch.empty_like(wl.slots)
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def step(with_kernels: bool):
+        compute = torch.cuda.current_stream()
+        in_free, out_free = [None] * n_buf, [None] * n_buf
+        copy_in.wait_stream(compute)
+        copy_out.wait_stream(compute)
+        with torch.cuda.stream(copy_in):
+            d_slots.copy_(h_slots, non_blocking=True)
+        for layer in range(LAYERS):
+            s = layer % n_buf
+            with torch.cuda.stream(copy_in):
+                if in_free[s] is not None:
+                    copy_in.wait_event(in_free[s])
+                d_in[s].copy_(h_in[layer], non_blocking=True)
+                in_ready = torch.cuda.Event()
+                in_ready.record(copy_in)
+            compute.wait_event(in_ready)
+            if out_free[s] is not None:
+                compute.wait_event(out_free[s])
+            if with_kernels:
+                q = d_in[s][:BATCH * HEADS * ROW].view(BATCH, HEADS, ROW)
+                new = d_in[s][BATCH * HEADS * ROW:].view(BATCH, ROW)
+                if not fused:
+                    wl.kv.append(wl.views[layer], new[:, :LATENT], new[:, LATENT:], d_slots, status=wl.status)
+                wl.kv.mla_decode(q, wl.views[layer], wl.table, wl.kv_len, BLOCK, SCALE, out=d_out[s], workspace=wl.ws,
+                                 variant=variant, status=wl.status,
+                                 new_rows=(new[:, :LATENT], new[:, LATENT:]) if fused else None, stable_tables=True)
+            in_free[s] = torch.cuda.Event()
+            in_free[s].record(compute)
+            out_ready = torch.cuda.Event()
+            out_ready.record(compute)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(out_ready)
+                h_out[layer].copy_(d_out[s].view(-1), non_blocking=True)
+                out_free[s] = torch.cuda.Event()
+                out_free[s].record(copy_out)
+        compute.wait_stream(copy_in)
+        compute.wait_stream(copy_out)
+
+    g_e2e = capture(torch, lambda: step(True))
+    g_floor = capture(torch, lambda: step(False))
+    for _ in range(max(3, args.warmup // 2)):
+        g_e2e.replay()
+    ms_e2e = timed(torch, g_e2e.replay, args.steps, barrier)
+    # the read-back result is the device result, bit for bit
+    if not torch.equal(h_out[LAYERS - 1].view(torch.int16), wl.out[LAYERS - 1].reshape(-1).cpu().view(torch.int16)):
+        raise RuntimeError("bench self-check failed: end-to-end output differs from the resident run")
+    for _ in range(3):
+        g_floor.replay()
+    ms_floor = timed(torch, g_floor.replay, args.steps, barrier)
+    return ms_e2e, ms_floor
+
+
+# ---------------------------------------------------------------------------------------------------
+# The two multi-GPU configurations: legs of the default run (a few layers resident) and, with --workload,
+# runs of their own
+# ---------------------------------------------------------------------------------------------------
+def leg_ragged(torch, dist, b200kv, layers: int, steps: int, use_graph: bool = True):
+    """configs[2]: 256 ragged sequences (lengths 512..32768 from a seed) partitioned over the ranks by length
+    (no data-path collective), fragmented tables, 16 consecutive decode steps per run with the append fused
+    into each attention launch. Three of rank 0's sequences are checked against the oracle."""
+    import numpy as np
+
+    import kvo
+    import scenarios
+    from b200kv import dist as kvdist
+
+    rank, world, _ = dist_env()
+    hbm_peak, _, peak_kind = measured_peaks()
+    status = b200kv.new_status()
+    lens_all = scenarios.ragged_lengths(256, 512, 32768)
+    ranks, loads = kvdist.partition_sequences(lens_all, world)
+    kv_len_np = lens_all[ranks == rank].astype(np.int32)
+    nseq = len(kv_len_np)
+    decode_steps = 16
+    blocks = int(sum(scenarios.blocks_for(int(n) + decode_steps, BLOCK) for n in kv_len_np)) + 8
+    table_np = scenarios.fragmented_tables(kv_len_np + decode_steps, BLOCK, blocks)
+    pool = torch.empty((layers, blocks * BLOCK, ROW), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(pool, SEED + rank, kvo.STREAM_KV)
+    q = torch.empty((nseq, HEADS, ROW), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(q, SEED + rank, kvo.STREAM_Q, 0, SCALE)
+    new = torch.empty((nseq, ROW), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(new, SEED + rank, kvo.STREAM_NEW)
+    out = torch.empty((nseq, HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
+    table = torch.from_numpy(table_np).cuda()
+    views = [b200kv.pool_view(pool[l]) for l in range(layers)]
+    ws = torch.empty(b200kv.decode_workspace_bytes(nseq), dtype=torch.uint8, device="cuda")
+    # lengths of each of the 16 consecutive decode steps (the new token included), precomputed on the device
+    lens_steps = [torch.from_numpy(kv_len_np + i + 1).cuda() for i in range(decode_steps)]
+
+    def step():
+        for i in range(decode_steps):
+            for l in range(layers):
+                b200kv.mla_decode(q, views[l], table, lens_steps[i], BLOCK, SCALE, out=out, workspace=ws, status=status,
+                                  new_rows=(new[:, :LATENT], new[:, LATENT:]), stable_tables=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    run = capture(torch, step).replay if use_graph else step
+    for _ in range(2):
+        run()
+    ms = timed(torch, run, steps, barrier) / steps
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    st = status.cpu().tolist()
+    if st[0] != 0:
+        raise RuntimeError(f"ragged leg: device status word reports {st}")
+    err = None
+    if rank == 0:
+        # the last layer's output of the last decode step, three sequences, against the oracle
+        final_len = kv_len_np + decode_steps
+        err = 0.0
+        for b in (0, nseq // 2, nseq - 1):
+            n = int(final_len[b])
+            tok = np.arange(n)
+            rows = table_np[b, tok // BLOCK].astype(np.int64) * BLOCK + tok % BLOCK
+            kv_rows = pool[layers - 1][torch.from_numpy(rows).cuda()].contiguous()
+            pool_np = kv_rows.view(torch.int16).cpu().numpy().view(np.uint16)
+            q_np = q[b].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)[None]
+            ident = np.arange(scenarios.blocks_for(n, BLOCK), dtype=np.int32)[None]
+            want, _ = kvo.mla_decode(q_np, pool_np, ident, np.array([n], np.int32), BLOCK, SCALE, use_double=True)
+            got = out[b].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+            err = max(err, float(np.abs(kvo.bf16_to_f32(got) - kvo.bf16_to_f32(want[0])).max()))
+        if not err <= 2e-3:
+            raise RuntimeError(f"ragged leg: attention differs from the oracle by {err:.3e}")
+    scale43 = 43.0 / layers
+    tokens = float(sum(int((lens_all + i + 1).sum()) for i in range(decode_steps)))
+    my_bytes = float(sum(int((kv_len_np + i + 1).sum()) for i in range(decode_steps))) * ROW * 2 * layers
+    gbs = my_bytes / (ms * 1e-3) * 1e-9
+    del pool
+    return {
+        "workload": (f"configs[2]: 256 sequences, lengths 512..32768 (seeded), partitioned over {world} rank(s) by "
+                     f"length (rank 0 holds {nseq}, load imbalance {loads.max() / loads.mean():.4f}), fragmented "
+                     f"tables, {decode_steps} decode steps per run with the append fused into each launch"),
+        "layers_resident": layers, "value": 256 * decode_steps / (ms * scale43 * 1e-3), "unit": "tokens/s",
+        "ms_per_run_43_layers": ms * scale43, "context_tokens_per_run": tokens,
+        "rank0_hbm_gbs": gbs, "rank0_frac_of_measured_hbm": gbs / hbm_peak, "peak_kind": peak_kind,
+        "max_abs_err": err, "scaling": "strong",
+    }
+
+
+def leg_longctx(torch, dist, b200kv, layers: int, steps: int, exchange_kind: str = "peer", use_graph: bool = True):
+    """configs[3]: one sequence of 262,144 tokens split by KV range over the ranks; every layer ends with the
+    exchange of the ranks' partials (peer memory over NVLink, or an NCCL all-gather) and the log-sum-exp merge.
+    Rank 0 checks layer 0 against the oracle on 8 heads over the whole sequence."""
+    import numpy as np
+
+    import kvo
+    import scenarios
+    from b200kv import dist as kvdist
+
+    rank, world, _ = dist_env()
+    hbm_peak, _, peak_kind = measured_peaks()
+    status = b200kv.new_status()
+    n = 262144
+    begin, length = kvdist.split_kv_range(n, BLOCK, world, rank)
+    my_blocks = scenarios.blocks_for(length, BLOCK)
+    total_blocks = n // BLOCK
+    # this rank's pool holds only its block range; its table column j maps block begin / BLOCK + j
+    table_np = np.zeros((1, total_blocks), dtype=np.int32)
+    table_np[0, begin // BLOCK: begin // BLOCK + my_blocks] = kvo.permutation(my_blocks, seed=SEED + rank)
+    pool = torch.empty((layers, my_blocks * BLOCK, ROW), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(pool, SEED + rank, kvo.STREAM_KV)
+    q = torch.empty((1, HEADS, ROW), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(q, SEED, kvo.STREAM_Q, 0, SCALE)
+    table = torch.from_numpy(table_np).cuda()
+    lens = torch.tensor([length], dtype=torch.int32, device="cuda")
+    begins = torch.tensor([begin], dtype=torch.int32, device="cuda")
+    views = [b200kv.pool_view(pool[l]) for l in range(layers)]
+    ws = torch.empty(b200kv.decode_workspace_bytes(1), dtype=torch.uint8, device="cuda")
+    po = torch.empty((HEADS, LATENT), dtype=torch.float32, device="cuda")
+    pm = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
+    pl = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
+    out = torch.empty((layers, HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
+    exchange = kvdist.PeerExchange(HEADS) if exchange_kind == "peer" else None
+
+    def decode(l):
+        b200kv.mla_decode(q, views[l], table, lens, BLOCK, SCALE, kv_begin=begins,
+                          partial=(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS)), workspace=ws,
+                          status=status, stable_tables=True)
+
+    def step():
+        for l in range(layers):
+            decode(l)
+            if exchange is not None:
+                exchange.merge(po, pm, pl, out[l], lse, status=status)
+            elif world > 1:
+                kvdist.merge_across_ranks(po, pm, pl, out[l], lse)
+            else:
+                b200kv.lse_merge(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS), out[l], lse)
+
+    def decode_only():
+        for l in range(layers):
+            decode(l)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    graphs = use_graph and not (exchange is None and world > 1)  # NCCL calls are launched eagerly
+    run = capture(torch, step).replay if graphs else step
+    run_decode = capture(torch, decode_only).replay if graphs else decode_only
+    for _ in range(3):
+        run()
+    barrier()
+    t = torch.tensor([timed(torch, run, steps, barrier) / steps, timed(torch, run_decode, steps, barrier) / steps],
+                     dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_decode = (float(x) for x in t.cpu())
+    st = status.cpu().tolist()
+    if st[0] != 0:
+        raise RuntimeError(f"longctx leg: device status word reports {st}")
+    err = None
+    if rank == 0:
+        # Layer 0 of every rank's shard regenerated on the host (the device generator and the oracle's agree bit
+        # for bit), the whole sequence attended by the oracle on 8 heads.
+        kvo.lib().kvo_set_num_threads(host_threads())
+        shards, tables = [], []
+        row_base = 0
+        for r in range(world):
+            _, r_len = kvdist.split_kv_range(n, BLOCK, world, r)
+            r_blocks = scenarios.blocks_for(r_len, BLOCK)
+            shards.append(kvo.normal_bf16(r_blocks * BLOCK * ROW, kvo.STREAM_KV, seed=SEED + r).reshape(-1, ROW))
+            tables.append(kvo.permutation(r_blocks, seed=SEED + r).astype(np.int64) + row_base // BLOCK)
+            row_base += r_blocks * BLOCK
+        pool_np = np.concatenate(shards)
+        table_all = np.concatenate(tables).astype(np.int32)[None]
+        heads = np.arange(0, HEADS, 8)
+        q_np = q.view(torch.int16).cpu().numpy().view(np.uint16)
+        want, _ = kvo.mla_decode(q_np[:, heads], pool_np, table_all, np.array([n], np.int32), BLOCK, SCALE)
+        got = out[0].view(torch.int16).cpu().numpy().view(np.uint16)[heads]
+        err = float(np.abs(kvo.bf16_to_f32(got) - kvo.bf16_to_f32(want[0])).max())
+        if not err <= 2e-3:
+            raise RuntimeError(f"longctx leg: attention differs from the oracle by {err:.3e}")
+    if exchange is not None:
+        barrier()
+        exchange.close()
+    scale43 = 43.0 / layers
+    gbs = float(length) * ROW * 2 * layers / (ms * 1e-3) * 1e-9
+    how = ("partials pushed into every rank's inbox over peer memory (NVLink) and merged by the same kernel"
+           if exchange is not None else "all-gather of 131,584-byte partials (NCCL) + LSE merge")
+    del pool
+    return {
+        "workload": (f"configs[3]: one sequence of {n} tokens split by KV range over {world} rank(s) ({length} tokens "
+                     f"on rank 0); per layer: decode of the shard, then {how}"),
+        "layers_resident": layers, "ms_per_step_43_layers": ms * scale43, "value": 1.0 / (ms * scale43 * 1e-3),
+        "unit": "tokens/s", "us_per_layer": ms * 1e3 / layers, "decode_us_per_layer": ms_decode * 1e3 / layers,
+        "exchange_us_per_layer": (ms - ms_decode) * 1e3 / layers, "rank0_hbm_gbs": gbs,
+        "rank0_frac_of_measured_hbm": gbs / hbm_peak, "peak_kind": peak_kind, "max_abs_err": err, "scaling": "strong",
+    }
+
+
 def run_b200_arm(args):
     import torch
     import torch.distributed as dist
@@ -447,25 +784,21 @@ def run_b200_arm(args):
             wl.kv.mla_decode(wl.q[layer], wl.views[layer], wl.table, wl.kv_len, BLOCK, SCALE, out=wl.out[layer],
                              workspace=wl.ws, variant=variant, status=wl.status, stable_tables=True)
 
-    # The 43-layer step is launch-bound from Python (about 15 us of interpreter time per C-ABI call), so the
-    # step is captured once in a CUDA graph and replayed: the timed region holds kernels only.
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
     fused = args.variant != "simt" and not args.separate_append
     if fused:
         # The fused append must leave the pool as the append kernel does: one layer, bit for bit.
-        wl.pool[0].index_fill_(0, wl.slots.long(), 0)
+        wl.latent[0].index_fill_(0, wl.slots.long(), 0)
+        wl.rope[0].index_fill_(0, wl.slots.long(), 0)
         new0 = wl.new_rows[0]
         b200kv.mla_decode(wl.q[0], wl.views[0], wl.table, wl.kv_len, BLOCK, SCALE, out=wl.out[0], workspace=wl.ws,
                           variant=variant, status=wl.status, new_rows=(new0[:, :LATENT], new0[:, LATENT:]))
         torch.cuda.synchronize()
-        if not torch.equal(wl.pool[0][wl.slots.long()].view(torch.int16), new0.view(torch.int16)):
+        got0 = torch.cat([wl.latent[0][wl.slots.long()], wl.rope[0][wl.slots.long()]], dim=1)
+        if not torch.equal(got0.view(torch.int16), new0.view(torch.int16)):
             raise RuntimeError("fused append: the pool rows differ from the appended rows")
-    with torch.cuda.stream(side):
-        wl.step_resident(variant, fused=fused)
-        attention_only()
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
+
+    # The 43-layer step is launch-bound from Python (about 15 us of interpreter time per C-ABI call), so the
+    # step is captured once in a CUDA graph and replayed: the timed region holds kernels only.
     class Eager:
         def __init__(self, fn):
             self.fn = fn
@@ -474,14 +807,12 @@ def run_b200_arm(args):
             self.fn()
 
     if args.no_graph:
+        wl.step_resident(variant, fused=fused)
+        attention_only()
         g_step, g_attn = Eager(lambda: wl.step_resident(variant, fused=fused)), Eager(attention_only)
     else:
-        g_step = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_step):
-            wl.step_resident(variant, fused=fused)
-        g_attn = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_attn):
-            attention_only()
+        g_step = capture(torch, lambda: wl.step_resident(variant, fused=fused))
+        g_attn = capture(torch, attention_only)
     launches_per_step = LAYERS * (2 if fused else 3)  # (append,) decode, finalize/merge per layer
 
     # ---- device-resident timing (value) ----
@@ -491,133 +822,52 @@ def run_b200_arm(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        g_step.replay()
-    t1.record()
-    barrier()
-    ms_total = t0.elapsed_time(t1)
+    ms_total = timed(torch, g_step.replay, args.steps, barrier)
     # the dominant kernel alone: 43 attention launches (one per layer pool) per replay
-    a0 = torch.cuda.Event(enable_timing=True)
-    a1 = torch.cuda.Event(enable_timing=True)
     g_attn.replay()
-    a0.record()
-    for _ in range(args.steps):
-        g_attn.replay()
-    a1.record()
-    barrier()
+    attn_ms = timed(torch, g_attn.replay, args.steps, barrier) / (args.steps * LAYERS)
     clocks = sampler.stop() if rank == 0 else None
-    attn_ms = a0.elapsed_time(a1) / (args.steps * LAYERS)
     st = wl.status.cpu().tolist()
     if st[0] != 0:
         raise RuntimeError(f"device status word reports {st}")
 
-    def measure_e2e():
-        # ---- end-to-end timing through the C ABI with host buffers (e2e) ----
-        h_q = torch.empty((LAYERS, BATCH, HEADS, ROW), dtype=torch.bfloat16).pin_memory()
-        h_new = torch.empty((LAYERS, BATCH, ROW), dtype=torch.bfloat16).pin_memory()
-        h_slots = torch.from_numpy(wl.slots_np).pin_memory()
-        h_out = torch.empty((LAYERS, BATCH, HEADS, LATENT), dtype=torch.bfloat16).pin_memory()
-        h_q.copy_(wl.q.cpu())
-        h_new.copy_(wl.new_rows.cpu())
-        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-        d_q = [torch.empty_like(wl.q[0]) for _ in range(2)]
-        d_new = [torch.empty_like(wl.new_rows[0]) for _ in range(2)]
-        d_out = [torch.empty_like(wl.out[0]) for _ in range(2)]
-        d_slots = torch.empty_like(wl.slots)
-
-        def step_e2e():
-            # Layer l's inputs are uploaded on one stream while layer l-1 computes and layer l-2's result is
-            # read back on a third; two buffers per direction. Every byte the step consumes starts in pinned
-            # host memory and every result ends there.
-            compute = torch.cuda.current_stream()
-            in_ready = [None, None]
-            in_free = [None, None]
-            out_ready = [None, None]
-            out_free = [None, None]
-            copy_in.wait_stream(compute)
-            copy_out.wait_stream(compute)
-            with torch.cuda.stream(copy_in):
-                d_slots.copy_(h_slots, non_blocking=True)
-            for layer in range(LAYERS):
-                s = layer & 1
-                with torch.cuda.stream(copy_in):
-                    if in_free[s] is not None:
-                        copy_in.wait_event(in_free[s])
-                    d_q[s].copy_(h_q[layer], non_blocking=True)
-                    d_new[s].copy_(h_new[layer], non_blocking=True)
-                    in_ready[s] = torch.cuda.Event()
-                    in_ready[s].record(copy_in)
-                compute.wait_event(in_ready[s])
-                if out_free[s] is not None:
-                    compute.wait_event(out_free[s])
-                if not fused:
-                    wl.kv.append(wl.views[layer], d_new[s][:, :LATENT], d_new[s][:, LATENT:], d_slots, status=wl.status)
-                wl.kv.mla_decode(d_q[s], wl.views[layer], wl.table, wl.kv_len, BLOCK, SCALE, out=d_out[s],
-                                 workspace=wl.ws, variant=variant, status=wl.status,
-                                 new_rows=(d_new[s][:, :LATENT], d_new[s][:, LATENT:]) if fused else None,
-                                 stable_tables=True)
-                in_free[s] = torch.cuda.Event()
-                in_free[s].record(compute)
-                out_ready[s] = torch.cuda.Event()
-                out_ready[s].record(compute)
-                with torch.cuda.stream(copy_out):
-                    copy_out.wait_event(out_ready[s])
-                    h_out[layer].copy_(d_out[s], non_blocking=True)
-                    out_free[s] = torch.cuda.Event()
-                    out_free[s].record(copy_out)
-            compute.wait_stream(copy_in)
-            compute.wait_stream(copy_out)
-
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            step_e2e()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        g_e2e = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_e2e):
-            step_e2e()
-        for _ in range(max(1, args.warmup // 2)):
-            g_e2e.replay()
-        barrier()
-        e0 = torch.cuda.Event(enable_timing=True)
-        e1 = torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            g_e2e.replay()
-        e1.record()
-        barrier()
-        e2e_ms_total = e0.elapsed_time(e1)
-        # the read-back result is the device result, bit for bit
-        if not torch.equal(h_out[LAYERS - 1].view(torch.int16), wl.out[LAYERS - 1].cpu().view(torch.int16)):
-            raise RuntimeError("bench self-check failed: end-to-end output differs from the resident run")
-        return e2e_ms_total
-
-    e2e_ms_total = float('nan') if args.skip_e2e else measure_e2e()
+    e2e_ms_total, floor_ms_total = ((float('nan'), float('nan')) if args.skip_e2e
+                                    else measure_e2e(torch, b200kv, wl, variant, fused, args, barrier))
     h2d = LAYERS * (BATCH * HEADS * ROW * 2 + BATCH * ROW * 2) + BATCH * 4
     d2h = LAYERS * BATCH * HEADS * LATENT * 2
 
-    times = torch.tensor([ms_total, e2e_ms_total, attn_ms], dtype=torch.float64, device="cuda")
+    times = torch.tensor([ms_total, e2e_ms_total, attn_ms, floor_ms_total], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms_total, attn_ms = (float(x) for x in times.cpu())
+    ms_total, e2e_ms_total, attn_ms, floor_ms_total = (float(x) for x in times.cpu())
 
     move = (measure_move_kernels(torch, b200kv, wl, hbm_peak, use_graph=not args.no_graph)
             if (rank == 0 and not args.skip_move) else None)
+    wl.close()
+    del wl
+    torch.cuda.empty_cache()
+    # ---- the two multi-GPU configurations, a few layers each, as extra keys of the same line ----
+    legs = {}
+    if not args.skip_legs:
+        legs["longctx"] = leg_longctx(torch, dist, b200kv, layers=min(4, LAYERS), steps=10, use_graph=not args.no_graph)
+        torch.cuda.empty_cache()
+        legs["ragged"] = leg_ragged(torch, dist, b200kv, layers=min(2, LAYERS), steps=3, use_graph=not args.no_graph)
+        torch.cuda.empty_cache()
     if rank == 0:
         cpu_value, cpu_sample_desc, cpu_threads = (cpu_sample() if (world == 1 and not args.skip_cpu)
                                                     else (None, "skipped (rank 0 at N=1 only)", 0))
         ms_per_step = ms_total / args.steps
         value = world * BATCH / (ms_per_step * 1e-3)
         achieved = ATTN_BYTES_PER_LAUNCH / (attn_ms * 1e-3) * 1e-9
+        e2e_ms = None if args.skip_e2e else e2e_ms_total / args.steps
+        floor_ms = None if args.skip_e2e else floor_ms_total / args.steps
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[1]: B=32 x ctx 4096 per GPU, 43 layers, block 64, seeded permuted "
-                                   "block tables, latent KV ~ N(0,1) bf16, 64 heads x 576",
+            "config": {"workload": WORKLOAD_TEXT,
+                       "memory": "KV spans, activations and workspace carved from one arena allocation "
+                                 "(reserve / commit / seal); per-layer pool = base + layer * bytes",
                        "l2": "inputs larger than L2 (151 MB per layer, 6.49 GB pool walked layer by layer)",
                        "launch": "one CUDA graph replay per step (43 x decode with the append fused in + finalize)"
                                  if fused else "one CUDA graph replay per step (43 x append + decode + finalize)",
@@ -627,19 +877,24 @@ def run_b200_arm(args):
                          else "MlaDecodeSimtKernel + LseMergeKernel",
                          "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "peak_kind": peak_kind,
+                         "frac_of_8tbs_nominal": achieved / HBM_SPEC_GBS,
+                         "targets": {"attention_frac_asked": 0.60, "met": achieved / hbm_peak >= 0.60},
                          "traffic": NCU_DRAM_BYTES_PER_LAUNCH if args.variant != "simt" else None,
-                         "traffic_source": "ncu capture of MlaDecodeTcKernel at this workload's shape "
-                                           "(profiles/mla_decode_tc_b32x4k_2layers.md): DRAM read 153.83 MB "
-                                           "+ write 4.91 MB per launch",
+                         "traffic_source": "ncu capture of the attention launch at this workload's shape "
+                                           "(profiles/mla_decode_tc_b32x4k_2layers.md): dram__bytes_read.sum + "
+                                           "dram__bytes_write.sum per launch",
                          "algorithmic_bytes_per_launch": ATTN_BYTES_PER_LAUNCH, "us_per_launch": attn_ms * 1e3,
                          "tflops": ATTN_FLOPS_PER_LAUNCH / (attn_ms * 1e-3) * 1e-12,
                          "frac_of_measured_bf16_peak": ATTN_FLOPS_PER_LAUNCH / (attn_ms * 1e-3) * 1e-12 / tflops_peak},
             "move_kernels": move,
             "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": cpu_threads, "kind": "port",
                              "sample": cpu_sample_desc},
-            "e2e": {"value": None if args.skip_e2e else world * BATCH / (e2e_ms_total / args.steps * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": None if args.skip_e2e else e2e_ms_total / args.steps},
+            "e2e": {"value": None if args.skip_e2e else world * BATCH / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "copy_floor_ms": floor_ms,
+                    "copies": "one H2D (q and new rows, one pinned block) and one D2H per layer, four device "
+                              "buffers per direction; copy_floor_ms = the same copies with no kernels"},
+            "longctx": legs.get("longctx"), "ragged": legs.get("ragged"),
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
@@ -648,160 +903,33 @@ def run_b200_arm(args):
         dist.destroy_process_group()
 
 
-# ---------------------------------------------------------------------------------------------------
-# The two multi-GPU configurations (not the driver's default workload; run with --workload)
-# ---------------------------------------------------------------------------------------------------
 def run_extra_workload(args):
-    """--workload ragged : configs[2], 256 ragged sequences partitioned over the ranks by length
-                           (no collective), fragmented tables, 16 decode steps per timed run.
-       --workload longctx: configs[3], one 262,144-token sequence split by KV range over the ranks; every
-                           layer ends with an all-gather of the partials (NCCL) and the LSE merge."""
-    import numpy as np
+    """--workload ragged | longctx: one of the two multi-GPU configurations as a run of its own."""
     import torch
     import torch.distributed as dist
 
     import b200kv
-    import kvo
-    import scenarios
-    from b200kv import dist as kvdist
 
     rank, world, local = dist_env()
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
-    hbm_peak, _, peak_kind = measured_peaks()
-    layers = args.layers
-    status = b200kv.new_status()
-
     if args.workload == "ragged":
-        lens_all = scenarios.ragged_lengths(256, 512, 32768)
-        ranks, loads = kvdist.partition_sequences(lens_all, world)
-        kv_len_np = lens_all[ranks == rank].astype(np.int32)
-        nseq = len(kv_len_np)
-        blocks = int(sum(scenarios.blocks_for(int(n) + 16, BLOCK) for n in kv_len_np)) + 8
-        table_np = scenarios.fragmented_tables(kv_len_np + 16, BLOCK, blocks)
-        pool = torch.empty((layers, blocks * BLOCK, ROW), dtype=torch.bfloat16, device="cuda")
-        b200kv.fill_normal_bf16(pool, SEED + rank, kvo.STREAM_KV)
-        q = torch.empty((nseq, HEADS, ROW), dtype=torch.bfloat16, device="cuda")
-        b200kv.fill_normal_bf16(q, SEED + rank, kvo.STREAM_Q, 0, SCALE)
-        new = torch.empty((nseq, ROW), dtype=torch.bfloat16, device="cuda")
-        b200kv.fill_normal_bf16(new, SEED + rank, kvo.STREAM_NEW)
-        out = torch.empty((nseq, HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
-        table = torch.from_numpy(table_np).cuda()
-        views = [b200kv.pool_view(pool[l]) for l in range(layers)]
-        ws = torch.empty(b200kv.decode_workspace_bytes(nseq), dtype=torch.uint8, device="cuda")
-        decode_steps = 16
-        # lengths and slots of each of the 16 consecutive decode steps, precomputed on the device
-        lens_steps = [torch.from_numpy(kv_len_np + i + 1).cuda() for i in range(decode_steps)]
-        slots_steps = []
-        for i in range(decode_steps):
-            pos = kv_len_np.astype(np.int64) + i
-            slots_steps.append(torch.from_numpy(
-                (table_np[np.arange(nseq), pos // BLOCK].astype(np.int64) * BLOCK + pos % BLOCK).astype(np.int32)).cuda())
-
-        def step():
-            for i in range(decode_steps):
-                for l in range(layers):
-                    b200kv.append(views[l], new[:, :LATENT], new[:, LATENT:], slots_steps[i], status=status)
-                    b200kv.mla_decode(q, views[l], table, lens_steps[i], BLOCK, SCALE, out=out, workspace=ws,
-                                      status=status)
-        tokens_per_step = 256 * decode_steps
-        bytes_per_step = float(sum(int((kv_len_np + i + 1).sum()) for i in range(decode_steps))) * ROW * 2 * layers
-        desc = (f"configs[2]: 256 sequences, lengths 512..32768 (seeded), LPT partition over {world} rank(s) "
-                f"(rank 0 holds {nseq} sequences, load imbalance {loads.max() / loads.mean():.4f}), fragmented tables, "
-                f"{decode_steps} decode steps per run, {layers} of 43 layers resident")
+        res = leg_ragged(torch, dist, b200kv, args.layers, args.steps, use_graph=not args.no_graph)
+        ms = res["ms_per_run_43_layers"]
     else:
-        n = 262144
-        begin, length = kvdist.split_kv_range(n, BLOCK, world, rank)
-        my_blocks = scenarios.blocks_for(length, BLOCK)
-        total_blocks = n // BLOCK
-        # this rank's pool holds only its block range; its table column j maps block begin/BLOCK + j
-        table_np = np.zeros((1, total_blocks), dtype=np.int32)
-        table_np[0, begin // BLOCK: begin // BLOCK + my_blocks] = kvo.permutation(my_blocks, seed=SEED + rank)
-        pool = torch.empty((layers, my_blocks * BLOCK, ROW), dtype=torch.bfloat16, device="cuda")
-        b200kv.fill_normal_bf16(pool, SEED + rank, kvo.STREAM_KV)
-        q = torch.empty((1, HEADS, ROW), dtype=torch.bfloat16, device="cuda")
-        b200kv.fill_normal_bf16(q, SEED, kvo.STREAM_Q, 0, SCALE)
-        table = torch.from_numpy(table_np).cuda()
-        lens = torch.tensor([length], dtype=torch.int32, device="cuda")
-        begins = torch.tensor([begin], dtype=torch.int32, device="cuda")
-        views = [b200kv.pool_view(pool[l]) for l in range(layers)]
-        ws = torch.empty(b200kv.decode_workspace_bytes(1), dtype=torch.uint8, device="cuda")
-        po = torch.empty((HEADS, LATENT), dtype=torch.float32, device="cuda")
-        pm = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
-        pl = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
-        out = torch.empty((HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
-        lse = torch.empty((HEADS,), dtype=torch.float32, device="cuda")
-
-        exchange = kvdist.PeerExchange(HEADS) if args.exchange == "peer" else None
-
-        def step():
-            for l in range(layers):
-                b200kv.mla_decode(q, views[l], table, lens, BLOCK, SCALE, kv_begin=begins,
-                                  partial=(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS)),
-                                  workspace=ws, status=status)
-                if exchange is not None:
-                    exchange.merge(po, pm, pl, out, lse, status=status)
-                elif world > 1:
-                    kvdist.merge_across_ranks(po, pm, pl, out, lse)
-                else:
-                    b200kv.lse_merge(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS), out, lse)
-        tokens_per_step = 1
-        bytes_per_step = float(length) * ROW * 2 * layers  # this rank's shard: the roofline is per GPU
-        how = ("partials pushed into every rank's inbox over peer memory (NVLink), merged by a kernel that waits for "
-               "the peers' flags" if exchange is not None else "all-gather of 131,584-byte partials (NCCL) + LSE merge")
-        desc = (f"configs[3]: one sequence of {n} tokens split by KV range over {world} rank(s) "
-                f"({length} tokens on rank 0), per layer: {how}; {layers} of 43 layers")
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(1, args.warmup)):
-        step()
-    barrier()
-    run_step = step
-    use_graph = not args.no_graph and not (args.workload == "longctx" and args.exchange == "nccl" and world > 1)
-    if use_graph:
-        # One CUDA graph per step (a C-ABI call from Python costs more host time than these kernels run).
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            step()
-        torch.cuda.current_stream().wait_stream(side)
-        barrier()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        run_step = graph.replay
-        for _ in range(3):
-            run_step()
-        barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        run_step()
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / args.steps
-    st = status.cpu().tolist()
-    if st[0] != 0:
-        raise RuntimeError(f"device status word reports {st}")
+        res = leg_longctx(torch, dist, b200kv, args.layers, args.steps, args.exchange, use_graph=not args.no_graph)
+        ms = res["ms_per_step_43_layers"]
     if rank == 0:
-        scale43 = 43.0 / layers
-        gbs = bytes_per_step / (ms * 1e-3) * 1e-9
         print(json.dumps({
-            "metric": f"decode tokens/s ({args.workload})", "value": tokens_per_step / (ms * scale43 * 1e-3),
-            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms * scale43, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": {"workload": desc},
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": gbs / hbm_peak, "peak_kind": peak_kind,
+            "metric": f"decode tokens/s ({args.workload})", "value": res["value"], "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": res["workload"]},
+            "roofline": {"bound": "hbm", "achieved": res["rank0_hbm_gbs"], "peak": measured_peaks()[0], "unit": "GB/s",
+                         "frac": res["rank0_frac_of_measured_hbm"], "peak_kind": res["peak_kind"],
                          "note": "rank 0's KV bytes per step over the step time, launch overhead included"},
+            "detail": res,
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -819,6 +947,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-move", action="store_true")
+    ap.add_argument("--skip-legs", action="store_true", help="leave out the longctx and ragged legs of the default run")
     ap.add_argument("--separate-append", action="store_true",
                     help="append as a launch of its own before each attention launch (default: fused into it)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],

@@ -427,11 +427,22 @@ typedef struct b200kv_kv_cache {
   int64_t slot_mapping_handle; /* "kv.slot_mapping": int32 [tokens_per_step]              */
   int64_t latent_handle;      /* "kv.latent_cache": bf16 [layers][blocks][block][512]      */
   int64_t rope_handle;        /* "kv.rope_cache":   bf16 [layers][blocks][block][64]       */
+  int64_t max_blocks_per_seq; /* columns of the block table                                */
+  int64_t seq_lens_handle;    /* "kv.seq_lens": int32 [max_seqs], or -1 (batched form only) */
 } b200kv_kv_cache;
 
-/* Reserves the four KV spans (RESERVE phase). */
+/* Reserves the four KV spans (RESERVE phase) with the reference's geometry: one sequence's blocks per layer,
+ * blocks = ceil(max_context / block_size), a table of max_seqs rows of that many columns. */
 int32_t b200kv_kv_cache_reserve(b200kv_arena* arena, int64_t max_context, int64_t block_size, int64_t layers,
                                 int64_t max_seqs, int64_t tokens_per_step, b200kv_kv_cache* out);
+/* The batched form of the same reservation (the reference keeps one token per step and one sequence,
+ * src/memory/static_arena_manager.cpp:37-39, 298-300): a pool of num_blocks blocks per layer shared by max_seqs
+ * sequences through b200kv_block_pool, a table [max_seqs][max_blocks_per_seq], slots for tokens_per_step
+ * appended rows (a decode step appends one per sequence, a prefill chunk many) and the lengths [max_seqs],
+ * all int32 and all carved from the same arena under the reference's span names. */
+int32_t b200kv_kv_cache_reserve_batched(b200kv_arena* arena, int64_t num_blocks, int64_t block_size, int64_t layers,
+                                        int64_t max_seqs, int64_t max_blocks_per_seq, int64_t tokens_per_step,
+                                        b200kv_kv_cache* out);
 /* One layer's pool view after Commit: base + layer * blocks * block_size * width * 2
  * (src/pipeline/pipeline.cpp:391-395). */
 int32_t b200kv_kv_cache_layer_view(const b200kv_arena* arena, const b200kv_kv_cache* cache, int64_t layer,

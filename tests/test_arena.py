@@ -132,3 +132,26 @@ def test_kv_cache_reservation_and_layer_views():
         arena.layer_view(cache, 43)
     with pytest.raises(b200kv.B200KVError):
         b200kv.Arena(b200kv.ARENA_HOST_SIM).reserve_kv_cache(max_context=64, block_size=128)  # below one block
+
+
+def test_batched_kv_cache_reservation_host_sim():
+    """The batched form: a pool shared by many sequences, a table per sequence, the step's slots and the lengths,
+    under the reference's span names and in its order, all in one allocation."""
+    arena = b200kv.Arena(b200kv.ARENA_HOST_SIM)
+    cache = arena.reserve_kv_cache_batched(num_blocks=40, block_size=64, layers=3, max_seqs=5, max_blocks_per_seq=12,
+                                           tokens_per_step=256)
+    g = cache.geometry
+    assert (g.blocks_per_layer, g.total_blocks) == (40, 120)
+    assert g.latent_bytes == 3 * 40 * 64 * 512 * 2 and g.rope_bytes == 3 * 40 * 64 * 64 * 2
+    assert g.block_table_bytes == 5 * 12 * 4 and g.slot_mapping_bytes == 256 * 4
+    assert cache.max_blocks_per_seq == 12 and cache.seq_lens_handle >= 0
+    handles = [cache.block_table_handle, cache.slot_mapping_handle, cache.seq_lens_handle, cache.latent_handle,
+               cache.rope_handle]
+    offsets = [arena.offset(h) for h in handles]
+    assert offsets == sorted(offsets) and all(o % 512 == 0 for o in offsets)
+    arena.commit()
+    assert arena.allocations == 1
+    view = arena.layer_view(cache, 2)
+    assert view.pool_rows == 40 * 64 and view.latent == arena.address(cache.latent_handle) + 2 * 40 * 64 * 512 * 2
+    with pytest.raises(b200kv.B200KVError):
+        b200kv.Arena(b200kv.ARENA_HOST_SIM).reserve_kv_cache_batched(0, 64, 1, 1, 1, 1)
