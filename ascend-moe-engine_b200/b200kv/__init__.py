@@ -356,6 +356,30 @@ def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: f
     check(lib.b200kv_mla_decode(ctypes.byref(args), _stream_handle(stream), _ptr(status)))
 
 
+def _decode_args(q, view: PoolView, block_table, kv_len, block_size: int, scale: float, out=None, lse=None, kv_begin=None,
+                 workspace=None, max_ctas: int = 0, stable_tables: bool = False) -> DecodeArgs:
+    args = DecodeArgs()
+    args.q = _ptr(q)
+    args.q_seq_stride = q.stride(0)
+    args.q_head_stride = q.stride(1)
+    args.pool = view
+    args.block_table = _ptr(block_table)
+    args.max_blocks = block_table.stride(0)
+    args.kv_len = _ptr(kv_len)
+    args.kv_begin = _ptr(kv_begin)
+    args.batch = q.shape[0]
+    args.heads = q.shape[1]
+    args.block_size = block_size
+    args.scale = scale
+    args.out = _ptr(out)
+    args.lse = _ptr(lse)
+    args.workspace = _ptr(workspace)
+    args.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    args.max_ctas = max_ctas
+    args.flags = 1 if stable_tables else 0
+    return args
+
+
 def mla_decode_static(q, view: PoolView, block_table, kv_len, block_size: int, scale: float, out=None, lse=None,
                       kv_begin=None, partial=None, max_ctas: int = 0, status=None, stream=None) -> None:
     """b200kv_mla_decode_static: the same attention, with the library's built-in scratch instead of a
@@ -524,7 +548,7 @@ class Arena:
             raise B200KVError(ERR_INVALID, last_error())
 
     def close(self):
-        if self._h:
+        if self._h and lib is not None:  # (the module may already be gone at interpreter exit)
             lib.b200kv_arena_destroy(self._h)
             self._h = None
 

@@ -71,6 +71,8 @@ lib.b200kv_peer_buffer_close.restype = c_int32
 lib.b200kv_peer_buffer_close.argtypes = [c_void_p]
 lib.b200kv_peer_buffer_free.restype = c_int32
 lib.b200kv_peer_buffer_free.argtypes = [c_void_p]
+lib.b200kv_mla_decode_peer.restype = c_int32
+lib.b200kv_mla_decode_peer.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p]
 lib.b200kv_peer_merge.restype = c_int32
 lib.b200kv_peer_merge.argtypes = [c_void_p, c_int32, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p]
@@ -121,6 +123,18 @@ class PeerExchange:
 
         check(lib.b200kv_peer_merge(self._table, self.world, self.rank, self.rows, _ptr(partial_o), _ptr(partial_m),
                                     _ptr(partial_l), _ptr(out), _ptr(lse), _stream_handle(stream), _ptr(status)))
+        return out
+
+    def decode_merge(self, q, view, block_table, kv_len, block_size: int, scale: float, out, lse=None, kv_begin=None,
+                     workspace=None, max_ctas: int = 0, status=None, stream=None, stable_tables: bool = False):
+        """b200kv_mla_decode_peer: attention over this rank's shard (kv_begin / kv_len) and the merge across the
+        ranks in one call; q bf16 [B, 64, 576] with B * 64 == rows, out bf16 [B, 64, 512] on every rank."""
+        from . import _decode_args, _ptr, _stream_handle
+
+        args = _decode_args(q, view, block_table, kv_len, block_size, scale, out=out, lse=lse, kv_begin=kv_begin,
+                            workspace=workspace, max_ctas=max_ctas, stable_tables=stable_tables)
+        check(lib.b200kv_mla_decode_peer(ctypes.byref(args), self._table, self.world, self.rank,
+                                         _stream_handle(stream), _ptr(status)))
         return out
 
     def close(self):

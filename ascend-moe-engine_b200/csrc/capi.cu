@@ -4,6 +4,7 @@
 #include <cstdio>
 
 #include "common.cuh"
+#include "kv_peer.cuh"
 
 namespace b200kv {
 
@@ -29,8 +30,10 @@ int32_t SimtSplitCount(int32_t batch, int32_t sms);
 size_t SimtWorkspaceBytes(int32_t batch, int32_t heads, int32_t sms);
 size_t TcWorkspaceBytes(int32_t n_ctas);
 bool TcSupports(const b200kv_decode_args& a);
+bool TcPeerSupports(const b200kv_decode_args& a);
 int32_t LaunchMlaDecodeSimt(const b200kv_decode_args& a, cudaStream_t stream, int32_t* status);
-int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status);
+int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status,
+                          const PeerRing* ring);
 int32_t LaunchLseMerge(const float* part_o, const float* part_m, const float* part_l, int32_t n_parts, int64_t rows,
                        void* out, float* lse, float* merged_o, float* merged_m, float* merged_l, cudaStream_t stream);
 
@@ -139,8 +142,48 @@ extern "C" int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* strea
     SetLastError("decode: workspace of %zu bytes (16-byte aligned) required, %zu given", need, a.workspace_bytes);
     return a.workspace == nullptr ? B200KV_ERR_NULLPTR : B200KV_ERR_INVALID;
   }
-  if (use_tc) return LaunchMlaDecodeTc(a, ctas, static_cast<cudaStream_t>(stream), status);
+  if (use_tc) return LaunchMlaDecodeTc(a, ctas, static_cast<cudaStream_t>(stream), status, nullptr);
   return LaunchMlaDecodeSimt(a, static_cast<cudaStream_t>(stream), status);
+}
+
+extern "C" int32_t b200kv_mla_decode_peer(const b200kv_decode_args* args, void* const* peer_buffers, int32_t world,
+                                          int32_t rank, void* stream, b200kv_status_word* status) {
+  if (args == nullptr || peer_buffers == nullptr) {
+    SetLastError("decode_peer: args and peer_buffers must be non-null");
+    return B200KV_ERR_NULLPTR;
+  }
+  const b200kv_decode_args& a = *args;
+  if (int32_t rc = ValidateDecodeArgs(a, "decode_peer")) return rc;
+  if (a.batch == 0) return B200KV_OK;
+  if (a.out == nullptr || a.partial_o != nullptr || world < 1 || world > kPeerMaxWorld || rank < 0 || rank >= world ||
+      a.new_latent != nullptr || a.new_rope != nullptr) {
+    SetLastError("decode_peer refused: it writes the merged result to out (no partial_* buffers, no fused append); "
+                 "world %d (1..%d), rank %d", world, kPeerMaxWorld, rank);
+    return B200KV_ERR_INVALID;
+  }
+  if (!TcSupports(a) || !TcPeerSupports(a) || a.variant == B200KV_DECODE_SIMT) {
+    SetLastError("decode_peer: it runs on the tensor-core kernel (64 heads, block_size %% 64 == 0, 16-byte aligned q) for "
+                 "batches of fewer than 16 sequences; otherwise decode into partial_* and call b200kv_peer_merge");
+    return B200KV_ERR_INVALID;
+  }
+  PeerRing ring{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_buffers[r] == nullptr) {
+      SetLastError("decode_peer: the exchange buffer of rank %d is null", r);
+      return B200KV_ERR_NULLPTR;
+    }
+    ring.peer[r] = static_cast<unsigned char*>(peer_buffers[r]);
+  }
+  ring.world = world;
+  ring.rank = rank;
+  ring.rows = static_cast<int64_t>(a.batch) * a.heads;
+  const int32_t ctas = a.max_ctas > 0 ? a.max_ctas : CurrentDeviceSmCount();
+  const size_t need = TcWorkspaceBytes(ctas);
+  if (a.workspace == nullptr || a.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a.workspace) & 15u) != 0) {
+    SetLastError("decode_peer: workspace of %zu bytes (16-byte aligned) required, %zu given", need, a.workspace_bytes);
+    return a.workspace == nullptr ? B200KV_ERR_NULLPTR : B200KV_ERR_INVALID;
+  }
+  return LaunchMlaDecodeTc(a, ctas, static_cast<cudaStream_t>(stream), status, &ring);
 }
 
 extern "C" int32_t b200kv_lse_merge(const float* partial_o, const float* partial_m, const float* partial_l,

@@ -24,28 +24,15 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "kv_peer.cuh"
 
 namespace b200kv {
 namespace {
 
-constexpr int kRowWords = B200KV_LATENT_DIM + 2;  // O[512], m, l
-constexpr int kMaxWorld = 16;
+constexpr int kRowWords = kPeerRowWords;
+constexpr int kMaxWorld = kPeerMaxWorld;
 
-struct PeerLayout {
-  size_t inbox_bytes;  // one half
-  size_t epoch_offset;
-  size_t done_offset;
-  size_t total;
-};
-
-__host__ __device__ inline PeerLayout LayoutOf(int world, int64_t rows) {
-  PeerLayout l;
-  l.inbox_bytes = static_cast<size_t>(world) * rows * kRowWords * sizeof(uint64_t);
-  l.epoch_offset = (2 * l.inbox_bytes + 255) & ~static_cast<size_t>(255);
-  l.done_offset = l.epoch_offset + 64;
-  l.total = l.done_offset + 64;
-  return l;
-}
+__host__ __device__ inline PeerLayout LayoutOf(int world, int64_t rows) { return PeerLayoutOf(world, rows); }
 
 struct PeerParams {
   unsigned char* peer[kMaxWorld];  // exchange buffers of all ranks as seen from this process (own included)
@@ -60,21 +47,9 @@ struct PeerParams {
   int32_t* status;
 };
 
-__device__ __forceinline__ uint64_t LoadWord(const uint64_t* p) {
-  uint64_t v;
-  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ void StoreWord(uint64_t* p, uint64_t v) {
-  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-
-__device__ __forceinline__ uint64_t TimerNs() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
+__device__ __forceinline__ uint64_t LoadWord(const uint64_t* p) { return PeerLoadWord(p); }
+__device__ __forceinline__ void StoreWord(uint64_t* p, uint64_t v) { PeerStoreWord(p, v); }
+__device__ __forceinline__ uint64_t TimerNs() { return PeerTimerNs(); }
 
 // One warp per row: pushes the row of this rank's partial to every rank, waits for the row from every rank,
 // then the log-sum-exp merge M = max m_r, L = sum l_r e^(m_r - M), out = sum O_r e^(m_r - M) / L,

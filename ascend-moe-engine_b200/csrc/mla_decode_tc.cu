@@ -33,6 +33,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "kv_peer.cuh"
 #include "sm100_ptx.cuh"
 
 namespace b200kv {
@@ -74,7 +75,7 @@ struct Misc {
   uint64_t s_full[2];
   uint64_t s_empty[2];
   uint64_t p_full[kStages];
-  uint64_t q_full;
+  uint64_t q_full[kGroups];  // Q lands in the same four slab groups as a stage: QK starts on the first
   uint64_t q_empty;
   uint64_t o_full;
   uint64_t o_empty;
@@ -114,6 +115,7 @@ struct TcParams {
   int32_t batch;
   int32_t block_size;
   int32_t stable_tables;  // lengths and block table may be read before the stream dependency wait
+  int32_t force_ws;       // every segment leaves a partial in the workspace, one that covers its sequence too
   float scale_log2;  // scale * log2(e)
   __nv_bfloat16* out;
   float* lse;
@@ -367,9 +369,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     return true;
   };
   // Q of one sequence: nine 64-column slabs of 64 head rows.
-  auto issue_q = [&](int seq) {  // lanes 0 .. 8, one slab each
-    const uint32_t qbar = bar(&misc->q_full);
-    if (lane == 0) ptx::MbarArriveExpectTx(qbar, kQBytes);
+  auto issue_q = [&](int seq) {  // lanes 0 .. 8, one slab each, completing on its group's barrier
+    const uint32_t qbar = bar(&misc->q_full[my_group]);
+    if (lane < 8 && (lane & 1) == 0) ptx::MbarArriveExpectTx(qbar, (my_group == kGroups - 1 ? 3 : 2) * kQSlabBytes);
     ptx::TmaLoad3D(q_addr + lane * kQSlabBytes, &q_map, 64 * lane, 0, seq, qbar);
   };
 
@@ -378,6 +380,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     // The producer warp initialises the barriers, finds this CTA's slice of the flat tile list and
     // puts Q and the first tiles in flight at once: the other warps' setup (TMEM allocation, the
     // barrier below) then overlaps the first loads' latency instead of preceding it.
+    // The lengths are the head of a chain of dependent loads (lengths, block table, tiles): when the caller
+    // vouches for them their load goes out first and the barrier set-up runs under its latency.
+    int early_len = 0;
+    if (p.stable_tables != 0 && lane < p.batch) early_len = p.kv_len[lane];
     if (lane == 0) {
       for (int s = 0; s < kStages; ++s) {
         for (int k = 0; k < kGroups; ++k) {
@@ -391,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::MbarInit(bar(&misc->s_empty[s]), kSoftmaxWarps);
       }
       ptx::MbarInit(bar(&misc->new_row_full), 1);
-      ptx::MbarInit(bar(&misc->q_full), 1);
+      for (int k = 0; k < kGroups; ++k) ptx::MbarInit(bar(&misc->q_full[k]), 1);
       ptx::MbarInit(bar(&misc->q_empty), 1);
       ptx::MbarInit(bar(&misc->o_full), 1);
       ptx::MbarInit(bar(&misc->o_empty), kSoftmaxWarps);
@@ -414,7 +420,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     // 2^30); only the running totals are 64-bit. This warp's instruction count is on every launch's critical
     // path, so the scans are kept short.
     long long total = 0, nonempty = 0;
-    const int first_tiles = lane < p.batch ? TilesOf(p.kv_len[lane]) : 0;  // the first chunk's lengths, kept
+    const int first_tiles =  // the first chunk's lengths, kept
+        lane < p.batch ? TilesOf(p.stable_tables != 0 ? early_len : p.kv_len[lane]) : 0;
     for (int b0 = 0; b0 < p.batch; b0 += 32) {
       int t = b0 == 0 ? first_tiles : (b0 + lane < p.batch ? TilesOf(p.kv_len[b0 + lane]) : 0);
       int ne = t > 0 ? 1 : 0;
@@ -487,11 +494,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int64_t row0 = n_first > 0 ? tile_row(start_seq, begin, start_tile) : 0;
       const int64_t row1 = n_first > 1 ? tile_row(start_seq, begin, start_tile + 1) : 0;
       if (p.stable_tables != 0) GridDependencyWait();  // Q and the pool are the preceding kernels' to write
-      if (lane < 9) {
-        issue_q(start_seq);
-        if (n_first > 0) issue_slab(row0, 0);
-        if (n_first > 1) issue_slab(row1, 1);
+      // Group by group, Q's slabs and the first tile's together: QK starts when the first group of both has
+      // landed, a quarter of the way into the 144 KB, not at its end.
+      for (int c = 0; c < kGroups; ++c) {
+        if (lane < 9 && my_group == c) {
+          issue_q(start_seq);
+          if (n_first > 0) issue_slab(row0, 0);
+        }
       }
+      if (lane < 9 && n_first > 1) issue_slab(row1, 1);
       pre_issued = n_first;
     } else if (p.stable_tables != 0) {
       GridDependencyWait();
@@ -647,7 +658,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (__shfl_sync(0xffffffffu, have, 0) == 0) break;
         const int n = __shfl_sync(0xffffffffu, t_hi - t_lo, 0);
         if (is_qk) {
-          ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_full), seg & 1, misc, p.status, 22));
           for (int i = 0; i < n && ok; ++i) {
             const int g = __shfl_sync(0xffffffffu, g0 + i, 0);
             const int stage = g % kStages;
@@ -658,6 +668,11 @@ __global__ void __launch_bounds__(kThreads, 1)
               ok = __all_sync(0xffffffffu,
                               BoundedWait(bar(&misc->s_empty[buf]), ((g >> 1) & 1) ^ 1, misc, p.status, 25));
             }
+            // A segment's first tile also waits, group by group, for the sequence's Q.
+            const bool first_of_segment = i == 0;
+            if (ok && first_of_segment) {
+              ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_full[0]), seg & 1, misc, p.status, 22));
+            }
             if (!ok) break;
             ptx::TcFenceAfterSync();
             const uint64_t kdesc = DescAt(k_desc0, stage * kStageBytes);
@@ -666,14 +681,23 @@ __global__ void __launch_bounds__(kThreads, 1)
             // offsets; a runtime offset costs the uniform-datapath issue rate).
             IssueQkGroup<0, 2>(q_desc, kdesc, d);
             ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][1]), kv_parity, misc, p.status, 26));
+            if (ok && first_of_segment) {
+              ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_full[1]), seg & 1, misc, p.status, 22));
+            }
             if (!ok) break;
             ptx::TcFenceAfterSync();
             IssueQkGroup<2, 2>(q_desc, kdesc, d);
             ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][2]), kv_parity, misc, p.status, 27));
+            if (ok && first_of_segment) {
+              ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_full[2]), seg & 1, misc, p.status, 22));
+            }
             if (!ok) break;
             ptx::TcFenceAfterSync();
             IssueQkGroup<4, 2>(q_desc, kdesc, d);
             ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][3]), kv_parity, misc, p.status, 28));
+            if (ok && first_of_segment) {
+              ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->q_full[3]), seg & 1, misc, p.status, 22));
+            }
             if (!ok) break;
             ptx::TcFenceAfterSync();
             IssueQkGroup<6, 3>(q_desc, kdesc, d);
@@ -890,8 +914,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!ok) break;
       ptx::TcFenceAfterSync();
       const bool whole = (t_lo == 0 && t_hi == seq_tiles);
-      const bool to_user_partial = whole && p.user_o != nullptr;
-      const bool to_ws = !whole;
+      const bool to_ws = !whole || p.force_ws != 0;
+      const bool to_user_partial = !to_ws && p.user_o != nullptr;
       const int slot = cta * 2 + (first_segment_of_cta ? 0 : 1);
       // Lane j < 16 writes row j of this warp's sixteen: its (m, l) sit in quad j % 8, entry j / 8.
       const int from = 4 * (lane & 7);
@@ -981,18 +1005,27 @@ __global__ void __launch_bounds__(kThreads, 1)
 // memory, and every thread accumulates weight x data.
 // kGroups = 1: 128 threads, 256 columns per CTA in two passes, every thread walks all parts (batches, where a
 // sequence has a handful of parts: 32 CTAs per sequence). kGroups = 8: 256 threads, 32 columns per CTA, a
-// chunk is 64 parts of which each warp takes eight, summed through shared memory at the end (a few long
-// sequences with a hundred parts each: 256 CTAs per sequence).
+// chunk is 256 parts of which each warp takes 32 consecutive ones, summed through shared memory at the end
+// (a few long sequences with a hundred parts each: 256 CTAs per sequence, one chunk, one round of weights).
 // The kernel needs a few hundred bytes of shared memory, so its CTAs fit beside a resident decode CTA.
-template <int kGroups>
+//
+// kPeer (with kGroups = 8): the sequence is a KV-range shard of a longer one that other GPUs hold the rest of.
+// The CTA's merged columns are not written out but pushed, as tagged words, into every rank's exchange buffer
+// over peer memory, and the same threads then wait (bounded) for the other ranks' words of their columns,
+// merge them and write the final rows: the exchange protocol of kv_peer.cu without a kernel, and a pass over
+// the partial, in between. A thread waits only for words that other GPUs' kernels write.
+template <int kGroups, bool kPeer = false>
 __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2)
-    MlaFinalizeKernel(TcParams p, int32_t n_ctas) {
+    MlaFinalizeKernel(TcParams p, int32_t n_ctas, PeerRing ring) {
+  static_assert(!kPeer || kGroups == 8, "the peer form is built on the few-sequences variant");
   constexpr int kThreadsF = kGroups == 1 ? 128 : 256;
   constexpr int kGroupThreads = kThreadsF / kGroups;   // 128 or 32: columns a group covers per pass
   constexpr int kPasses = kGroups == 1 ? 2 : 1;
   constexpr int kDv = kGroupThreads * kPasses;         // 256 or 32 output columns per CTA
-  constexpr int kChunk = 8 * kGroups;                  // parts per chunk: 8 per group
-  constexpr int kSub = 4;                              // parts whose data a thread has in flight
+  constexpr int kGroupParts = kGroups == 1 ? 8 : 32;   // parts of a chunk that one group takes
+  constexpr int kChunk = kGroupParts * kGroups;        // parts per chunk: 8, or 256 (a long sequence's in one go)
+  constexpr int kRounds = kGroupParts / 8;             // a warp works out the weights of 8 parts x 4 heads at a time
+  constexpr int kSub = kGroups == 1 ? 4 : 8;           // parts whose data a thread has in flight
   constexpr int kDvChunks = kLatent / kDv;             // 2 or 16
   constexpr int kQuads = kHeads / 4;
 
@@ -1073,7 +1106,7 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
   // below are what that kernel wrote, so they wait for its completion.
   GridDependencyTrigger();
   GridDependencyWait();
-  if (mine > 0 && cf == cl) return;  // written directly by the decode kernel
+  if (!kPeer && mine > 0 && cf == cl) return;  // written directly by the decode kernel
 
   float acc[kPasses][4];
 #pragma unroll
@@ -1089,12 +1122,12 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
     if (c0 != cf) __syncthreads();  // the previous chunk's weights and slots have been used
     if (tid < kChunk) s_slot[tid] = slot_of(c0 + tid);
     __syncthreads();
-    // This thread's parts of the chunk: 8 consecutive ones per group, four at a time.
+    // This thread's parts of the chunk: kGroupParts consecutive ones per group, kSub at a time.
     float4 data[kSub][kPasses];
     auto load_sub = [&](int sub) {
 #pragma unroll
       for (int k = 0; k < kSub; ++k) {
-        const int slot = s_slot[group * 8 + sub * kSub + k];
+        const int slot = s_slot[group * kGroupParts + sub * kSub + k];
 #pragma unroll
         for (int q = 0; q < kPasses; ++q) {
           data[k][q] = slot >= 0 ? ws4[(static_cast<int64_t>(slot) * kQuads + hq) * kLatent + dv_first + kGroupThreads * q]
@@ -1103,16 +1136,26 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
       }
     };
     load_sub(0);
-    // ---- weights of the chunk: warp g of the first kGroups warps takes parts 8 g .. 8 g + 7, lane = (part, head) ----
-    float m_mine = -INFINITY, l_mine = 0.0f;
+    // ---- weights of the chunk: warp g of the first kGroups warps takes its group's parts, eight at a time,
+    // lane = (part, head) ----
+    float m_mine[kRounds], l_mine[kRounds];
     if (warp < kGroups) {
-      const int slot = s_slot[warp * 8 + (lane >> 2)];
-      if (slot >= 0) {
-        l_mine = p.ws_l[slot * kHeads + 4 * hq + (lane & 3)];
-        m_mine = p.ws_m[slot * kHeads + 4 * hq + (lane & 3)];
+      float gmax = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        const int slot = s_slot[warp * kGroupParts + 8 * r + (lane >> 2)];
+        m_mine[r] = -INFINITY;
+        l_mine[r] = 0.0f;
+        if (slot >= 0) {
+          l_mine[r] = p.ws_l[slot * kHeads + 4 * hq + (lane & 3)];
+          m_mine[r] = p.ws_m[slot * kHeads + 4 * hq + (lane & 3)];
+        }
       }
-      if (!(l_mine > 0.0f)) m_mine = -INFINITY;
-      float gmax = m_mine;
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        if (!(l_mine[r] > 0.0f)) m_mine[r] = -INFINITY;
+        gmax = fmaxf(gmax, m_mine[r]);
+      }
 #pragma unroll
       for (int off = 4; off < 32; off <<= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, off));
       if (lane < 4) s_gmax[warp][lane] = gmax;
@@ -1124,9 +1167,13 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
       float new_big = old_big;
 #pragma unroll
       for (int g = 0; g < kGroups; ++g) new_big = fmaxf(new_big, s_gmax[g][i]);
-      const float w = (l_mine > 0.0f && new_big != -INFINITY) ? expf(m_mine - new_big) : 0.0f;
-      s_w[warp * 8 + (lane >> 2)][i] = w;
-      float gsum = l_mine * w;
+      float gsum = 0.0f;
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        const float w = (l_mine[r] > 0.0f && new_big != -INFINITY) ? expf(m_mine[r] - new_big) : 0.0f;
+        s_w[warp * kGroupParts + 8 * r + (lane >> 2)][i] = w;
+        gsum = fmaf(l_mine[r], w, gsum);
+      }
 #pragma unroll
       for (int off = 4; off < 32; off <<= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, off);
       if (lane < 4) s_gsum[warp][lane] = gsum;
@@ -1159,17 +1206,17 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
         acc[q][3] *= cr.w;
       }
     }
-#pragma unroll
-    for (int sub = 0; sub < 8 / kSub; ++sub) {
+#pragma unroll 1
+    for (int sub = 0; sub < kGroupParts / kSub; ++sub) {
       if (sub > 0) {
-        if (s_slot[group * 8 + sub * kSub] < 0 && dense) break;  // dense: parts are consecutive, the rest is absent
+        if (s_slot[group * kGroupParts + sub * kSub] < 0 && dense) break;  // dense: parts are consecutive, the rest is absent
         load_sub(sub);
       }
 #pragma unroll
       for (int k = 0; k < kSub; ++k) {
         // An absent part has weight zero and zero data; a present one with l = 0 may hold anything (0 x NaN is
         // not 0), so its data is dropped with its weight.
-        const float4 w = *reinterpret_cast<const float4*>(s_w[group * 8 + sub * kSub + k]);
+        const float4 w = *reinterpret_cast<const float4*>(s_w[group * kGroupParts + sub * kSub + k]);
 #pragma unroll
         for (int q = 0; q < kPasses; ++q) {
           acc[q][0] = fmaf(w.x != 0.0f ? data[k][q].x : 0.0f, w.x, acc[q][0]);
@@ -1192,6 +1239,97 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
       acc[0][2] += v.z;
       acc[0][3] += v.w;
     }
+  }
+  if constexpr (kPeer) {
+    // ---- across the GPUs: push this rank's merged columns, wait for the others', merge, write ----
+    const int64_t row_first = static_cast<int64_t>(b) * kHeads + 4 * hq;
+    const PeerLayout lay = PeerLayoutOf(ring.world, ring.rows);
+    unsigned char* own = ring.peer[ring.rank];
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(own + lay.epoch_offset) + 1u;
+    const uint64_t tag = static_cast<uint64_t>(epoch) << 32;
+    const size_t half = (epoch & 1u) * lay.inbox_bytes;
+    const bool owns_ml = dv0 == 0 && lane < 4;  // lane i of the first column range also carries (m, l) of head i
+    for (int dst = 0; dst < ring.world; ++dst) {
+      uint64_t* inbox = reinterpret_cast<uint64_t*>(ring.peer[dst] + half) +
+                        (static_cast<size_t>(ring.rank) * ring.rows + row_first) * kPeerRowWords;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) PeerStoreWord(inbox + i * kPeerRowWords + dv_first, tag | __float_as_uint(acc[0][i]));
+      if (owns_ml) {
+        PeerStoreWord(inbox + lane * kPeerRowWords + kLatent, tag | __float_as_uint(s_big[lane]));
+        PeerStoreWord(inbox + lane * kPeerRowWords + kLatent + 1, tag | __float_as_uint(s_sum[lane]));
+      }
+    }
+    const uint64_t* inbox = reinterpret_cast<const uint64_t*>(own + half);
+    const uint64_t start = PeerTimerNs();
+    float big[4], total_l[4], merged[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      big[i] = -INFINITY;
+      total_l[i] = 0.0f;
+      merged[i] = 0.0f;
+    }
+    bool ok = true;
+    for (int src = 0; src < ring.world && ok; ++src) {
+      const uint64_t* words = inbox + (static_cast<size_t>(src) * ring.rows + row_first) * kPeerRowWords;
+      uint64_t w[12];
+      for (uint32_t spins = 0;; ++spins) {
+        bool here = true;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          w[i] = PeerLoadWord(words + i * kPeerRowWords + dv_first);
+          w[4 + i] = PeerLoadWord(words + i * kPeerRowWords + kLatent);
+          w[8 + i] = PeerLoadWord(words + i * kPeerRowWords + kLatent + 1);
+        }
+#pragma unroll
+        for (int i = 0; i < 12; ++i) here = here && (w[i] >> 32) == epoch;
+        if (__all_sync(0xffffffffu, here)) break;
+        if ((spins & 63u) == 63u && PeerTimerNs() - start > 1000000000ull) {
+          if (lane == 0) RecordError(p.status, B200KV_DEV_TIMEOUT, 51, src, static_cast<int32_t>(epoch));
+          ok = false;
+          break;
+        }
+      }
+      if (!ok) break;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float m = __uint_as_float(static_cast<uint32_t>(w[4 + i]));
+        const float l = __uint_as_float(static_cast<uint32_t>(w[8 + i]));
+        if (!(l > 0.0f)) continue;  // an empty shard
+        const float new_big = fmaxf(big[i], m);
+        const float carry = big[i] == -INFINITY ? 0.0f : expf(big[i] - new_big);
+        const float weight = expf(m - new_big);
+        big[i] = new_big;
+        total_l[i] = total_l[i] * carry + l * weight;
+        merged[i] = fmaf(merged[i], carry, __uint_as_float(static_cast<uint32_t>(w[i])) * weight);
+      }
+    }
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float inv = total_l[i] > 0.0f ? 1.0f / total_l[i] : 0.0f;
+        p.out[(row_first + i) * kLatent + dv_first] = __float2bfloat16_rn(merged[i] * inv);
+      }
+      if (owns_ml && p.lse != nullptr) {
+        float lse_value = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (i == lane && total_l[i] > 0.0f) lse_value = big[i] + logf(total_l[i]);
+        }
+        p.lse[row_first + lane] = lse_value;
+      }
+    }
+    // The epoch is complete for this rank when every CTA is done with the inbox half; a launch whose wait ran
+    // out completes it too, so that the ranks that did arrive are not held up in the next one by this one.
+    __syncwarp();
+    if (lane == 0) {
+      uint32_t* done = reinterpret_cast<uint32_t*>(own + lay.done_offset);
+      __threadfence();
+      if (atomicAdd(done, 1u) == gridDim.x - 1) {
+        *done = 0;
+        *reinterpret_cast<volatile uint32_t*>(own + lay.epoch_offset) = epoch;
+      }
+    }
+    return;
   }
   const int64_t row0 = static_cast<int64_t>(b) * kHeads + 4 * hq;
 #pragma unroll
@@ -1370,7 +1508,12 @@ bool TcSupports(const b200kv_decode_args& a) {
          a.pool.latent_row_stride * 2 < (1ll << 40);
 }
 
-int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status) {
+bool TcPeerSupports(const b200kv_decode_args& a) { return a.batch < 16; }
+
+// ring != nullptr: the call's sequences are KV-range shards and the merge kernel finishes them across the GPUs
+// (TcPeerSupports says for which batches that form exists).
+int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status,
+                          const PeerRing* ring) {
   if (a.new_latent != nullptr || a.new_rope != nullptr) {
     if (a.new_latent == nullptr || a.new_rope == nullptr) {
       SetLastError("decode: a fused append needs both new_latent and new_rope");
@@ -1413,6 +1556,7 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.kv_begin = a.kv_begin;
   p.pool_rows = a.pool.pool_rows;
   p.stable_tables = (a.flags & B200KV_DECODE_STABLE_TABLES) != 0 ? 1 : 0;
+  p.force_ws = ring != nullptr ? 1 : 0;
   p.new_latent = static_cast<const char*>(a.new_latent);
   p.new_rope = static_cast<const char*>(a.new_rope);
   p.new_latent_bytes = a.new_latent_stride * 2;
@@ -1445,12 +1589,17 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   // A handful of long sequences: 256 CTAs per sequence, the parts shared out among a CTA's eight warps, so that
   // the merge still fills the GPU. Batches: 32 CTAs per sequence, every thread walking the sequence's few parts.
   if (a.batch < 16) {
+    if (ring != nullptr) {
+      return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<8, true>, dim3(static_cast<unsigned>(a.batch) * 16 * (kLatent / 32)),
+                                        dim3(256), 0, stream, p, n_ctas, *ring),
+                       "decode finalize + peer merge launch");
+    }
     return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<8>, dim3(static_cast<unsigned>(a.batch) * 16 * (kLatent / 32)), dim3(256), 0,
-                                      stream, p, n_ctas),
+                                      stream, p, n_ctas, PeerRing{}),
                      "decode finalize launch");
   }
   return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<1>, dim3(static_cast<unsigned>(a.batch) * 16 * (kLatent / 256)), dim3(128), 0,
-                                    stream, p, n_ctas),
+                                    stream, p, n_ctas, PeerRing{}),
                    "decode finalize launch");
 }
 

@@ -15,7 +15,9 @@ namespace b200kv {
 int32_t ValidateDecodeArgs(const b200kv_decode_args& a, const char* who);
 bool TcSupports(const b200kv_decode_args& a);
 size_t TcWorkspaceBytes(int32_t n_ctas);
-int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status);
+struct PeerRing;
+int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStream_t stream, int32_t* status,
+                          const PeerRing* ring);
 int32_t ValidatePoolView(const b200kv_pool_view* pool);
 }  // namespace b200kv
 
@@ -87,5 +89,5 @@ extern "C" int32_t b200kv_mla_decode_static(const b200kv_decode_args* args, void
   a.workspace_bytes = kStaticScratchBytes;
   // Nothing in the scratch has to start at zero: every partial slot a launch reads was written by the
   // same launch's decode kernel first.
-  return LaunchMlaDecodeTc(a, ctas, static_cast<cudaStream_t>(stream), status);
+  return LaunchMlaDecodeTc(a, ctas, static_cast<cudaStream_t>(stream), status, nullptr);
 }

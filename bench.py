@@ -644,7 +644,8 @@ def leg_ragged(torch, dist, b200kv, layers: int, steps: int, use_graph: bool = T
     }
 
 
-def leg_longctx(torch, dist, b200kv, layers: int, steps: int, exchange_kind: str = "peer", use_graph: bool = True):
+def leg_longctx(torch, dist, b200kv, layers: int, steps: int, exchange_kind: str = "peer", use_graph: bool = True,
+                max_ctas: int = 0, tokens: int = 262144):
     """configs[3]: one sequence of 262,144 tokens split by KV range over the ranks; every layer ends with the
     exchange of the ranks' partials (peer memory over NVLink, or an NCCL all-gather) and the log-sum-exp merge.
     Rank 0 checks layer 0 against the oracle on 8 heads over the whole sequence."""
@@ -657,7 +658,7 @@ def leg_longctx(torch, dist, b200kv, layers: int, steps: int, exchange_kind: str
     rank, world, _ = dist_env()
     hbm_peak, _, peak_kind = measured_peaks()
     status = b200kv.new_status()
-    n = 262144
+    n = tokens
     begin, length = kvdist.split_kv_range(n, BLOCK, world, rank)
     my_blocks = scenarios.blocks_for(length, BLOCK)
     total_blocks = n // BLOCK
@@ -683,14 +684,18 @@ def leg_longctx(torch, dist, b200kv, layers: int, steps: int, exchange_kind: str
     def decode(l):
         b200kv.mla_decode(q, views[l], table, lens, BLOCK, SCALE, kv_begin=begins,
                           partial=(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS)), workspace=ws,
-                          status=status, stable_tables=True)
+                          status=status, stable_tables=True, max_ctas=max_ctas)
 
     def step():
         for l in range(layers):
-            decode(l)
             if exchange is not None:
-                exchange.merge(po, pm, pl, out[l], lse, status=status)
-            elif world > 1:
+                # decode of the shard and the merge across the ranks as one call of two kernels
+                exchange.decode_merge(q, views[l], table, lens, BLOCK, SCALE, out[l].view(1, HEADS, LATENT), lse=lse,
+                                      kv_begin=begins, workspace=ws, status=status, stable_tables=True,
+                                      max_ctas=max_ctas)
+                continue
+            decode(l)
+            if world > 1:
                 kvdist.merge_across_ranks(po, pm, pl, out[l], lse)
             else:
                 b200kv.lse_merge(po.view(1, HEADS, LATENT), pm.view(1, HEADS), pl.view(1, HEADS), out[l], lse)
@@ -745,7 +750,8 @@ def leg_longctx(torch, dist, b200kv, layers: int, steps: int, exchange_kind: str
         exchange.close()
     scale43 = 43.0 / layers
     gbs = float(length) * ROW * 2 * layers / (ms * 1e-3) * 1e-9
-    how = ("partials pushed into every rank's inbox over peer memory (NVLink) and merged by the same kernel"
+    how = ("the kernel that merges the shard's per-CTA partials pushes the result into every rank's inbox over peer "
+           "memory (NVLink) and merges what arrives"
            if exchange is not None else "all-gather of 131,584-byte partials (NCCL) + LSE merge")
     del pool
     return {
@@ -918,7 +924,8 @@ def run_extra_workload(args):
         res = leg_ragged(torch, dist, b200kv, args.layers, args.steps, use_graph=not args.no_graph)
         ms = res["ms_per_run_43_layers"]
     else:
-        res = leg_longctx(torch, dist, b200kv, args.layers, args.steps, args.exchange, use_graph=not args.no_graph)
+        res = leg_longctx(torch, dist, b200kv, args.layers, args.steps, args.exchange, use_graph=not args.no_graph,
+                          max_ctas=args.max_ctas, tokens=args.tokens)
         ms = res["ms_per_step_43_layers"]
     if rank == 0:
         print(json.dumps({
@@ -947,6 +954,8 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-move", action="store_true")
+    ap.add_argument("--max-ctas", type=int, default=0, help="longctx only: grid of the decode kernel (0 = one CTA per SM)")
+    ap.add_argument("--tokens", type=int, default=262144, help="longctx only: length of the sequence (a multiple of 64)")
     ap.add_argument("--skip-legs", action="store_true", help="leave out the longctx and ragged legs of the default run")
     ap.add_argument("--separate-append", action="store_true",
                     help="append as a launch of its own before each attention launch (default: fused into it)")

@@ -258,6 +258,18 @@ int32_t b200kv_peer_buffer_free(void* ptr);
 int32_t b200kv_peer_merge(void* const* peer_buffers, int32_t world, int32_t rank, int64_t rows, const float* partial_o,
                           const float* partial_m, const float* partial_l, void* out_bf16, float* lse, void* stream,
                           b200kv_status_word* status);
+/*
+ * Decode attention over this rank's KV-range shard and the merge across the ranks as one call of two kernels:
+ * the decode kernel leaves its per-CTA partials in the workspace, and the kernel that merges them pushes the
+ * shard's result straight into every rank's exchange buffer, waits (bounded) for the other ranks' and writes
+ * the whole sequence's attention to args->out (bf16 [batch][64][512]; args->lse optional) on every rank. The
+ * same as b200kv_mla_decode into partial_* followed by b200kv_peer_merge, without the kernel and the pass over
+ * the partial in between. args->kv_begin / kv_len select the shard; partial_*, new_latent and new_rope must be
+ * null; the exchange buffers are those of b200kv_peer_buffer_alloc for rows = batch * 64. Runs on the
+ * tensor-core kernel for batches of fewer than 16 sequences (a long context is one sequence, or a few).
+ */
+int32_t b200kv_mla_decode_peer(const b200kv_decode_args* args, void* const* peer_buffers, int32_t world, int32_t rank,
+                               void* stream, b200kv_status_word* status);
 
 /*
  * The stages on either side of the path (the reference runs them as separate operators).

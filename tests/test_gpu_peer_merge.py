@@ -48,9 +48,15 @@ outs = [torch.zeros((heads, 512), dtype=torch.bfloat16, device="cuda") for _ in 
 lses = [torch.zeros((heads,), dtype=torch.float32, device="cuda") for _ in range(layers)]
 status = b200kv.new_status()
 exchange = kvdist.PeerExchange(heads)
+FUSED = os.environ.get("PEER_FUSED") == "1"   # b200kv_mla_decode_peer instead of decode + b200kv_peer_merge
 
 def step():
     for l in range(layers):
+        if FUSED:
+            exchange.decode_merge(q, b200kv.pool_view(d_pools[l]), d_table, d_len, bs, 1.0 / 24.0, outs[l].view(1, heads, 512),
+                                  lse=lses[l], kv_begin=d_begin, workspace=ws, status=status,
+                                  max_ctas=(0, 5, 1)[l % 3])
+            continue
         b200kv.mla_decode(q, b200kv.pool_view(d_pools[l]), d_table, d_len, bs, 1.0 / 24.0, kv_begin=d_begin,
                           partial=(po, pm, pl), workspace=ws, status=status)
         exchange.merge(po.view(heads, 512), pm.view(heads), pl.view(heads), outs[l], lses[l], status=status)
@@ -78,12 +84,13 @@ check("capture")   # capture does not run the kernels: outputs are still zero, s
 '''
 
 
-def _run_workers(world, tmp_path):
+def _run_workers(world, tmp_path, fused=False):
     script = tmp_path / "peer_worker.py"
     body = WORKER.replace('check("capture")   # capture does not run the kernels: outputs are still zero, so this must be skipped below',
                           'torch.cuda.synchronize()\nfor _ in range(3):\n    graph.replay()\n    check("graph replay")\ndist.barrier()\nexchange.close()\ndist.destroy_process_group()\nprint("PEER_OK", rank)')
     script.write_text(f"ROOT = {ROOT!r}\n" + body)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29533", WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29534" if fused else "29533", WORLD_SIZE=str(world),
+               NCCL_NVLS_ENABLE="0", PEER_FUSED="1" if fused else "0")
     procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(world)]
     outputs = []
@@ -123,14 +130,57 @@ def test_peer_merge_single_rank_matches_lse_merge():
     exchange.close()
 
 
+@pytest.mark.parametrize("fused", [False, True], ids=["decode_then_merge", "decode_peer"])
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_merge_two_ranks(tmp_path):
-    _run_workers(2, tmp_path)
+def test_peer_merge_two_ranks(tmp_path, fused):
+    _run_workers(2, tmp_path, fused)
 
 
+@pytest.mark.parametrize("fused", [False, True], ids=["decode_then_merge", "decode_peer"])
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
-def test_peer_merge_four_ranks(tmp_path):
-    _run_workers(4, tmp_path)
+def test_peer_merge_four_ranks(tmp_path, fused):
+    _run_workers(4, tmp_path, fused)
+
+
+@pytest.mark.parametrize("max_ctas", [0, 7, 1])
+def test_decode_peer_single_rank_equals_decode(max_ctas):
+    """b200kv_mla_decode_peer with one rank: the merge kernel pushes into its own inbox and merges one shard, so
+    the result must equal b200kv_mla_decode's on the same inputs (bit for bit where both merge the same parts),
+    through several epochs and for a shard selected by kv_begin; sequences whose shard is empty give zeros."""
+    from b200kv import dist as kvdist
+
+    bs = 64
+    kv_len = np.array([64 * 30 + 5, 0, 700], dtype=np.int32)
+    kv_begin = np.array([64 * 3, 0, 0], dtype=np.int32)
+    B = len(kv_len)
+    blocks = int(sum(scenarios.blocks_for(int(b + n), bs) for b, n in zip(kv_begin, kv_len))) + 4
+    table = scenarios.fragmented_tables(kv_begin + kv_len, bs, blocks)
+    pool_np = kvo.make_pool(blocks * bs)
+    q_np = kvo.make_q(B, scale=2.0 / 24.0)
+    pool, q = to_dev_bf16(pool_np), to_dev_bf16(q_np)
+    tbl, lens, begins = to_dev_i32(table), to_dev_i32(kv_len), to_dev_i32(kv_begin)
+    ws = torch.empty(b200kv.decode_workspace_bytes(B, 64, max_ctas), dtype=torch.uint8, device="cuda")
+    exchange = kvdist.PeerExchange(B * 64)
+    status = b200kv.new_status()
+    ref_out, ref_lse = scenarios.ref_attention_f64(q_np, pool_np, table, kv_len, bs, 1.0 / 24.0, kv_begin=kv_begin)
+    for epoch in range(3):
+        out = torch.full((B, 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+        lse = torch.full((B, 64), float("nan"), dtype=torch.float32, device="cuda")
+        exchange.decode_merge(q, b200kv.pool_view(pool), tbl, lens, bs, 1.0 / 24.0, out, lse=lse.view(-1), kv_begin=begins,
+                              workspace=ws, max_ctas=max_ctas, status=status)
+        torch.cuda.synchronize()
+        assert status.cpu().tolist()[0] == 0, status.cpu().tolist()
+        scenarios.check_attention(from_dev_bf16(out), lse.cpu().numpy(), ref_out, ref_lse,
+                                  what=f"decode_peer, one rank, epoch {epoch}, max_ctas {max_ctas}")
+        assert (from_dev_bf16(out)[1] == 0).all()
+    exchange.close()
+    # refused where it cannot run
+    big_q = to_dev_bf16(kvo.make_q(16))
+    with pytest.raises(b200kv.B200KVError):
+        kvdist.PeerExchange(16 * 64).decode_merge(big_q, b200kv.pool_view(pool), to_dev_i32(np.zeros((16, 4))),
+                                                  to_dev_i32(np.zeros(16)), bs, 1.0 / 24.0,
+                                                  torch.zeros((16, 64, 512), dtype=torch.bfloat16, device="cuda"),
+                                                  workspace=ws)
 
 
 def test_peer_merge_wait_runs_out_when_a_peer_never_arrives():
