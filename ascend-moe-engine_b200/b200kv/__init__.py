@@ -639,6 +639,128 @@ class Arena:
         return view
 
 
+class EngineConfig(Structure):
+    """b200kv_engine_config (include/b200kv.h)."""
+
+    _fields_ = [("layers", c_int32), ("max_seqs", c_int32), ("num_blocks", c_int32), ("block_size", c_int32),
+                ("max_blocks_per_seq", c_int32), ("max_step_tokens", c_int32), ("scale", c_float), ("eps", c_float),
+                ("backend", c_int32)]
+
+
+class Engine:
+    """The KV path as the engine drives it, batched (b200kv_engine_*): Build once, then per step begin_step, per
+    layer layer_append / layer_attend, end_step. Device tensors are torch tensors; nothing here allocates them."""
+
+    def __init__(self, layers: int, max_seqs: int, num_blocks: int, block_size: int, max_blocks_per_seq: int,
+                 max_step_tokens: int, scale: float, eps: float = 1e-6, backend: int = 0):
+        lib.b200kv_engine_create.restype = c_void_p
+        lib.b200kv_engine_create.argtypes = [POINTER(EngineConfig)]
+        lib.b200kv_engine_destroy.restype = None
+        lib.b200kv_engine_destroy.argtypes = [c_void_p]
+        for name in ("arena", "cache", "block_pool", "status"):
+            fn = getattr(lib, f"b200kv_engine_{name}")
+            fn.restype = c_void_p
+            fn.argtypes = [c_void_p]
+        for name in ("admit", "release"):
+            fn = getattr(lib, f"b200kv_engine_{name}")
+            fn.restype = c_int32
+            fn.argtypes = [c_void_p, c_int32]
+        lib.b200kv_engine_begin_step.restype = c_int32
+        lib.b200kv_engine_begin_step.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_void_p]
+        lib.b200kv_engine_layer_append.restype = c_int32
+        lib.b200kv_engine_layer_append.argtypes = [c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                                   c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p]
+        lib.b200kv_engine_layer_attend.restype = c_int32
+        lib.b200kv_engine_layer_attend.argtypes = [c_void_p, c_int32, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p]
+        lib.b200kv_engine_end_step.restype = c_int32
+        lib.b200kv_engine_end_step.argtypes = [c_void_p]
+        lib.b200kv_engine_stats_json.restype = c_int64
+        lib.b200kv_engine_stats_json.argtypes = [c_void_p, c_char_p, c_int64]
+        lib.b200kv_arena_allocations.restype = c_int32
+        lib.b200kv_arena_allocations.argtypes = [c_void_p]
+        lib.b200kv_arena_address.restype = c_void_p
+        lib.b200kv_arena_address.argtypes = [c_void_p, c_int64]
+        lib.b200kv_arena_sealed.restype = c_int32
+        lib.b200kv_arena_sealed.argtypes = [c_void_p]
+        self.config = EngineConfig(layers, max_seqs, num_blocks, block_size, max_blocks_per_seq, max_step_tokens, scale,
+                                   eps, backend)
+        self._h = lib.b200kv_engine_create(ctypes.byref(self.config))
+        if not self._h:
+            raise B200KVError(ERR_INVALID, last_error())
+
+    def close(self):
+        if self._h and lib is not None:
+            lib.b200kv_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    @property
+    def cache(self) -> KvCache:
+        return ctypes.cast(lib.b200kv_engine_cache(self._h), POINTER(KvCache)).contents
+
+    @property
+    def allocations(self) -> int:
+        return int(lib.b200kv_arena_allocations(lib.b200kv_engine_arena(self._h)))
+
+    @property
+    def sealed(self) -> bool:
+        return bool(lib.b200kv_arena_sealed(lib.b200kv_engine_arena(self._h)))
+
+    def span_address(self, handle: int) -> int:
+        return int(lib.b200kv_arena_address(lib.b200kv_engine_arena(self._h), handle))
+
+    def admit(self, seq: int):
+        check(lib.b200kv_engine_admit(self._h, seq))
+
+    def release(self, seq: int):
+        check(lib.b200kv_engine_release(self._h, seq))
+
+    def seq_len(self, seq: int) -> int:
+        return int(lib.b200kv_block_pool_seq_len(lib.b200kv_engine_block_pool(self._h), seq))
+
+    def table(self):
+        import numpy as np
+
+        ptr = lib.b200kv_block_pool_table(lib.b200kv_engine_block_pool(self._h))
+        c = self.config
+        return np.ctypeslib.as_array(ptr, shape=(c.max_seqs, c.max_blocks_per_seq)).copy()
+
+    def begin_step(self, seqs, new_tokens=None, stream=None):
+        import numpy as np
+
+        ids = np.ascontiguousarray(seqs, dtype=np.int32)
+        grow = None if new_tokens is None else np.ascontiguousarray(new_tokens, dtype=np.int32)
+        check(lib.b200kv_engine_begin_step(self._h, ids.ctypes.data, None if grow is None else grow.ctypes.data, len(ids),
+                                           _stream_handle(stream) if self.config.backend == 0 else None))
+
+    def layer_append(self, layer: int, kv_a, gamma, cos, sin, q_rope=None, stream=None):
+        check(lib.b200kv_engine_layer_append(
+            self._h, layer, _ptr(kv_a), kv_a.stride(0), _ptr(gamma), _ptr(cos), cos.stride(0) if cos.dim() == 2 else 0,
+            _ptr(sin), sin.stride(0) if sin.dim() == 2 else 0, _ptr(q_rope),
+            0 if q_rope is None else q_rope.stride(0), 0 if q_rope is None else q_rope.stride(1), _stream_handle(stream)))
+
+    def layer_attend(self, layer: int, q, out, out_fp8=None, out_scales=None, stream=None):
+        check(lib.b200kv_engine_layer_attend(self._h, layer, _ptr(q), q.stride(0), q.stride(1), _ptr(out), _ptr(out_fp8),
+                                             _ptr(out_scales), _stream_handle(stream)))
+
+    def end_step(self):
+        check(lib.b200kv_engine_end_step(self._h))
+
+    def status(self):
+        """The engine's device status word as a tensor over the arena."""
+        import torch
+
+        return device_tensor(int(lib.b200kv_engine_status(self._h)), (4,), torch.int32)
+
+    def stats_json(self) -> str:
+        buf = ctypes.create_string_buffer(512)
+        lib.b200kv_engine_stats_json(self._h, buf, 512)
+        return buf.value.decode()
+
+
 class _RawDeviceMemory:
     """Memory someone else owns, described for torch through the CUDA array interface."""
 

@@ -28,6 +28,7 @@ SOURCES = [
     "kv_partition.cpp",
     "aclnn_shim.cu", "aclnn_other_ops.cu", "kv_stages.cu", "kv_peer.cu", "kv_indexer.cu",
     "no_alloc.cu",
+    "kv_engine.cpp",
 ]
 
 NVCC_FLAGS = [

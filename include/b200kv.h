@@ -461,6 +461,61 @@ int32_t b200kv_kv_cache_layer_view(const b200kv_arena* arena, const b200kv_kv_ca
                                    b200kv_pool_view* out);
 
 /* ------------------------------------------------------------------------------------------------
+ * The path as the engine drives it, batched. What Dsv4Pipeline::Build and ::DecodeStep do for the paged cache and
+ * the attention stages (src/pipeline/pipeline.cpp:212-258, 496-537), for max_seqs sequences and for prefill chunks
+ * of many tokens where the reference keeps one sequence and one token per step
+ * (src/memory/static_arena_manager.cpp:37-39; src/pipeline/pipeline.cpp:40, 515-519; apps/moe_runner.cpp:434-439).
+ *   create        Build: the KV spans reserved in a static arena, the attention workspace noted, one Commit, the
+ *                 workspace, Seal; the block pool; one pinned block for the per-step upload. Nothing allocates
+ *                 afterwards.
+ *   admit/release a sequence enters with no tokens / leaves and its blocks return to the free list.
+ *   begin_step    seqs[i] grows by new_tokens[i] tokens (null: one each, a decode step; more: a prefill chunk).
+ *                 Plan, then commit: a step that does not fit (tokens per step, blocks per sequence, free blocks)
+ *                 is refused and changes nothing. The step's table rows (row i = seqs[i]), lengths and slots go
+ *                 to the device with ONE copy (the reference's slot mailbox, :515-519).
+ *   layer_append  stages 6-8 of the reference's layer (kv_a_norm, rope, kv_cache_write) for the step's new tokens,
+ *                 rows in step order (all tokens of seqs[0], then seqs[1], ...): b200kv_append_fused.
+ *   layer_attend  stage 9 (decode attention of the step's sequences over their whole context) and, when out_fp8
+ *                 is given, stage 10 (MX quantisation of the output): decode steps only.
+ *   end_step      the step made no allocation (the reference asserts this per step, :502-503, 535-536) and the
+ *                 block pool's invariants hold.
+ * Tensors are device pointers, bf16, strides in elements; q is [n_seqs][64][576] with its rope part already
+ * rotated or rotated in place by layer_append (q_rope). The status word lives in the arena.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct b200kv_engine b200kv_engine;
+typedef struct b200kv_engine_config {
+  int32_t layers;
+  int32_t max_seqs;
+  int32_t num_blocks;         /* per layer, shared by all sequences */
+  int32_t block_size;         /* rows per block, a multiple of 64 */
+  int32_t max_blocks_per_seq; /* columns of the block table */
+  int32_t max_step_tokens;    /* new tokens per step: max_seqs for decode, a prefill chunk's total otherwise */
+  float scale;                /* softmax scale */
+  float eps;                  /* RMSNorm epsilon (the reference passes 1e-6) */
+  int32_t backend;            /* B200KV_ARENA_DEVICE; B200KV_ARENA_HOST_SIM runs the bookkeeping without a GPU */
+} b200kv_engine_config;
+
+b200kv_engine* b200kv_engine_create(const b200kv_engine_config* config);
+void b200kv_engine_destroy(b200kv_engine* engine);
+const b200kv_arena* b200kv_engine_arena(const b200kv_engine* engine);
+const b200kv_kv_cache* b200kv_engine_cache(const b200kv_engine* engine);
+const b200kv_block_pool* b200kv_engine_block_pool(const b200kv_engine* engine);
+b200kv_status_word* b200kv_engine_status(const b200kv_engine* engine);
+int32_t b200kv_engine_admit(b200kv_engine* engine, int32_t seq);
+int32_t b200kv_engine_release(b200kv_engine* engine, int32_t seq);
+int32_t b200kv_engine_begin_step(b200kv_engine* engine, const int32_t* seqs, const int32_t* new_tokens, int32_t n_seqs,
+                                 void* stream);
+int32_t b200kv_engine_layer_append(b200kv_engine* engine, int32_t layer, const void* kv_a, int64_t kv_a_stride,
+                                   const void* gamma, const void* cos, int64_t cos_stride, const void* sin,
+                                   int64_t sin_stride, void* q_rope, int64_t q_token_stride, int64_t q_head_stride,
+                                   void* stream);
+int32_t b200kv_engine_layer_attend(b200kv_engine* engine, int32_t layer, const void* q, int64_t q_seq_stride,
+                                   int64_t q_head_stride, void* out, void* out_fp8, void* out_scales, void* stream);
+int32_t b200kv_engine_end_step(b200kv_engine* engine);
+/* The "paged_attention" object of the reference's diagnostics for the engine's current state. */
+int64_t b200kv_engine_stats_json(const b200kv_engine* engine, char* buffer, int64_t capacity);
+
+/* ------------------------------------------------------------------------------------------------
  * Multi-GPU work partition (host). No counterpart in the reference, which runs on one device
  * (include/moe/core/config.hpp:280).
  * ---------------------------------------------------------------------------------------------- */
