@@ -182,6 +182,18 @@ def _load() -> ctypes.CDLL:
 lib = _load()
 
 
+def fault_inject(entry_point: str, after_calls: int = 0) -> None:
+    """The call of `entry_point` after the next `after_calls` ones fails on the host with ERR_RUNTIME (tests)."""
+    lib.b200kv_fault_inject.restype = c_int32
+    lib.b200kv_fault_inject.argtypes = [c_char_p, c_int32]
+    check(lib.b200kv_fault_inject(entry_point.encode(), after_calls))
+
+
+def fault_clear() -> int:
+    lib.b200kv_fault_clear.restype = c_int64
+    return int(lib.b200kv_fault_clear())
+
+
 def last_error() -> str:
     return (lib.b200kv_last_error() or b"").decode()
 
@@ -748,6 +760,19 @@ class Engine:
 
     def end_step(self):
         check(lib.b200kv_engine_end_step(self._h))
+
+    def abort_step(self):
+        lib.b200kv_engine_abort_step.restype = c_int32
+        lib.b200kv_engine_abort_step.argtypes = [c_void_p]
+        check(lib.b200kv_engine_abort_step(self._h))
+
+    def free_list(self):
+        import numpy as np
+
+        pool = lib.b200kv_engine_block_pool(self._h)
+        out = np.empty(self.config.num_blocks, dtype=np.int32)
+        n = lib.b200kv_block_pool_export_free(pool, out.ctypes.data, self.config.num_blocks)
+        return out[:n].copy()
 
     def status(self):
         """The engine's device status word as a tensor over the arena."""

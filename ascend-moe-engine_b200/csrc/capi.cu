@@ -1,7 +1,11 @@
 // C-ABI entry points that are not pure kernel launches: error text, decode dispatch, merge, and the
 // seeded device-side generator.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
 
 #include "common.cuh"
 #include "kv_peer.cuh"
@@ -17,6 +21,31 @@ void SetLastError(const char* fmt, ...) {
   va_start(args, fmt);
   vsnprintf(g_error, sizeof(g_error), fmt, args);
   va_end(args);
+}
+
+// ---- host-side fault injection -------------------------------------------------------------------------
+// Tests of failure handling make a named entry point fail BEFORE it reaches the device, as the reference's
+// stand-in runtime does (mock/runtime_faults.cpp:8-23: FailRuntimeCall(name, calls) lets `calls` calls of that
+// name through and fails the next). Nothing on the GPU is ever made to fault. Off unless armed: one relaxed
+// load per call.
+namespace {
+std::atomic<bool> g_fault_armed{false};
+std::mutex g_fault_mutex;
+std::string g_fault_name;
+int32_t g_fault_remaining = 0;
+int64_t g_fault_fired = 0;
+}  // namespace
+
+int32_t FaultCheck(const char* entry_point) {
+  if (!g_fault_armed.load(std::memory_order_relaxed)) return B200KV_OK;
+  std::lock_guard<std::mutex> lock(g_fault_mutex);
+  if (g_fault_name != entry_point) return B200KV_OK;
+  if (g_fault_remaining-- > 0) return B200KV_OK;
+  g_fault_armed.store(false, std::memory_order_relaxed);
+  g_fault_name.clear();
+  ++g_fault_fired;
+  SetLastError("injected failure: %s", entry_point);
+  return B200KV_ERR_RUNTIME;
 }
 
 int32_t CheckCuda(cudaError_t err, const char* what) {
@@ -104,6 +133,27 @@ using namespace b200kv;
 
 extern "C" const char* b200kv_last_error(void) { return g_error; }
 
+extern "C" int32_t b200kv_fault_inject(const char* entry_point, int32_t after_calls) {
+  if (entry_point == nullptr || after_calls < 0) {
+    SetLastError("fault_inject: a name and a count of calls to let through (>= 0)");
+    return entry_point == nullptr ? B200KV_ERR_NULLPTR : B200KV_ERR_INVALID;
+  }
+  std::lock_guard<std::mutex> lock(g_fault_mutex);
+  g_fault_name = entry_point;
+  g_fault_remaining = after_calls;
+  g_fault_armed.store(true, std::memory_order_relaxed);
+  return B200KV_OK;
+}
+
+extern "C" int64_t b200kv_fault_clear(void) {
+  std::lock_guard<std::mutex> lock(g_fault_mutex);
+  g_fault_armed.store(false, std::memory_order_relaxed);
+  g_fault_name.clear();
+  const int64_t fired = g_fault_fired;
+  g_fault_fired = 0;
+  return fired;
+}
+
 extern "C" int32_t b200kv_abi_version(void) { return 3; }
 
 extern "C" size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas) {
@@ -121,6 +171,7 @@ extern "C" int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* strea
     return B200KV_ERR_NULLPTR;
   }
   const b200kv_decode_args& a = *args;
+  if (int32_t rc = FaultCheck("b200kv_mla_decode")) return rc;
   if (int32_t rc = ValidateDecodeArgs(a, "decode")) return rc;
   if (a.batch == 0) return B200KV_OK;
   const bool tc_ok = TcSupports(a);
@@ -153,6 +204,7 @@ extern "C" int32_t b200kv_mla_decode_peer(const b200kv_decode_args* args, void* 
     return B200KV_ERR_NULLPTR;
   }
   const b200kv_decode_args& a = *args;
+  if (int32_t rc = FaultCheck("b200kv_mla_decode_peer")) return rc;
   if (int32_t rc = ValidateDecodeArgs(a, "decode_peer")) return rc;
   if (a.batch == 0) return B200KV_OK;
   if (a.out == nullptr || a.partial_o != nullptr || world < 1 || world > kPeerMaxWorld || rank < 0 || rank >= world ||
@@ -188,6 +240,7 @@ extern "C" int32_t b200kv_mla_decode_peer(const b200kv_decode_args* args, void* 
 
 extern "C" int32_t b200kv_lse_merge(const float* partial_o, const float* partial_m, const float* partial_l,
                                     int32_t n_parts, int64_t rows, void* out_bf16, float* lse, void* stream) {
+  if (int32_t rc = FaultCheck("b200kv_lse_merge")) return rc;
   if (rows == 0) return B200KV_OK;
   if (partial_o == nullptr || partial_m == nullptr || partial_l == nullptr || out_bf16 == nullptr) {
     SetLastError("lse_merge: partial buffers and out must be non-null");

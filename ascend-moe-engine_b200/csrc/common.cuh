@@ -12,6 +12,9 @@ namespace b200kv {
 // Host: per-thread error text behind b200kv_last_error().
 void SetLastError(const char* fmt, ...);
 int32_t CheckCuda(cudaError_t err, const char* what);
+// Host-side fault injection (b200kv_fault_inject): B200KV_ERR_RUNTIME when this call of `entry_point` is the one a
+// test asked to fail, before anything reaches the device; B200KV_OK otherwise.
+int32_t FaultCheck(const char* entry_point);
 
 // Device: record the first error in the caller's status word and carry on. Kernels never trap:
 // the failing access is skipped and the host reads the word after its next synchronisation.

@@ -158,6 +158,30 @@ extern "C" int32_t b200kv_block_pool_grow(b200kv_block_pool* pool, int32_t seq, 
   return B200KV_OK;
 }
 
+// Takes back the last n_tokens of a sequence and returns the blocks that empties to the FRONT of the free
+// list, newest first: undoing the most recent grows in reverse order restores tables, lengths and the free
+// list exactly (a step that is abandoned half way leaves no trace).
+extern "C" int32_t b200kv_block_pool_ungrow(b200kv_block_pool* pool, int32_t seq, int32_t n_tokens) {
+  if (!SeqInRange(pool, seq, "ungrow")) return pool ? B200KV_ERR_INVALID : B200KV_ERR_NULLPTR;
+  if (!pool->live[seq] || n_tokens < 0 || n_tokens > pool->lens[seq]) {
+    SetLastError("ungrow: sequence %d live=%d holds %d tokens, %d to take back", seq, static_cast<int>(pool->live[seq]),
+                 pool->lens[seq], n_tokens);
+    return B200KV_ERR_INVALID;
+  }
+  const int32_t new_len = pool->lens[seq] - n_tokens;
+  const int32_t keep = (new_len + pool->block_size - 1) / pool->block_size;
+  int32_t* row = pool->table + static_cast<size_t>(seq) * pool->max_blocks_per_seq;
+  for (int32_t i = pool->used_blocks[seq] - 1; i >= keep; --i) {
+    pool->head = pool->head == 0 ? pool->num_blocks - 1 : pool->head - 1;
+    pool->ring[pool->head] = row[i];
+    ++pool->free_count;
+    row[i] = 0;
+  }
+  pool->used_blocks[seq] = keep;
+  pool->lens[seq] = new_len;
+  return B200KV_OK;
+}
+
 extern "C" int32_t b200kv_block_pool_release(b200kv_block_pool* pool, int32_t seq) {
   if (!SeqInRange(pool, seq, "release")) return pool ? B200KV_ERR_INVALID : B200KV_ERR_NULLPTR;
   if (!pool->live[seq]) {

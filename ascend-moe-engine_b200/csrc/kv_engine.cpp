@@ -26,6 +26,7 @@
 namespace b200kv {
 void SetLastError(const char* fmt, ...);
 int32_t CheckCuda(cudaError_t err, const char* what);
+int32_t FaultCheck(const char* entry_point);
 }  // namespace b200kv
 
 using b200kv::CheckCuda;
@@ -53,8 +54,8 @@ struct b200kv_engine {
   int32_t allocations_at_begin = 0;
   int64_t steps = 0;
   int64_t active_tokens = 0;
-  std::vector<int32_t> scratch_slots;  // sized at Build
-  std::vector<int32_t> step_seq_ids;   // sized at Build
+  std::vector<int32_t> step_seq_ids;   // sized at Build: the step's sequences and by how much each grew
+  std::vector<int32_t> step_grown;
 };
 
 namespace {
@@ -126,8 +127,8 @@ extern "C" b200kv_engine* b200kv_engine_create(const b200kv_engine_config* confi
   std::memset(e->staging, 0, e->staging_bytes);
   e->pool = b200kv_block_pool_create(c.num_blocks, c.block_size, c.max_seqs, c.max_blocks_per_seq, nullptr);
   if (e->pool == nullptr) return fail();
-  e->scratch_slots.resize(static_cast<size_t>(c.max_step_tokens));
   e->step_seq_ids.resize(static_cast<size_t>(c.max_seqs));
+  e->step_grown.resize(static_cast<size_t>(c.max_seqs));
   if (b200kv_arena_seal(e->arena) != B200KV_OK) return fail();
   return e;
 }
@@ -219,24 +220,46 @@ extern "C" int32_t b200kv_engine_begin_step(b200kv_engine* e, const int32_t* seq
                 static_cast<size_t>(e->cfg.max_blocks_per_seq) * 4);
     s_lens[i] = b200kv_block_pool_seq_len(e->pool, seqs[i]);
     e->step_seq_ids[static_cast<size_t>(i)] = seqs[i];
+    e->step_grown[static_cast<size_t>(i)] = n;
   }
   for (int32_t i = at; i < e->cfg.max_step_tokens; ++i) s_slots[i] = -1;  // padding rows write nothing
   e->allocations_at_begin = b200kv_arena_allocations(e->arena);
-  if (e->cfg.backend == B200KV_ARENA_DEVICE) {
-    // ONE upload per step: the table rows, the slots and the lengths lie in the arena in this order.
-    if (int32_t rc = CheckCuda(cudaMemcpyAsync(e->d_table, e->staging, e->staging_bytes, cudaMemcpyHostToDevice,
-                                               static_cast<cudaStream_t>(stream)),
-                               "engine step upload")) {
-      return rc;
-    }
-  } else {
-    std::memcpy(e->d_table, e->staging, e->staging_bytes);
-  }
-  e->in_step = true;
   e->step_seqs = n_seqs;
   e->step_tokens = at;
+  // ONE upload per step: the table rows, the slots and the lengths lie in the arena in this order. An upload
+  // that fails takes the step's growth back: the call changed nothing.
+  int32_t rc = b200kv::FaultCheck("b200kv_engine_step_upload");
+  if (rc == B200KV_OK) {
+    if (e->cfg.backend == B200KV_ARENA_DEVICE) {
+      rc = CheckCuda(cudaMemcpyAsync(e->d_table, e->staging, e->staging_bytes, cudaMemcpyHostToDevice,
+                                     static_cast<cudaStream_t>(stream)),
+                     "engine step upload");
+    } else {
+      std::memcpy(e->d_table, e->staging, e->staging_bytes);
+    }
+  }
+  if (rc != B200KV_OK) {
+    for (int32_t i = n_seqs - 1; i >= 0; --i) b200kv_block_pool_ungrow(e->pool, seqs[i], e->step_grown[static_cast<size_t>(i)]);
+    return rc;
+  }
+  e->in_step = true;
   e->active_tokens += at;
   return B200KV_OK;
+}
+
+extern "C" int32_t b200kv_engine_abort_step(b200kv_engine* e) {
+  if (e == nullptr) return B200KV_ERR_NULLPTR;
+  if (!e->in_step) return Refuse("engine_abort_step: no step in flight");
+  // The step's growth is taken back newest first, which restores tables, lengths and the free list exactly.
+  // Rows the step's launches already wrote lie beyond every sequence's length and mean nothing.
+  for (int32_t i = e->step_seqs - 1; i >= 0; --i) {
+    if (int32_t rc = b200kv_block_pool_ungrow(e->pool, e->step_seq_ids[static_cast<size_t>(i)], e->step_grown[static_cast<size_t>(i)])) {
+      return rc;
+    }
+  }
+  e->active_tokens -= e->step_tokens;
+  e->in_step = false;
+  return b200kv_block_pool_validate(e->pool);
 }
 
 extern "C" int32_t b200kv_engine_layer_append(b200kv_engine* e, int32_t layer, const void* kv_a, int64_t kv_a_stride,

@@ -191,6 +191,7 @@ extern "C" size_t b200kv_indexer_workspace_bytes(int32_t batch, int64_t max_kv_l
 }
 
 extern "C" int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* stream, b200kv_status_word* status) {
+  if (int32_t rc = FaultCheck("b200kv_indexer_topk")) return rc;
   if (args == nullptr) {
     SetLastError("indexer_topk: args is null");
     return B200KV_ERR_NULLPTR;

@@ -280,6 +280,7 @@ using namespace b200kv;
 extern "C" int32_t b200kv_append(const b200kv_pool_view* pool, const void* latent_src, int64_t src_latent_stride,
                                  const void* rope_src, int64_t src_rope_stride, const int32_t* slot_mapping,
                                  int64_t n_tokens, void* stream, b200kv_status_word* status) {
+  if (int32_t rc = FaultCheck("b200kv_append")) return rc;
   if (int32_t rc = CheckPool(pool)) return rc;
   if (n_tokens == 0) return B200KV_OK;
   if (latent_src == nullptr || rope_src == nullptr || slot_mapping == nullptr) {
@@ -307,6 +308,7 @@ extern "C" int32_t b200kv_gather(const b200kv_pool_view* pool, const int32_t* bl
                                  int64_t out_latent_stride, void* out_rope, int64_t out_rope_stride,
                                  const int64_t* out_row_offsets, int64_t total_rows, void* stream,
                                  b200kv_status_word* status) {
+  if (int32_t rc = FaultCheck("b200kv_gather")) return rc;
   if (int32_t rc = CheckPool(pool)) return rc;
   if (batch == 0 || total_rows == 0) return B200KV_OK;
   if (block_table == nullptr || kv_len == nullptr || out_latent == nullptr || out_rope == nullptr ||
@@ -336,6 +338,7 @@ extern "C" int32_t b200kv_resolve_rows(const int32_t* block_table, int64_t max_b
                                        const int32_t* token_index, int64_t max_selected, const int32_t* n_selected,
                                        int64_t batch, int64_t pool_rows, int32_t* rows, void* stream,
                                        b200kv_status_word* status) {
+  if (int32_t rc = FaultCheck("b200kv_resolve_rows")) return rc;
   if (batch == 0 || max_selected == 0) return B200KV_OK;
   if (block_table == nullptr || token_index == nullptr || n_selected == nullptr || rows == nullptr) {
     SetLastError("resolve_rows: block_table, token_index, n_selected and rows must be non-null");

@@ -198,6 +198,7 @@ extern "C" int32_t b200kv_peer_buffer_free(void* ptr) {
 extern "C" int32_t b200kv_peer_merge(void* const* peer_buffers, int32_t world, int32_t rank, int64_t rows,
                                      const float* partial_o, const float* partial_m, const float* partial_l,
                                      void* out_bf16, float* lse, void* stream, b200kv_status_word* status) {
+  if (int32_t rc = FaultCheck("b200kv_peer_merge")) return rc;
   if (peer_buffers == nullptr || partial_o == nullptr || partial_m == nullptr || partial_l == nullptr || out_bf16 == nullptr) {
     SetLastError("peer_merge: peer_buffers, the three partial arrays and out must be non-null");
     return B200KV_ERR_NULLPTR;

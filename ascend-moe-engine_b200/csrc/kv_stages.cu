@@ -308,6 +308,7 @@ int32_t ValidatePoolView(const b200kv_pool_view* pool);
 using namespace b200kv;
 
 extern "C" int32_t b200kv_append_fused(const b200kv_producer_args* args, void* stream, b200kv_status_word* status) {
+  if (int32_t rc = FaultCheck("b200kv_append_fused")) return rc;
   if (args == nullptr) {
     SetLastError("append_fused: args is null");
     return B200KV_ERR_NULLPTR;
@@ -415,6 +416,7 @@ extern "C" int32_t b200kv_rope_half64(void* x, int64_t token_stride, int64_t vec
 
 extern "C" int32_t b200kv_mx_quant_e4m3(const void* x, int64_t x_stride, int64_t rows, int64_t cols, void* q,
                                         int64_t q_stride, void* scales, int64_t scale_stride, void* stream) {
+  if (int32_t rc = FaultCheck("b200kv_mx_quant_e4m3")) return rc;
   if (rows == 0 || cols == 0) return B200KV_OK;
   if (x == nullptr || q == nullptr || scales == nullptr) {
     SetLastError("mx_quant_e4m3: x, q and scales must be non-null");

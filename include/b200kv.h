@@ -63,6 +63,19 @@ const char* b200kv_last_error(void);
 int32_t b200kv_abi_version(void);
 
 /*
+ * Host-side fault injection, for tests of failure handling. After b200kv_fault_inject(name, n) the next n calls
+ * of the entry point `name` go through and the one after fails with B200KV_ERR_RUNTIME ("injected failure: name")
+ * before anything reaches the device; then the hook disarms itself. The counterpart of the reference's
+ * FailRuntimeCall(name, calls) (mock/runtime_faults.cpp:8-23, used by tests/mock_failure_teardown.cpp:153-184).
+ * Names: the device entry points b200kv_append, b200kv_gather, b200kv_resolve_rows, b200kv_mla_decode,
+ * b200kv_mla_decode_peer, b200kv_lse_merge, b200kv_peer_merge, b200kv_append_fused, b200kv_mx_quant_e4m3,
+ * b200kv_indexer_topk, and b200kv_engine_step_upload (the per-step copy of b200kv_engine_begin_step).
+ * No GPU fault is ever made. b200kv_fault_clear disarms and returns how many injected failures fired.
+ */
+int32_t b200kv_fault_inject(const char* entry_point, int32_t after_calls);
+int64_t b200kv_fault_clear(void);
+
+/*
  * Append. Replaces the launch of aclnnScatterPaKvCache planned at src/pipeline/pipeline.cpp:226-234
  * (prototype include/moe/core/op_table.hpp:365-372, cache mode "Norm"): for each token row t,
  *   pool.latent[slot[t]] = latent_src[t],  pool.rope[slot[t]] = rope_src[t].
@@ -360,6 +373,9 @@ int32_t b200kv_block_pool_admit(b200kv_block_pool* pool, int32_t seq);
 /* Extends `seq` by n_tokens; writes the new tokens' slots (flat pool rows) to slots_out[0..n). */
 int32_t b200kv_block_pool_grow(b200kv_block_pool* pool, int32_t seq, int32_t n_tokens, int32_t* slots_out);
 int32_t b200kv_block_pool_release(b200kv_block_pool* pool, int32_t seq);
+/* Takes back the last n_tokens of `seq`; blocks that empties return to the FRONT of the free list, so that undoing
+ * the most recent grows in reverse order restores tables, lengths and the free list exactly. */
+int32_t b200kv_block_pool_ungrow(b200kv_block_pool* pool, int32_t seq, int32_t n_tokens);
 int32_t b200kv_block_pool_free_count(const b200kv_block_pool* pool);
 int32_t b200kv_block_pool_seq_len(const b200kv_block_pool* pool, int32_t seq);
 /* Host views: table [max_seqs][max_blocks_per_seq] (unused entries 0), lens [max_seqs]. */
@@ -477,6 +493,7 @@ int32_t b200kv_kv_cache_layer_view(const b200kv_arena* arena, const b200kv_kv_ca
  *                 rows in step order (all tokens of seqs[0], then seqs[1], ...): b200kv_append_fused.
  *   layer_attend  stage 9 (decode attention of the step's sequences over their whole context) and, when out_fp8
  *                 is given, stage 10 (MX quantisation of the output): decode steps only.
+ *   abort_step    a step one of whose launches failed is taken back as a whole.
  *   end_step      the step made no allocation (the reference asserts this per step, :502-503, 535-536) and the
  *                 block pool's invariants hold.
  * Tensors are device pointers, bf16, strides in elements; q is [n_seqs][64][576] with its rope part already
@@ -512,6 +529,9 @@ int32_t b200kv_engine_layer_append(b200kv_engine* engine, int32_t layer, const v
 int32_t b200kv_engine_layer_attend(b200kv_engine* engine, int32_t layer, const void* q, int64_t q_seq_stride,
                                    int64_t q_head_stride, void* out, void* out_fp8, void* out_scales, void* stream);
 int32_t b200kv_engine_end_step(b200kv_engine* engine);
+/* Abandons the step in flight (a launch of it failed): every sequence gives back what the step added, tables,
+ * lengths and the free list are as before begin_step. */
+int32_t b200kv_engine_abort_step(b200kv_engine* engine);
 /* The "paged_attention" object of the reference's diagnostics for the engine's current state. */
 int64_t b200kv_engine_stats_json(const b200kv_engine* engine, char* buffer, int64_t capacity);
 

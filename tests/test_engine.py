@@ -89,3 +89,56 @@ def test_a_step_that_does_not_fit_changes_nothing():
     assert (e.seq_len(0), e.seq_len(1)) == (65, 37)
     with pytest.raises(b200kv.B200KVError):
         e.end_step()              # no step in flight
+
+
+def snapshot(e):
+    return {s: e.seq_len(s) for s in range(4)}, e.table().copy(), e.free_list()
+
+
+def same(a, b):
+    return a[0] == b[0] and np.array_equal(a[1], b[1]) and np.array_equal(a[2], b[2])
+
+
+def test_an_abandoned_step_leaves_no_trace():
+    """abort_step takes the step's growth back newest first: lengths, table rows and the ORDER of the free list
+    are those of before begin_step, however many blocks the step had taken."""
+    e = make(max_step_tokens=200)
+    for s in (0, 1, 3):
+        e.admit(s)
+    e.begin_step([1, 0], [70, 10])
+    e.end_step()
+    before = snapshot(e)
+    e.begin_step([3, 0, 1], [130, 60, 1])      # three new blocks for 3, one for 0, none for 1
+    assert not same(snapshot(e), before)
+    e.abort_step()
+    assert same(snapshot(e), before)
+    with pytest.raises(b200kv.B200KVError):
+        e.abort_step()                          # nothing in flight any more
+    e.begin_step([3, 0, 1], [130, 60, 1])      # the same step again takes the same blocks in the same order
+    after = snapshot(e)
+    e.end_step()
+    assert after[0] == {0: 70, 1: 71, 2: -1, 3: 130}
+
+
+def test_an_injected_upload_failure_is_a_refused_step():
+    """The host-side fault hook fails the n-th call of a named entry point before it reaches the device, as the
+    reference's FailRuntimeCall does for its stand-in runtime. A step whose upload fails changed nothing."""
+    e = make(max_step_tokens=200)
+    e.admit(0)
+    e.admit(1)
+    e.begin_step([0, 1], [65, 3])
+    e.end_step()
+    before = snapshot(e)
+    b200kv.fault_inject("b200kv_engine_step_upload", after_calls=1)
+    e.begin_step([0, 1])                        # the first call goes through
+    e.end_step()
+    mid = snapshot(e)
+    with pytest.raises(b200kv.B200KVError) as err:
+        e.begin_step([1, 0], [64, 64])          # the second is the injected failure
+    assert err.value.code == b200kv.ERR_RUNTIME and "injected failure: b200kv_engine_step_upload" in str(err.value)
+    assert same(snapshot(e), mid) and not same(mid, before)
+    assert b200kv.fault_clear() == 1            # one failure fired, and the hook disarmed itself
+    e.begin_step([1, 0], [64, 64])              # the same step goes through now
+    e.end_step()
+    with pytest.raises(b200kv.B200KVError):
+        b200kv.fault_inject("b200kv_append", -1)

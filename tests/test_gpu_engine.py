@@ -145,3 +145,81 @@ def test_sixteen_decode_steps_of_eight_sequences_after_chunked_prefill():
     assert f'"active_context_tokens": {sum(lens.values())}' in eng.stats_json()
     del latent, rope, status
     eng.close()
+
+
+def test_a_failed_launch_in_mid_step_leaves_pool_and_arena_consistent():
+    """The attention launch of the second layer of a step fails on the host (injected, before it reaches the
+    device: no GPU fault is made). The error comes back as a status, the step is abandoned as a whole
+    (lengths, tables and the free list as before it, no allocation made), the GPU context is unharmed, and the
+    same step then runs to the oracle's result."""
+    layers, bs = 3, 64
+    eng = b200kv.Engine(layers=layers, max_seqs=4, num_blocks=24, block_size=bs, max_blocks_per_seq=6, max_step_tokens=192,
+                        scale=1.0 / 24.0)
+    c = eng.cache
+    rows = 24 * bs
+    latent = b200kv.device_tensor(eng.span_address(c.latent_handle), (layers, rows, 512), torch.bfloat16)
+    rope = b200kv.device_tensor(eng.span_address(c.rope_handle), (layers, rows, 64), torch.bfloat16)
+    gamma = kvo.f32_to_bf16(np.ones(512, dtype=np.float32))
+    d_gamma = to_dev_bf16(gamma)
+    oracle_pool = [np.zeros((rows, 576), dtype=np.uint16) for _ in range(layers)]
+    seqs, prompt = [0, 1, 2], [100, 64, 1]
+    for s in seqs:
+        eng.admit(s)
+    eng.begin_step(seqs, prompt)
+    table = eng.table()
+    slots = np.concatenate([table[s][np.arange(n) // bs].astype(np.int64) * bs + np.arange(n) % bs
+                            for s, n in zip(seqs, prompt)]).astype(np.int32)
+    cos, sin = rope_rows(np.concatenate([np.arange(n) for n in prompt]))
+    for l in range(layers):
+        kv_a = kvo.normal_bf16(len(slots) * 576, 3, first=l * 99991).reshape(-1, 576)
+        eng.layer_append(l, to_dev_bf16(kv_a), d_gamma, to_dev_bf16(cos), to_dev_bf16(sin))
+        kvo.append_fused(oracle_pool[l], kv_a, gamma, cos, sin, slots)
+    eng.end_step()
+    lens = dict(zip(seqs, prompt))
+
+    def decode_step(fail_layer=None):
+        eng.begin_step(seqs)
+        table = eng.table()[seqs]
+        slots = np.array([int(table[i][lens[s] // bs]) * bs + lens[s] % bs for i, s in enumerate(seqs)], dtype=np.int32)
+        cos, sin = rope_rows([lens[s] for s in seqs])
+        kv_len = np.array([lens[s] + 1 for s in seqs], dtype=np.int32)
+        for l in range(layers):
+            kv_a = kvo.normal_bf16(3 * 576, 3, first=7777 + l).reshape(3, 576)
+            q = kvo.make_q(3, seed=kvo.BASE_SEED + l)
+            out = torch.full((3, 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+            eng.layer_append(l, to_dev_bf16(kv_a), d_gamma, to_dev_bf16(cos), to_dev_bf16(sin))
+            if fail_layer is None:
+                kvo.append_fused(oracle_pool[l], kv_a, gamma, cos, sin, slots)
+            eng.layer_attend(l, to_dev_bf16(q), out)      # raises on the injected failure
+            if fail_layer is not None:
+                continue                                   # (the oracle's pool does not follow an abandoned step)
+            want, _ = kvo.mla_decode(q, oracle_pool[l], table, kv_len, bs, 1.0 / 24.0, use_double=True)
+            scenarios.check_attention(from_dev_bf16(out), None, kvo.bf16_to_f32(want).astype(np.float64), None,
+                                      what=f"after the failed step, layer {l}")
+        eng.end_step()
+
+    before = ({s: eng.seq_len(s) for s in seqs}, eng.table().copy(), eng.free_list(), eng.allocations)
+    b200kv.fault_inject("b200kv_mla_decode", after_calls=1)   # layer 0 attends, layer 1's launch fails
+    with pytest.raises(b200kv.B200KVError) as err:
+        decode_step(fail_layer=1)
+    assert err.value.code == b200kv.ERR_RUNTIME and "injected failure: b200kv_mla_decode" in str(err.value)
+    with pytest.raises(b200kv.B200KVError):
+        eng.begin_step(seqs)                                   # the failed step is still in flight
+    eng.abort_step()
+    torch.cuda.synchronize()
+    assert eng.status().cpu().tolist()[0] == 0
+    after = ({s: eng.seq_len(s) for s in seqs}, eng.table().copy(), eng.free_list(), eng.allocations)
+    assert before[0] == after[0] and np.array_equal(before[1], after[1]) and np.array_equal(before[2], after[2])
+    assert before[3] == after[3] and b200kv.fault_clear() == 1
+    decode_step()                                              # the same step, now to the end
+    for s in seqs:
+        lens[s] += 1
+    for l in range(layers):
+        got = np.concatenate([from_dev_bf16(latent[l]), from_dev_bf16(rope[l])], axis=1)
+        live = np.zeros(rows, dtype=bool)
+        for s in seqs:
+            t = np.arange(lens[s])
+            live[eng.table()[s][t // bs].astype(np.int64) * bs + t % bs] = True
+        assert np.array_equal(got[live], oracle_pool[l][live]), f"layer {l}: live rows differ from the oracle's"
+    del latent, rope
+    eng.close()
