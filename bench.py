@@ -376,6 +376,36 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
     bytes_append = rows * (ROW * 2 * 2 + 4)
     res["append"] = {"rows_per_launch": rows, "algorithmic_bytes": bytes_append, "us_per_launch": t * 1e6,
                      "achieved_gbs": bytes_append / t * 1e-9, "frac_of_measured_hbm": bytes_append / t * 1e-9 / hbm_peak}
+    # The same 16,384 rows as the churn configuration's prefill chunk really presents them: 64 sequences x 256
+    # tokens from activations [T][512] and [T][64] into 64-row blocks (runs of 64 consecutive slots) of the two
+    # caches.
+    lat_src = torch.empty((4, rows, LATENT), dtype=torch.bfloat16, device="cuda")
+    rope_src = torch.empty((4, rows, ROW - LATENT), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(lat_src, SEED, 4)
+    b200kv.fill_normal_bf16(rope_src, SEED, 5)
+    block_ids = torch.randperm(wl.blocks, device="cuda", dtype=torch.int64)
+    run_sets = []
+    for i in range(4):
+        ids = block_ids[i * (rows // BLOCK):(i + 1) * (rows // BLOCK)]
+        run_sets.append((ids[:, None] * BLOCK + torch.arange(BLOCK, device="cuda")[None, :]).reshape(-1).to(torch.int32).contiguous())
+
+    def do_append_chunk(i):
+        b200kv.append(wl.views[i % LAYERS], lat_src[i % 4], rope_src[i % 4], run_sets[i % 4], status=wl.status)
+    t = timeit(do_append_chunk, 86)
+    res["append_prefill_chunk"] = {"rows_per_launch": rows, "algorithmic_bytes": bytes_append, "us_per_launch": t * 1e6,
+                                   "achieved_gbs": bytes_append / t * 1e-9,
+                                   "frac_of_measured_hbm": bytes_append / t * 1e-9 / hbm_peak,
+                                   "shape": "64 sequences x 256 tokens into 64-row blocks, sources [T][512] and [T][64]"}
+    # What a plain device-to-device copy of the same bytes reaches at this size (one launch of 18.9 MB read and
+    # 18.9 MB written, eight source and eight destination buffers in turn so that neither side stays in L2): the
+    # ceiling a launch of this size has, whatever the kernel.
+    flat_src = torch.empty((8, bytes_append // 4), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(flat_src, SEED, 6)
+    flat_dst = torch.empty_like(flat_src)
+    t = timeit(lambda i: flat_dst[i % 8].copy_(flat_src[(i + 3) % 8]), 88)
+    res["plain_copy_same_bytes"] = {"bytes": bytes_append, "us_per_launch": t * 1e6,
+                                    "achieved_gbs": bytes_append / t * 1e-9,
+                                    "frac_of_measured_hbm": bytes_append / t * 1e-9 / hbm_peak}
     # Decode-shaped append (32 rows): launch-latency bound, reported as latency.
     t = timeit(lambda i: b200kv.append(wl.views[i % LAYERS], wl.new_rows[i % LAYERS][:, :LATENT],
                                        wl.new_rows[i % LAYERS][:, LATENT:], wl.slots, status=wl.status), 86)
@@ -449,7 +479,7 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
                            "us_per_launch": t * 1e6, "key_bytes": n_rows * 132,
                            "gflop": 2.0 * BATCH * CONTEXT * HEADS * 128 * 1e-9,
                            "tflops_fp32": 2.0 * BATCH * CONTEXT * HEADS * 128 / t * 1e-12}
-    del src, out_l, out_r, trig, fused_src, key8, k_scale
+    del src, out_l, out_r, trig, fused_src, key8, k_scale, lat_src, rope_src, flat_src, flat_dst
     return res
 
 

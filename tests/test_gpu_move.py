@@ -66,6 +66,53 @@ def test_append_split_caches_padding_and_bad_slot_status():
     assert (from_dev_bf16(lat) == want_l).all() and (from_dev_bf16(rope) == want_r).all()
 
 
+@pytest.mark.parametrize("case", ["chunks", "mixed", "scattered"])
+def test_append_through_shared_memory_on_back_to_back_rows(case):
+    """The reference's layout (latent [rows][512] and rope [rows][64] as two arrays, sources of the same shape):
+    runs of consecutive slots move as groups of 16 rows through shared memory with bulk copies, everything else
+    row by row in the same launch. chunks: the churn configuration's prefill chunk (sequences x 256 tokens into
+    64-row blocks). mixed: runs broken by padding, by a slot outside the pool, by block ends at odd offsets and
+    by a ragged tail. scattered: no runs at all."""
+    bs, blocks = 64, 300
+    rows = blocks * bs
+    order = kvo.permutation(blocks)
+    if case == "chunks":
+        slots = np.concatenate([order[4 * s + c].astype(np.int64) * bs + np.arange(bs) for s in range(64) for c in range(4)])
+    elif case == "mixed":
+        pieces, at = [], 0
+        for n in (64, 1, 17, 16, 64, 15, 33, 128, 5, 250):
+            pieces.append(order[at].astype(np.int64) * bs + (7 if n < 50 else 0) + np.arange(min(n, bs)))
+            if n > bs:
+                pieces.append(order[at + 1].astype(np.int64) * bs + np.arange(min(n - bs, bs)))
+            at += 3
+        slots = np.concatenate(pieces)
+        slots[40] = -1           # padding inside a run
+        slots[200] = rows + 5    # outside the pool: recorded, skipped
+        slots = slots[:-3]       # a ragged last group
+    else:
+        slots = kvo.permutation(rows)[:5000].astype(np.int64)
+    slots = slots.astype(np.int32)
+    n = len(slots)
+    src = kvo.normal_bf16(n * kvo.ROW, kvo.STREAM_NEW).reshape(n, kvo.ROW)
+    src_l, src_r = np.ascontiguousarray(src[:, :512]), np.ascontiguousarray(src[:, 512:])
+    want_l = np.full((rows, 512), POISON, dtype=np.uint16)
+    want_r = np.full((rows, 64), POISON, dtype=np.uint16)
+    bad = kvo.append(want_l, src_l, src_r, slots, rope_pool=want_r)
+    assert bad == (1 if case == "mixed" else 0)
+    lat = to_dev_bf16(np.full((rows, 512), POISON, dtype=np.uint16))
+    rope = to_dev_bf16(np.full((rows, 64), POISON, dtype=np.uint16))
+    status = b200kv.new_status()
+    for _ in range(2):   # idempotent
+        b200kv.append(b200kv.pool_view(lat, rope), to_dev_bf16(src_l), to_dev_bf16(src_r), to_dev_i32(slots), status=status)
+    torch.cuda.synchronize()
+    st = status.cpu().tolist()
+    if case == "mixed":
+        assert st[0] == b200kv.DEV_BAD_SLOT and st[1] == 200 and st[2] == rows + 5, st
+    else:
+        assert st[0] == 0, st
+    assert (from_dev_bf16(lat) == want_l).all() and (from_dev_bf16(rope) == want_r).all()
+
+
 def test_append_zero_tokens_is_a_no_op():
     pool = to_dev_bf16(np.full((64, kvo.ROW), POISON, dtype=np.uint16))
     empty = torch.empty((0, kvo.ROW), dtype=torch.bfloat16, device="cuda")
