@@ -109,13 +109,22 @@ int32_t ValidateDecodeArgs(const b200kv_decode_args& a, const char* who) {
   if (int32_t rc = ValidatePoolView(&a.pool)) return rc;
   if (a.batch == 0) return B200KV_OK;
   const bool want_partial = a.partial_o != nullptr || a.partial_m != nullptr || a.partial_l != nullptr;
-  if (a.q == nullptr || a.block_table == nullptr || a.kv_len == nullptr ||
+  if (a.q == nullptr || (a.block_table == nullptr && a.row_index == nullptr) || a.kv_len == nullptr ||
       (want_partial && (a.partial_o == nullptr || a.partial_m == nullptr || a.partial_l == nullptr)) ||
       (!want_partial && a.out == nullptr)) {
-    SetLastError("%s: q, block_table, kv_len and either out or all three partial_* buffers must be non-null", who);
+    SetLastError("%s: q, block_table (or row_index), kv_len and either out or all three partial_* buffers must be non-null", who);
     return B200KV_ERR_NULLPTR;
   }
-  if (a.batch < 0 || a.heads <= 0 || a.block_size <= 0 || a.max_blocks <= 0 || a.pool.pool_rows % a.block_size != 0 ||
+  if (a.row_index != nullptr) {
+    if (a.row_index_stride <= 0 || a.kv_begin != nullptr || a.new_latent != nullptr || a.new_rope != nullptr) {
+      SetLastError("%s refused: row_index wants a positive row_index_stride (%lld given), no kv_begin and no fused append",
+                   who, static_cast<long long>(a.row_index_stride));
+      return B200KV_ERR_INVALID;
+    }
+  }
+  const bool table_ok = a.row_index != nullptr ||
+                        (a.block_size > 0 && a.max_blocks > 0 && a.pool.pool_rows % a.block_size == 0);
+  if (a.batch < 0 || a.heads <= 0 || !table_ok ||
       !(a.scale > 0.0f) || a.q_head_stride < B200KV_LATENT_DIM + B200KV_ROPE_DIM || a.q_head_stride % 2 != 0 ||
       a.q_seq_stride % 2 != 0 || (a.batch > 1 && a.q_seq_stride < 0) || (reinterpret_cast<uintptr_t>(a.q) & 3u) != 0 ||
       (a.variant != B200KV_DECODE_AUTO && a.variant != B200KV_DECODE_SIMT && a.variant != B200KV_DECODE_TCGEN05)) {
@@ -154,7 +163,7 @@ extern "C" int64_t b200kv_fault_clear(void) {
   return fired;
 }
 
-extern "C" int32_t b200kv_abi_version(void) { return 3; }
+extern "C" int32_t b200kv_abi_version(void) { return 4; }
 
 extern "C" size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas) {
   if (batch <= 0 || heads <= 0) return 0;
@@ -176,8 +185,8 @@ extern "C" int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* strea
   if (a.batch == 0) return B200KV_OK;
   const bool tc_ok = TcSupports(a);
   if (a.variant == B200KV_DECODE_TCGEN05 && !tc_ok) {
-    SetLastError("decode: the tcgen05 kernel needs 64 heads, block_size %% 64 == 0, 16-byte aligned q with strides "
-                 "that are multiples of 8 elements");
+    SetLastError("decode: the tcgen05 kernel needs 64 heads, block_size %% 64 == 0 (or row_index), 16-byte aligned q "
+                 "with strides that are multiples of 8 elements");
     return B200KV_ERR_INVALID;
   }
   const bool use_tc = a.variant == B200KV_DECODE_TCGEN05 || (a.variant == B200KV_DECODE_AUTO && tc_ok);
@@ -194,6 +203,14 @@ extern "C" int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* strea
     return a.workspace == nullptr ? B200KV_ERR_NULLPTR : B200KV_ERR_INVALID;
   }
   if (use_tc) return LaunchMlaDecodeTc(a, ctas, static_cast<cudaStream_t>(stream), status, nullptr);
+  if (a.row_index != nullptr) {  // the CUDA-core kernel reads a row list as a table of single-row blocks
+    b200kv_decode_args as_table = a;
+    as_table.block_table = a.row_index;
+    as_table.max_blocks = a.row_index_stride;
+    as_table.block_size = 1;
+    as_table.row_index = nullptr;
+    return LaunchMlaDecodeSimt(as_table, static_cast<cudaStream_t>(stream), status);
+  }
   return LaunchMlaDecodeSimt(a, static_cast<cudaStream_t>(stream), status);
 }
 

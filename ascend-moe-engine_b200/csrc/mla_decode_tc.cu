@@ -116,6 +116,8 @@ struct TcParams {
   int32_t block_size;
   int32_t stable_tables;  // lengths and block table may be read before the stream dependency wait
   int32_t force_ws;       // every segment leaves a partial in the workspace, one that covers its sequence too
+  const int32_t* row_index;  // [B][row_index_stride]: the pool rows to attend over, in place of the block table; or null
+  int64_t row_index_stride;
   float scale_log2;  // scale * log2(e)
   __nv_bfloat16* out;
   float* lse;
@@ -344,6 +346,47 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::TmaLoad2DHint(dst, &rope_map, 0, static_cast<int32_t>(row), full, drop_policy);
     }
   };
+  // A tile of gathered rows (row_index in place of the block table): entries 64 t .. 64 t + 63 of the sequence's
+  // row list, four rows per load. Lane l takes rows 4 (l % 16) .. + 3 of the tile in the slabs of its parity (lanes
+  // 0-15: slabs 0, 2, 4, 6, 8; lanes 16-31: 1, 3, 5, 7): 144 loads of 512 bytes a tile, four or five a lane. The
+  // warp takes the tile group by group as PV gives the stage back, lane 0 announcing each group's bytes first.
+  // Entries past the sequence's length are not read (their rows load as row 0 and the softmax masks them); an
+  // entry inside it that is not a row of the pool is recorded and reads row 0.
+  auto issue_gathered = [&](int seq, int seq_len, int t, int g) -> bool {
+    const int stage = g % kStages;
+    const int first = t * kTile + 4 * (lane & 15);
+    int r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int j = first + i;
+      int row = 0;
+      if (j < seq_len && j < p.row_index_stride) {
+        row = p.row_index[static_cast<int64_t>(seq) * p.row_index_stride + j];
+        if (row < 0 || row >= p.pool_rows) {
+          RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, j, row);
+          row = 0;
+        }
+      }
+      r[i] = row;
+    }
+    const uint32_t dst = kv_addr + stage * kStageBytes + (lane & 15) * (4 * 128);
+    bool ok = true;
+    for (int c = 0; c < kGroups && ok; ++c) {
+      if (g >= kStages) {
+        ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_empty[stage][c]), ((g / kStages) & 1) ^ 1, misc, p.status, 10));
+        if (!ok) break;
+      }
+      const uint32_t full = bar(&misc->kv_full[stage][c]);
+      if (lane == 0) ptx::MbarArriveExpectTx(full, (c == kGroups - 1 ? 3 : 2) * kSlabBytes);
+      __syncwarp();
+      const int slab = 2 * c + (lane >> 4);
+      ptx::TmaGather4Hint(dst + slab * kSlabBytes, &latent_map, 64 * slab, r[0], r[1], r[2], r[3], full, drop_policy);
+      if (c == kGroups - 1 && lane < 16) {
+        ptx::TmaGather4Hint(dst + 8 * kSlabBytes, &rope_map, 0, r[0], r[1], r[2], r[3], full, drop_policy);
+      }
+    }
+    return ok;
+  };
   // Fused append, first half: the new row of `seq` starts towards shared memory.
   auto new_row_fetch = [&](int seq) {
     const uint32_t full = bar(&misc->new_row_full);
@@ -490,7 +533,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       // A tile that a fused append still has to write into is left to the main loop.
       const int t_end = min(start_seq_tiles - (p.new_latent != nullptr ? 1 : 0), start_tile + static_cast<int>(hi - lo));
       static_assert(kStages == 2, "the first tiles' rows are looked up before the dependency wait, two of them");
-      const int n_first = max(0, min(kStages, t_end - start_tile));
+      // (Gathered rows: every tile goes out from the main loop, which reads the row numbers after the wait.)
+      const int n_first = p.row_index != nullptr ? 0 : max(0, min(kStages, t_end - start_tile));
       const int64_t row0 = n_first > 0 ? tile_row(start_seq, begin, start_tile) : 0;
       const int64_t row1 = n_first > 1 ? tile_row(start_seq, begin, start_tile + 1) : 0;
       if (p.stable_tables != 0) GridDependencyWait();  // Q and the pool are the preceding kernels' to write
@@ -553,6 +597,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         for (int t = t_lo; t < t_hi; ++t, ++g) {
           if (g < pre_issued) continue;
+          if (p.row_index != nullptr) {
+            ok = issue_gathered(seq, seq_len, t, g);
+            if (!ok) break;
+            continue;
+          }
           const int64_t checked_row = tile_row_checked(seq, begin, t);
           const int64_t row = checked_row < 0 ? 0 : checked_row;
           if (appends && t == seq_tiles - 1) {
@@ -1380,8 +1429,9 @@ struct MapKey {
   int64_t stride;
   int64_t rows;
   int32_t width;
+  int32_t box_rows;
   bool operator==(const MapKey& o) const {
-    return base == o.base && stride == o.stride && rows == o.rows && width == o.width;
+    return base == o.base && stride == o.stride && rows == o.rows && width == o.width && box_rows == o.box_rows;
   }
 };
 struct MapKeyHash {
@@ -1389,16 +1439,17 @@ struct MapKeyHash {
     size_t h = reinterpret_cast<size_t>(k.base);
     h ^= static_cast<size_t>(k.stride) * 0x9E3779B97F4A7C15ull;
     h ^= static_cast<size_t>(k.rows) * 0xC2B2AE3D27D4EB4Full;
-    return h ^ static_cast<size_t>(k.width);
+    return h ^ static_cast<size_t>(k.width) ^ (static_cast<size_t>(k.box_rows) << 20);
   }
 };
 
-// Row-major [rows][width] bf16 view with row stride `stride` elements; box = 64 columns x 32 rows,
-// 128-byte swizzle. Maps are cached: a decode step reuses the same 2 x layers views every token.
-int32_t GetRowMap(const void* base, int64_t stride, int64_t rows, int32_t width, CUtensorMap* out) {
+// Row-major [rows][width] bf16 view with row stride `stride` elements; box = 64 columns x box_rows rows (a tile
+// of 64 consecutive rows, or a single row for the loads that gather four rows each), 128-byte swizzle. Maps are
+// cached: a decode step reuses the same 2 x layers views every token.
+int32_t GetRowMap(const void* base, int64_t stride, int64_t rows, int32_t width, int32_t box_rows, CUtensorMap* out) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{base, stride, rows, width};
+  const MapKey key{base, stride, rows, width, box_rows};
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
@@ -1414,7 +1465,7 @@ int32_t GetRowMap(const void* base, int64_t stride, int64_t rows, int32_t width,
   }
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(stride) * 2};
-  const cuuint32_t box[2] = {64, kTile};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   CUtensorMap map;
   const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
@@ -1503,7 +1554,9 @@ size_t TcWorkspaceBytes(int32_t n_ctas) {
 }
 
 bool TcSupports(const b200kv_decode_args& a) {
-  return a.heads == kHeads && a.block_size % kTile == 0 && a.q_head_stride % 8 == 0 && a.q_seq_stride % 8 == 0 &&
+  if (a.row_index != nullptr && (a.kv_begin != nullptr || a.new_latent != nullptr || a.row_index_stride < 1)) return false;
+  return a.heads == kHeads && (a.row_index != nullptr || a.block_size % kTile == 0) && a.q_head_stride % 8 == 0 &&
+         a.q_seq_stride % 8 == 0 &&
          (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0 && a.pool.pool_rows <= INT32_MAX &&
          a.pool.latent_row_stride * 2 < (1ll << 40);
 }
@@ -1540,8 +1593,9 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
     configured_device = device;
   }
   CUtensorMap latent_map, rope_map;
-  if (int32_t rc = GetRowMap(a.pool.latent, a.pool.latent_row_stride, a.pool.pool_rows, kLatent, &latent_map)) return rc;
-  if (int32_t rc = GetRowMap(a.pool.rope, a.pool.rope_row_stride, a.pool.pool_rows, kRope, &rope_map)) return rc;
+  const int32_t box_rows = a.row_index != nullptr ? 1 : kTile;  // gathered rows come four single-row boxes at a time
+  if (int32_t rc = GetRowMap(a.pool.latent, a.pool.latent_row_stride, a.pool.pool_rows, kLatent, box_rows, &latent_map)) return rc;
+  if (int32_t rc = GetRowMap(a.pool.rope, a.pool.rope_row_stride, a.pool.pool_rows, kRope, box_rows, &rope_map)) return rc;
 
   CUtensorMap q_map;
   if (int32_t rc = GetQMap(a.q, a.q_head_stride, a.q_seq_stride, a.batch, &q_map)) return rc;
@@ -1557,6 +1611,8 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.pool_rows = a.pool.pool_rows;
   p.stable_tables = (a.flags & B200KV_DECODE_STABLE_TABLES) != 0 ? 1 : 0;
   p.force_ws = ring != nullptr ? 1 : 0;
+  p.row_index = a.row_index;
+  p.row_index_stride = a.row_index_stride;
   p.new_latent = static_cast<const char*>(a.new_latent);
   p.new_rope = static_cast<const char*>(a.new_rope);
   p.new_latent_bytes = a.new_latent_stride * 2;

@@ -162,6 +162,17 @@ typedef struct b200kv_decode_args {
    * that kernel, and only then reads Q, the new rows and the pool. Without it everything is read after the wait.
    */
   uint32_t flags;
+  /*
+   * Gathered rows (null = none): the call attends, for sequence b, over the pool rows row_index[b][0 .. kv_len[b])
+   * (device int32, row stride row_index_stride elements; what b200kv_resolve_rows writes) instead of walking
+   * block_table, which is then ignored together with block_size and max_blocks; kv_begin and the fused append
+   * must be null. An entry that is not a row of the pool is recorded as B200KV_DEV_BAD_BLOCK. The tensor-core
+   * kernel takes the rows four at a time with the gathering form of the tiled TMA load (tile::gather4), 64 rows
+   * a tile, so a top-k selection runs on the same pipeline as a dense history; the CUDA-core kernel treats the
+   * list as a table of single-row blocks.
+   */
+  const int32_t* row_index;
+  int64_t row_index_stride;
 } b200kv_decode_args;
 #define B200KV_DECODE_STABLE_TABLES 1u
 
@@ -174,8 +185,9 @@ int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* stream, b200kv_s
  * b200kv_resolve_rows turns the selection into pool rows: rows[b][j] = block_table[b][t / bs] * bs + t % bs for
  * t = token_index[b][j], j < n_selected[b] (the rest -1; a token outside the table or the pool is recorded
  * as B200KV_DEV_BAD_BLOCK). b200kv_mla_decode then attends over exactly those rows when it is given
- * block_table = rows, max_blocks = max_selected, kv_len = n_selected and block_size = 1 (a table of single-row
- * blocks); that geometry runs on the CUDA-core kernel. All arrays device int32.
+ * row_index = rows, row_index_stride = max_selected and kv_len = n_selected (tensor-core kernel for 64 heads), or,
+ * equivalently, block_table = rows, max_blocks = max_selected and block_size = 1 (a table of single-row blocks,
+ * which runs on the CUDA-core kernel). All arrays device int32.
  */
 int32_t b200kv_resolve_rows(const int32_t* block_table, int64_t max_blocks, int64_t block_size, const int32_t* token_index,
                             int64_t max_selected, const int32_t* n_selected, int64_t batch, int64_t pool_rows,

@@ -221,6 +221,66 @@ def test_attention_over_a_selected_subset_of_tokens():
     assert st2.cpu().tolist()[0] == b200kv.DEV_BAD_BLOCK
 
 
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("max_ctas", [0, 3], ids=["all-sms", "3-ctas"])
+def test_attention_over_gathered_rows(variant, max_ctas):
+    """The row list itself as the call's argument (row_index): the tensor-core kernel loads the listed rows four
+    at a time with the gathering TMA load; the CUDA-core kernel reads the list as single-row blocks. Selections of
+    512 tokens in arbitrary order out of long, fragmented histories, a short one (17 rows: one partial tile), an
+    empty one, one of exactly a tile, and one whose list is longer than the others (stride larger than any count).
+    Against the float64 statement on the same rows, and the two kernels agree on what the rows are: a repeated
+    row counts twice."""
+    from gpu_util import from_dev_bf16, status_ok, to_dev_bf16, to_dev_i32
+
+    bs, stride = 64, 520
+    kv_len = np.array([3000, 640, 4096, 17, 0, 64, 2049], dtype=np.int32)
+    n_sel = np.array([512, 512, 512, 17, 0, 64, 515], dtype=np.int32)
+    B = len(kv_len)
+    blocks = int(sum(scenarios.blocks_for(int(n), bs) for n in kv_len)) + 3
+    table = scenarios.build_tables(kv_len, bs, blocks, order=kvo.permutation(blocks))
+    pool_np = kvo.make_pool(blocks * bs)
+    q_np = kvo.make_q(B, scale=2.0 / 24.0)
+    rows = np.full((B, stride), -1, dtype=np.int32)
+    for b in range(B):
+        if n_sel[b] == 0:
+            continue
+        picks = kvo.permutation(int(kv_len[b]), seed=kvo.BASE_SEED + 31 * b)[: n_sel[b]].astype(np.int64)
+        rows[b, : n_sel[b]] = table[b, picks // bs].astype(np.int64) * bs + picks % bs
+    rows[3, 5] = rows[3, 4]  # the same row twice
+    q, pool = to_dev_bf16(q_np), to_dev_bf16(pool_np)
+    status = b200kv.new_status()
+    out = torch.full((B, 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+    lse = torch.full((B, 64), float("nan"), dtype=torch.float32, device="cuda")
+    ws = torch.empty(b200kv.decode_workspace_bytes(B, 64, max_ctas), dtype=torch.uint8, device="cuda")
+    b200kv.mla_decode(q, b200kv.pool_view(pool), None, to_dev_i32(n_sel), bs, 1.0 / 24.0, out=out, lse=lse, workspace=ws,
+                      variant=variant, max_ctas=max_ctas, status=status, row_index=to_dev_i32(rows))
+    status_ok(status)
+    ref_out, ref_lse = scenarios.ref_attention_f64(q_np, pool_np, rows, n_sel, 1, 1.0 / 24.0)
+    scenarios.check_attention(from_dev_bf16(out), lse.cpu().numpy(), ref_out, ref_lse, what="gathered rows")
+
+
+def test_gathered_rows_outside_the_pool_are_recorded_not_read():
+    from gpu_util import to_dev_bf16, to_dev_i32
+
+    pool_rows = 256
+    pool = to_dev_bf16(kvo.make_pool(pool_rows))
+    q = to_dev_bf16(kvo.make_q(2))
+    rows = np.arange(2 * 64, dtype=np.int32).reshape(2, 64)
+    rows[1, 7] = pool_rows  # one past the end
+    out = torch.zeros((2, 64, 512), dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(b200kv.decode_workspace_bytes(2, 64, 0), dtype=torch.uint8, device="cuda")
+    for variant in (b200kv.DECODE_TCGEN05, b200kv.DECODE_SIMT):
+        status = b200kv.new_status()
+        b200kv.mla_decode(q, b200kv.pool_view(pool), None, to_dev_i32(np.array([64, 64], dtype=np.int32)), 64, 1.0 / 24.0,
+                          out=out, workspace=ws, variant=variant, status=status, row_index=to_dev_i32(rows))
+        torch.cuda.synchronize()
+        assert status.cpu().tolist()[0] == b200kv.DEV_BAD_BLOCK
+    with pytest.raises(b200kv.B200KVError) as err:  # a row list and a KV range exclude each other
+        b200kv.mla_decode(q, b200kv.pool_view(pool), None, to_dev_i32(np.array([64, 64], dtype=np.int32)), 64, 1.0 / 24.0,
+                          out=out, workspace=ws, row_index=to_dev_i32(rows), kv_begin=to_dev_i32(np.zeros(2, dtype=np.int32)))
+    assert err.value.code == b200kv.ERR_INVALID
+
+
 @pytest.mark.parametrize("seed", range(4))
 def test_random_batches_and_grid_sizes_match_the_reference(seed):
     """Many small random batches (lengths around the tile and block edges, empty sequences, one long sequence)

@@ -277,8 +277,19 @@ def test_sparse_attention_pipeline_indexer_then_resolved_rows_then_decode():
         t = exp_index[b, : exp_n[b]].astype(np.int64)
         exp_rows[b, : exp_n[b]] = table[b, t // bs].astype(np.int64) * bs + t % bs
     assert np.array_equal(rows.cpu().numpy(), exp_rows)
-    out, lse = run_decode(q, pool, exp_rows, exp_n, 1, 1.0 / 24.0, b200kv.DECODE_AUTO)
     ref_out, ref_lse = scenarios.ref_attention_f64(q, pool, exp_rows, exp_n, 1, 1.0 / 24.0)
+    # the rows go from the resolver to the attention on the device: the tensor-core kernel gathers them
+    from gpu_util import from_dev_bf16, status_ok
+    status = b200kv.new_status()
+    out = torch.full((B, 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+    lse = torch.full((B, 64), float("nan"), dtype=torch.float32, device="cuda")
+    ws = torch.empty(b200kv.decode_workspace_bytes(B), dtype=torch.uint8, device="cuda")
+    b200kv.mla_decode(to_dev_bf16(q), b200kv.pool_view(to_dev_bf16(pool)), None, n_sel, bs, 1.0 / 24.0, out=out, lse=lse,
+                      workspace=ws, variant=b200kv.DECODE_TCGEN05, status=status, row_index=rows)
+    status_ok(status)
+    scenarios.check_attention(from_dev_bf16(out), lse.cpu().numpy(), ref_out, ref_lse, what="sparse pipeline, gathered")
+    # and as a table of single-row blocks on the CUDA-core kernel
+    out, lse = run_decode(q, pool, exp_rows, exp_n, 1, 1.0 / 24.0, b200kv.DECODE_AUTO)
     scenarios.check_attention(out, lse, ref_out, ref_lse, what="sparse pipeline")
 
 
