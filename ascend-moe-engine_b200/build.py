@@ -26,7 +26,7 @@ SOURCES = [
     "kv_block_pool.cpp",
     "kv_arena.cpp",
     "kv_partition.cpp",
-    "aclnn_shim.cu", "aclnn_other_ops.cu", "kv_stages.cu", "kv_peer.cu", "kv_indexer.cu",
+    "aclnn_shim.cu", "aclnn_other_ops.cu", "kv_stages.cu", "kv_peer.cu", "kv_indexer.cu", "kv_indexer_tc.cu",
     "no_alloc.cu",
     "kv_engine.cpp",
 ]

@@ -5,11 +5,12 @@
 // plans it but does not apply it (include/moe/pipeline/pipeline.hpp:57-66). The positions go to
 // b200kv_resolve_rows and from there to the decode attention over single-row blocks.
 //
-// First version, on CUDA cores: correctness and a defined result come first here. The arithmetic is fixed
+// The score kernel in this file runs on CUDA cores and is the reproducible one (the tensor-core score kernel
+// is kv_indexer_tc.cu; b200kv_indexer_topk chooses). The arithmetic is fixed
 // to the operation (one thread owns a token and runs the same fp32 fma chains as the CPU statement: over
 // d = 0..127 for each head, then over the heads), so scores are bit-identical with the oracle and the
-// selection is exact: tokens are ordered by (score descending, position ascending) with a bitonic sort of
-// 64-bit keys in shared memory, 4,096 candidates at a time merged with the best k so far.
+// selection is exact: tokens are ordered by (score descending, position ascending) as 64-bit keys; a radix
+// select finds the k-th key and a bitonic sort in shared memory orders the k that are taken.
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -21,8 +22,6 @@ constexpr int kIndexDim = 128;
 constexpr int kMaxIndexHeads = 64;
 constexpr int kScoreThreads = 128;
 constexpr int kSortThreads = 1024;
-constexpr int kSortSlots = 8192;   // keys sorted at once: 4,096 new candidates + up to 2,048 kept, padded
-constexpr int kChunk = 4096;
 constexpr int kMaxK = 2048;
 
 __device__ __forceinline__ float E4m3ToFloat(uint32_t byte) {
@@ -126,61 +125,132 @@ __device__ __forceinline__ uint64_t SortKey(float score, uint32_t position) {
 
 constexpr uint64_t kEmptyKey = ~0ull;  // sorts last
 
-// One CTA per sequence: candidates come in chunks of 4,096, the best k so far stay in the first k slots.
+// One CTA per sequence. The k best tokens are the k smallest 64-bit keys, all distinct. A radix select finds
+// the k-th smallest key: the key's bits from the top in digits of 11, 11, 10 (the score) and 11, 11, 10 (the
+// position), each pass a histogram of the digit over the tokens that match the digits found so far, a block scan
+// of the histogram, and the digit in which the wanted rank falls. The passes stop as soon as every token that
+// still matches is wanted (with distinct scores: after the three score digits). Tokens whose key is at most
+// the one found are then collected, exactly k of them, and put in order with a bitonic sort of the k keys.
+// Work is linear in the sequence's length, passes over scores that the score kernel has just left in L2.
+constexpr int kRadixBins = 2048;
+
 __global__ void __launch_bounds__(kSortThreads)
-    IndexerTopkKernel(const float* scores, int64_t score_stride, const int32_t* kv_len, int32_t k, int32_t* index,
-                      int32_t* n_selected) {
+    IndexerSelectKernel(const float* scores, int64_t score_stride, const int32_t* kv_len, int32_t k, int32_t* index,
+                        int32_t* n_selected) {
   GridDependencyTrigger();
   GridDependencyWait();
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);  // [kSortSlots]
+  __shared__ uint64_t keys[kMaxK];
+  __shared__ uint32_t hist[kRadixBins];
+  __shared__ uint32_t warp_sum[32];
+  __shared__ uint32_t chosen[3];  // digit, tokens before it, tokens in it
+  __shared__ uint32_t n_taken;
   const int b = blockIdx.x;
   const int len = kv_len[b];
-  const int tid = threadIdx.x;
-  for (int i = tid; i < kSortSlots; i += kSortThreads) keys[i] = kEmptyKey;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kept = len < k ? len : k;
+  const float* row = scores + b * score_stride;
+  if (tid == 0) {
+    n_selected[b] = kept;
+    n_taken = 0;
+  }
+  for (int i = kept + tid; i < k; i += kSortThreads) index[b * k + i] = -1;
+  if (kept == 0) return;
   __syncthreads();
-  for (int c0 = 0; c0 < len; c0 += kChunk) {
-    // slots [0, k) hold the best so far (or empties); the chunk goes to [kMaxK, kMaxK + kChunk)
-    for (int i = tid; i < kChunk; i += kSortThreads) {
-      const int t = c0 + i;
-      keys[kMaxK + i] = t < len ? SortKey(scores[b * score_stride + t], static_cast<uint32_t>(t)) : kEmptyKey;
-    }
-    for (int i = k + tid; i < kMaxK; i += kSortThreads) keys[i] = kEmptyKey;
-    for (int i = kMaxK + kChunk + tid; i < kSortSlots; i += kSortThreads) keys[i] = kEmptyKey;
-    __syncthreads();
-    // Bitonic sort, ascending, of the populated prefix rounded up to a power of two: the first chunk has no
-    // kept keys in front of it, so it is sorted on its own (in place at kMaxK, then moved to the front).
-    const bool first = c0 == 0;
-    uint64_t* base = first ? keys + kMaxK : keys;
-    const int n_sort = first ? kChunk : kSortSlots;
-    for (int size = 2; size <= n_sort; size <<= 1) {
-      for (int stride = size >> 1; stride > 0; stride >>= 1) {
-        for (int i = tid; i < n_sort / 2; i += kSortThreads) {
-          const int lo = 2 * i - (i & (stride - 1));  // index of the pair's lower element
-          const int hi = lo + stride;
-          const bool ascending = (lo & size) == 0;
-          const uint64_t a = base[lo], c = base[hi];
-          if ((a > c) == ascending) {
-            base[lo] = c;
-            base[hi] = a;
-          }
-        }
-        __syncthreads();
+
+  uint64_t bound = ~0ull;  // every token is wanted when the sequence has at most k
+  if (len > kept) {
+    uint64_t prefix = 0, mask = 0;
+    uint32_t rank = static_cast<uint32_t>(kept);  // 1-based rank, among the tokens that match `prefix`, of the key wanted
+    const int shifts[6] = {53, 42, 32, 21, 10, 0};
+    const int widths[6] = {11, 11, 10, 11, 11, 10};
+    for (int pass = 0; pass < 6; ++pass) {
+      const int shift = shifts[pass];
+      const uint32_t digit_mask = (1u << widths[pass]) - 1u;
+      for (int i = tid; i < kRadixBins; i += kSortThreads) hist[i] = 0;
+      __syncthreads();
+      for (int t = tid; t < len; t += kSortThreads) {
+        const uint64_t key = SortKey(row[t], static_cast<uint32_t>(t));
+        if ((key & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
       }
+      __syncthreads();
+      // Thread t owns bins 2t and 2t + 1; an inclusive scan over the threads gives the tokens before its bins.
+      const uint32_t c0 = hist[2 * tid], c1 = hist[2 * tid + 1];
+      uint32_t incl = c0 + c1;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += up;
+      }
+      if (lane == 31) warp_sum[warp] = incl;
+      __syncthreads();
+      if (warp == 0) {
+        uint32_t v = warp_sum[lane];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const uint32_t up = __shfl_up_sync(0xffffffffu, v, off);
+          if (lane >= off) v += up;
+        }
+        warp_sum[lane] = v;  // inclusive over the warps
+      }
+      __syncthreads();
+      const uint32_t before = (warp > 0 ? warp_sum[warp - 1] : 0u) + incl - (c0 + c1);
+      if (before < rank && rank <= before + c0 + c1) {  // one thread: the rank falls in its bins
+        const bool in_first = rank <= before + c0;
+        chosen[0] = 2 * tid + (in_first ? 0 : 1);
+        chosen[1] = in_first ? before : before + c0;
+        chosen[2] = in_first ? c0 : c1;
+      }
+      __syncthreads();
+      prefix |= static_cast<uint64_t>(chosen[0]) << shift;
+      mask |= static_cast<uint64_t>(digit_mask) << shift;
+      rank -= chosen[1];
+      if (rank == chosen[2]) {  // all that still match are wanted: the bound is the largest key with this prefix
+        bound = prefix | ~mask;
+        break;
+      }
+      bound = prefix;  // after the last pass the prefix is the key itself
     }
-    if (first) {  // the best k of the first chunk to the front (k <= kMaxK: source and destination do not overlap)
-      for (int i = tid; i < k; i += kSortThreads) keys[i] = keys[kMaxK + i];
+  }
+  // Exactly `kept` keys are at most the bound.
+  for (int t = tid; t < len; t += kSortThreads) {
+    const uint64_t key = SortKey(row[t], static_cast<uint32_t>(t));
+    if (key <= bound) {
+      const uint32_t slot = atomicAdd(&n_taken, 1u);
+      if (slot < static_cast<uint32_t>(kMaxK)) keys[slot] = key;
+    }
+  }
+  int n_sort = 2;
+  while (n_sort < kept) n_sort <<= 1;
+  __syncthreads();
+  for (int i = kept + tid; i < n_sort; i += kSortThreads) keys[i] = kEmptyKey;
+  __syncthreads();
+  for (int size = 2; size <= n_sort; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = tid; i < n_sort / 2; i += kSortThreads) {
+        const int lo = 2 * i - (i & (stride - 1));  // index of the pair's lower element
+        const int hi = lo + stride;
+        const bool ascending = (lo & size) == 0;
+        const uint64_t a = keys[lo], c = keys[hi];
+        if ((a > c) == ascending) {
+          keys[lo] = c;
+          keys[hi] = a;
+        }
+      }
       __syncthreads();
     }
   }
-  const int kept = len < k ? len : k;
-  for (int i = tid; i < k; i += kSortThreads) {
-    index[b * k + i] = i < kept ? static_cast<int32_t>(keys[i] & 0xffffffffu) : -1;
-  }
-  if (tid == 0) n_selected[b] = kept;
+  for (int i = tid; i < kept; i += kSortThreads) index[b * k + i] = static_cast<int32_t>(keys[i] & 0xffffffffu);
 }
 
 }  // namespace
+}  // namespace b200kv
+
+namespace b200kv {
+bool IndexerTcSupports(int32_t heads, int32_t block_size, int64_t key_stride, int64_t pool_rows);
+int32_t LaunchIndexerScoreTc(const void* q, const float* q_scale, const void* weights, int32_t heads, const void* key_pool,
+                             int64_t key_stride, const float* k_scale, int64_t pool_rows, const int32_t* block_table,
+                             int64_t max_blocks, const int32_t* kv_len, int32_t batch, int32_t block_size, int64_t max_kv_len,
+                             float* scores, int64_t score_stride, cudaStream_t stream, int32_t* status);
 }  // namespace b200kv
 
 using namespace b200kv;
@@ -216,17 +286,14 @@ extern "C" int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* st
                  b200kv_indexer_workspace_bytes(a.batch, a.max_kv_len));
     return B200KV_ERR_INVALID;
   }
-  static thread_local int configured_device = -1;
-  int device = 0;
-  if (int32_t rc = CheckCuda(cudaGetDevice(&device), "cudaGetDevice")) return rc;
-  if (device != configured_device) {
-    if (int32_t rc = CheckCuda(cudaFuncSetAttribute(IndexerTopkKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    kSortSlots * 8),
-                               "indexer top-k smem opt-in")) {
-      return rc;
-    }
-    configured_device = device;
+  const bool tc_ok = IndexerTcSupports(a.heads, a.block_size, a.key_stride, a.pool_rows);
+  if ((a.variant != B200KV_INDEXER_AUTO && a.variant != B200KV_INDEXER_EXACT && a.variant != B200KV_INDEXER_TCGEN05) ||
+      (a.variant == B200KV_INDEXER_TCGEN05 && !tc_ok)) {
+    SetLastError("indexer_topk refused: variant %d (the tensor-core score kernel needs heads <= 64 and block_size %% 64 == 0; "
+                 "heads %d, block_size %d)", a.variant, a.heads, a.block_size);
+    return B200KV_ERR_INVALID;
   }
+  const bool use_tc = tc_ok && a.variant != B200KV_INDEXER_EXACT;
   ScoreParams p{};
   p.q = static_cast<const uint8_t*>(a.q);
   p.q_scale = a.q_scale;
@@ -244,12 +311,20 @@ extern "C" int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* st
   p.score_stride = (a.max_kv_len + 3) & ~3ll;
   p.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 grid(static_cast<unsigned>((a.max_kv_len + kScoreThreads - 1) / kScoreThreads), static_cast<unsigned>(a.batch));
-  if (int32_t rc = CheckCuda(LaunchOverlapped(IndexerScoreKernel, grid, dim3(kScoreThreads), 0, s, p), "indexer score launch")) {
-    return rc;
+  if (use_tc) {
+    if (int32_t rc = LaunchIndexerScoreTc(a.q, a.q_scale, a.weights, a.heads, a.key_pool, a.key_stride, a.k_scale, a.pool_rows,
+                                          a.block_table, a.max_blocks, a.kv_len, a.batch, a.block_size, a.max_kv_len, p.scores,
+                                          p.score_stride, s, status)) {
+      return rc;
+    }
+  } else {
+    const dim3 grid(static_cast<unsigned>((a.max_kv_len + kScoreThreads - 1) / kScoreThreads), static_cast<unsigned>(a.batch));
+    if (int32_t rc = CheckCuda(LaunchOverlapped(IndexerScoreKernel, grid, dim3(kScoreThreads), 0, s, p), "indexer score launch")) {
+      return rc;
+    }
   }
-  return CheckCuda(LaunchOverlapped(IndexerTopkKernel, dim3(static_cast<unsigned>(a.batch)), dim3(kSortThreads),
-                                    static_cast<size_t>(kSortSlots) * 8, s, static_cast<const float*>(p.scores), p.score_stride,
-                                    a.kv_len, a.k, a.index_out, a.n_selected_out),
+  return CheckCuda(LaunchOverlapped(IndexerSelectKernel, dim3(static_cast<unsigned>(a.batch)), dim3(kSortThreads), 0, s,
+                                    static_cast<const float*>(p.scores), p.score_stride, a.kv_len, a.k, a.index_out,
+                                    a.n_selected_out),
                    "indexer top-k launch");
 }

@@ -1549,6 +1549,29 @@ int32_t GetQMap(const void* base, int64_t head_stride, int64_t seq_stride, int32
 
 }  // namespace
 
+// Row-major [rows][128] one-byte view (FP8 vectors of 128) with a row stride of `stride_bytes`; box = the whole
+// 128-byte row x box_rows rows, 128-byte swizzle. For the indexer's tensor-core kernel; encoded per call.
+int32_t EncodeByteRowMap(const void* base, int64_t stride_bytes, int64_t rows, int32_t box_rows, CUtensorMap* out) {
+  EncodeTiledFn encode = ResolveEncodeTiled();
+  if (encode == nullptr) {
+    SetLastError("cuTensorMapEncodeTiled could not be resolved from the CUDA driver");
+    return B200KV_ERR_RUNTIME;
+  }
+  const cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(stride_bytes)};
+  const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    SetLastError("cuTensorMapEncodeTiled (byte rows) failed with CUresult %d (base %p, stride %lld, rows %lld)",
+                 static_cast<int>(rc), base, static_cast<long long>(stride_bytes), static_cast<long long>(rows));
+    return B200KV_ERR_RUNTIME;
+  }
+  return B200KV_OK;
+}
+
 size_t TcWorkspaceBytes(int32_t n_ctas) {
   return static_cast<size_t>(n_ctas) * 2 * kHeads * (kLatent + 2) * sizeof(float);
 }

@@ -200,12 +200,15 @@ int32_t b200kv_resolve_rows(const int32_t* block_table, int64_t max_blocks, int6
  * token of the step, every token t < kv_len[b] of the paged index-key cache scores
  *   score_t = sum_h w[b][h] * ReLU(q_scale[b][h] * k_scale[row_t] * (Q[b][h] . K[row_t])),
  * Q and K FP8 E4M3 vectors of 128, and index_out[b][0..k) receives the positions of the k best tokens, best
- * first (ties: lower position first; -1 beyond n_selected_out[b] = min(k, kv_len[b])). The arithmetic is fixed
- * to the operation (csrc/kv_indexer.cu states it), so the selection is reproducible bit for bit.
+ * first (ties: lower position first; -1 beyond n_selected_out[b] = min(k, kv_len[b])). Two score kernels. The
+ * exact one runs fixed fp32 fma chains on CUDA cores (csrc/kv_indexer.cu states them), so its selection is
+ * reproducible bit for bit. The tensor-core one (csrc/kv_indexer_tc.cu: tcgen05 FP8 MMA, 128 tokens x 64 heads
+ * a tile, keys through TMA) rounds the 128-term dot products differently: its scores agree to rounding error and
+ * its selection can differ from the exact one between tokens whose scores are that close.
  * q fp8 [batch][heads][128] (heads <= 64); q_scale fp32 and weights bf16 [batch][heads]; key_pool fp8
  * [pool_rows][key_stride] (16-byte aligned, stride a multiple of 16) with k_scale fp32 [pool_rows], addressed
  * through block_table / block_size like the KV pool; k <= 2048; workspace of
- * b200kv_indexer_workspace_bytes(batch, max_kv_len) bytes holds the scores. First version, on CUDA cores.
+ * b200kv_indexer_workspace_bytes(batch, max_kv_len) bytes holds the scores.
  */
 typedef struct b200kv_indexer_args {
   const void* q;
@@ -227,7 +230,11 @@ typedef struct b200kv_indexer_args {
   int32_t* n_selected_out; /* device int32 [batch] */
   void* workspace;
   size_t workspace_bytes;
+  int32_t variant; /* B200KV_INDEXER_AUTO, _EXACT or _TCGEN05 */
 } b200kv_indexer_args;
+#define B200KV_INDEXER_AUTO 0    /* tensor cores where the geometry allows, else CUDA cores            */
+#define B200KV_INDEXER_EXACT 1   /* CUDA cores: the fixed fp32 chains, reproducible bit for bit         */
+#define B200KV_INDEXER_TCGEN05 2 /* tensor cores: heads <= 64, block_size % 64 == 0; refused otherwise */
 
 size_t b200kv_indexer_workspace_bytes(int32_t batch, int64_t max_kv_len);
 int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* stream, b200kv_status_word* status);

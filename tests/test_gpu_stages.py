@@ -248,16 +248,88 @@ def test_indexer_selection_matches_oracle_bit_for_bit(lens, k):
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     st = b200kv.new_status()
     index, n_sel = b200kv.indexer_topk(d(q), d(qs), to_dev_bf16(w), d(key), d(ks), to_dev_i32(table), to_dev_i32(kv_len),
-                                       bs, int(max(lens)), k, status=st)
+                                       bs, int(max(lens)), k, status=st, variant=b200kv.INDEXER_EXACT)
     torch.cuda.synchronize()
     assert st.cpu().tolist()[0] == 0
     assert np.array_equal(n_sel.cpu().numpy(), exp_n)
     assert np.array_equal(index.cpu().numpy(), exp_index), "selection differs from the oracle"
 
 
+def _check_selection_up_to_rounding(index, n_sel, got_scores, exp_scores, exp_n, kv_len, k, eps_rel):
+    """The tensor-core scores differ from the oracle's by rounding, so its selection is checked as a selection:
+    per sequence the count, positions distinct and inside the sequence, the device's own scores in best-first
+    order with ties by position, every score within eps of the oracle's (both when the scores are at hand),
+    nothing better than the k-th oracle score (by more than eps) left out and nothing worse (by more than eps)
+    taken."""
+    assert np.array_equal(n_sel, exp_n)
+    for b in range(len(kv_len)):
+        n, m = int(kv_len[b]), int(n_sel[b])
+        assert (index[b, m:] == -1).all()
+        if n == 0:
+            continue
+        want = exp_scores[b, :n].astype(np.float64)
+        eps = eps_rel * max(np.abs(want).max(), 1e-30)
+        picked = index[b, :m].astype(np.int64)
+        assert len(set(picked.tolist())) == m and picked.min() >= 0 and picked.max() < n
+        if got_scores is not None:
+            got = got_scores[b, :n].astype(np.float64)
+            assert np.abs(want - got).max() <= eps, (b, np.abs(want - got).max(), eps)
+            mine = got[picked]
+            assert (np.diff(mine) <= 0).all(), "not best first by the kernel's own scores"
+            same = np.diff(mine) == 0
+            assert (np.diff(picked)[same] > 0).all(), "ties not by position"
+        assert (np.diff(want[picked]) <= 2 * eps).all(), "not best first by the oracle's scores, up to rounding"
+        if m < n:
+            kth = np.sort(want)[::-1][m - 1]
+            assert want[picked].min() >= kth - 2 * eps
+            rest = np.setdiff1d(np.arange(n), picked)
+            assert want[rest].max() <= kth + 2 * eps
+
+
+@pytest.mark.parametrize("lens,heads,k", [([4096, 300, 5000, 17, 0, 9000], 64, 512), ([70, 64], 64, 2048), ([12000], 64, 100),
+                                          ([1000, 129, 128, 1, 127], 16, 64), ([4097] * 8, 64, 512)])
+def test_indexer_tensor_core_scores_and_selection(lens, heads, k):
+    """The FP8 tcgen05 score kernel: scores within 1e-6 of the sequence's largest score of the oracle's fp32 chains
+    (the tensor core sums the 128 exact products of a dot product in another order), and the selection made from
+    them correct up to that. Fewer heads than the tile's 64, lengths around the tile (128) and block (64) edges, an
+    empty sequence, fragmented tables."""
+    B, bs = len(lens), 64
+    q, qs, w, key, ks, table, kv_len = _indexer_inputs(B, heads, lens, bs, seed=101 + k)
+    exp_scores, exp_index, exp_n = kvo.indexer_topk(q, qs, w, key, ks, table, kv_len, bs, k)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    st = b200kv.new_status()
+    got = []
+    index, n_sel = b200kv.indexer_topk(d(q), d(qs), to_dev_bf16(w), d(key), d(ks), to_dev_i32(table), to_dev_i32(kv_len),
+                                       bs, int(max(lens)), k, status=st, variant=b200kv.INDEXER_TCGEN05, scores_out=got)
+    torch.cuda.synchronize()
+    assert st.cpu().tolist()[0] == 0
+    _check_selection_up_to_rounding(index.cpu().numpy(), n_sel.cpu().numpy(), got[0].cpu().numpy(), exp_scores, exp_n,
+                                    kv_len, k, eps_rel=1e-6)
+
+
+def test_indexer_tensor_core_variant_is_refused_where_it_cannot_run_and_reports_bad_blocks():
+    B, heads, bs, k = 2, 64, 64, 16
+    q, qs, w, key, ks, table, kv_len = _indexer_inputs(B, heads, [200, 64], bs, seed=5)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    with pytest.raises(b200kv.B200KVError) as err:  # blocks of 16 tokens: a 64-row key load would leave its block
+        b200kv.indexer_topk(d(q), d(qs), to_dev_bf16(w), d(key), d(ks), to_dev_i32(table), to_dev_i32(kv_len), 16, 200, k,
+                            variant=b200kv.INDEXER_TCGEN05)
+    assert err.value.code == b200kv.ERR_INVALID
+    bad = table.copy()
+    bad[0, 1] = key.shape[0] // bs  # one block past the pool
+    st = b200kv.new_status()
+    got = []
+    b200kv.indexer_topk(d(q), d(qs), to_dev_bf16(w), d(key), d(ks), to_dev_i32(bad), to_dev_i32(kv_len), bs, 200, k,
+                        status=st, variant=b200kv.INDEXER_TCGEN05, scores_out=got)
+    torch.cuda.synchronize()
+    assert st.cpu().tolist()[0] == b200kv.DEV_BAD_BLOCK
+    assert np.isneginf(got[0].cpu().numpy()[0, 64:128]).all()  # the tokens of the missing block do not count
+
+
 def test_sparse_attention_pipeline_indexer_then_resolved_rows_then_decode():
     """The whole sparse path on the device: top-k positions from the indexer, their pool rows, attention over
-    exactly those rows; against the float64 reference over the oracle's selection."""
+    exactly those rows. The selection (tensor-core scores) against the oracle's up to rounding, the attention
+    against the float64 reference over the selected rows."""
     import scenarios
     from gpu_util import run_decode
 
@@ -271,10 +343,12 @@ def test_sparse_attention_pipeline_indexer_then_resolved_rows_then_decode():
                                        bs, max(lens), k)
     rows = b200kv.resolve_rows(to_dev_i32(table), bs, index, n_sel, pool.shape[0])
     torch.cuda.synchronize()
-    _, exp_index, exp_n = kvo.indexer_topk(q8, qs, w, key, ks, table, kv_len, bs, k)
-    exp_rows = np.full((B, k), -1, dtype=np.int32)
+    exp_scores, _, exp_n = kvo.indexer_topk(q8, qs, w, key, ks, table, kv_len, bs, k)
+    got_index = index.cpu().numpy()
+    _check_selection_up_to_rounding(got_index, n_sel.cpu().numpy(), None, exp_scores, exp_n, kv_len, k, eps_rel=1e-6)
+    exp_rows = np.full((B, k), -1, dtype=np.int32)  # the rows of the device's selection
     for b in range(B):
-        t = exp_index[b, : exp_n[b]].astype(np.int64)
+        t = got_index[b, : exp_n[b]].astype(np.int64)
         exp_rows[b, : exp_n[b]] = table[b, t // bs].astype(np.int64) * bs + t % bs
     assert np.array_equal(rows.cpu().numpy(), exp_rows)
     ref_out, ref_lse = scenarios.ref_attention_f64(q, pool, exp_rows, exp_n, 1, 1.0 / 24.0)
@@ -334,5 +408,7 @@ def test_indexer_operator_through_the_operator_abi():
     ws = torch.empty(ws_bytes.value, dtype=torch.uint8, device="cuda")
     assert L.aclnnQuantLightningIndexer(ws.data_ptr(), ws_bytes.value, exe, None) == 0
     torch.cuda.synchronize()
-    _, exp_index, _ = kvo.indexer_topk(q, qs, w, key, ks, table, kv_len, bs, k)
-    assert np.array_equal(out.cpu().numpy()[:, 0, :], exp_index)
+    exp_scores, _, exp_n = kvo.indexer_topk(q, qs, w, key, ks, table, kv_len, bs, k)
+    got = out.cpu().numpy()[:, 0, :]
+    _check_selection_up_to_rounding(got, (got >= 0).sum(axis=1).astype(np.int32), None, exp_scores, exp_n, kv_len, k,
+                                    eps_rel=1e-6)
