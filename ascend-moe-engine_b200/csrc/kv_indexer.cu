@@ -123,58 +123,77 @@ __device__ __forceinline__ uint64_t SortKey(float score, uint32_t position) {
   return (static_cast<uint64_t>(~bits) << 32) | position;
 }
 
-constexpr uint64_t kEmptyKey = ~0ull;  // sorts last
-
 // One CTA per sequence. The k best tokens are the k smallest 64-bit keys, all distinct. A radix select finds
 // the k-th smallest key: the key's bits from the top in digits of 11, 11, 10 (the score) and 11, 11, 10 (the
 // position), each pass a histogram of the digit over the tokens that match the digits found so far, a block scan
 // of the histogram, and the digit in which the wanted rank falls. The passes stop as soon as every token that
 // still matches is wanted (with distinct scores: after the three score digits). Tokens whose key is at most
-// the one found are then collected, exactly k of them, and put in order with a bitonic sort of the k keys.
-// Work is linear in the sequence's length, passes over scores that the score kernel has just left in L2.
+// the one found are then collected, exactly k of them, and sorted (bitonic, the short-range steps on registers).
+// A thread keeps the score images of its first eight tokens
+// in registers, so sequences of up to 8,192 tokens are read from memory once; work is linear in the length.
 constexpr int kRadixBins = 2048;
+constexpr int kHeldPerThread = 8;
 
 __global__ void __launch_bounds__(kSortThreads)
     IndexerSelectKernel(const float* scores, int64_t score_stride, const int32_t* kv_len, int32_t k, int32_t* index,
                         int32_t* n_selected) {
   GridDependencyTrigger();
-  GridDependencyWait();
   __shared__ uint64_t keys[kMaxK];
   __shared__ uint32_t hist[kRadixBins];
   __shared__ uint32_t warp_sum[32];
-  __shared__ uint32_t chosen[3];  // digit, tokens before it, tokens in it
+  __shared__ uint32_t chosen[2][3];  // per pass parity: digit, tokens before it, tokens in it
   __shared__ uint32_t n_taken;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < kRadixBins; i += kSortThreads) hist[i] = 0;
+  if (tid == 0) n_taken = 0;
+  GridDependencyWait();
   const int b = blockIdx.x;
   const int len = kv_len[b];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kept = len < k ? len : k;
   const float* row = scores + b * score_stride;
-  if (tid == 0) {
-    n_selected[b] = kept;
-    n_taken = 0;
-  }
+  if (tid == 0) n_selected[b] = kept;
   for (int i = kept + tid; i < k; i += kSortThreads) index[b * k + i] = -1;
   if (kept == 0) return;
-  __syncthreads();
+  // High word of the key (ascending = better) of this thread's tokens tid, tid + 1024, ...: the first eight held.
+  uint32_t held[kHeldPerThread];
+#pragma unroll
+  for (int j = 0; j < kHeldPerThread; ++j) {
+    const int t = tid + j * kSortThreads;
+    held[j] = t < len ? static_cast<uint32_t>(SortKey(row[t], 0u) >> 32) : 0u;
+  }
+  auto key_of = [&](int j, int t) -> uint64_t {  // j = t / 1024 (compile-time inside unrolled loops)
+    return (static_cast<uint64_t>(held[j]) << 32) | static_cast<uint32_t>(t);
+  };
+  __syncthreads();  // the histogram is clear
 
   uint64_t bound = ~0ull;  // every token is wanted when the sequence has at most k
   if (len > kept) {
     uint64_t prefix = 0, mask = 0;
     uint32_t rank = static_cast<uint32_t>(kept);  // 1-based rank, among the tokens that match `prefix`, of the key wanted
-    const int shifts[6] = {53, 42, 32, 21, 10, 0};
-    const int widths[6] = {11, 11, 10, 11, 11, 10};
     for (int pass = 0; pass < 6; ++pass) {
-      const int shift = shifts[pass];
-      const uint32_t digit_mask = (1u << widths[pass]) - 1u;
-      for (int i = tid; i < kRadixBins; i += kSortThreads) hist[i] = 0;
-      __syncthreads();
-      for (int t = tid; t < len; t += kSortThreads) {
+      const int shift = pass == 0 ? 53 : pass == 1 ? 42 : pass == 2 ? 32 : pass == 3 ? 21 : pass == 4 ? 10 : 0;
+      const uint32_t digit_mask = (pass == 2 || pass == 5) ? 1023u : 2047u;
+      // (Scores of one sequence are close together, so in the top digits most tokens fall into a few bins;
+      // shared-memory atomics on one address still cost less here than finding a warp's equal digits first with
+      // match.any, which was measured: 2.5 us more per launch.)
+#pragma unroll
+      for (int j = 0; j < kHeldPerThread; ++j) {
+        const int t = tid + j * kSortThreads;
+        if (t < len) {
+          const uint64_t key = key_of(j, t);
+          if ((key & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
+        }
+      }
+      for (int t = tid + kHeldPerThread * kSortThreads; t < len; t += kSortThreads) {
         const uint64_t key = SortKey(row[t], static_cast<uint32_t>(t));
         if ((key & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
       }
       __syncthreads();
-      // Thread t owns bins 2t and 2t + 1; an inclusive scan over the threads gives the tokens before its bins.
+      // Thread t owns bins 2t and 2t + 1 (and clears them for the next pass); a scan over the threads gives the
+      // tokens before its bins: shuffles inside the warp, and every warp adds up the warps before it for itself.
       const uint32_t c0 = hist[2 * tid], c1 = hist[2 * tid + 1];
+      hist[2 * tid] = 0;
+      hist[2 * tid + 1] = 0;
       uint32_t incl = c0 + c1;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -183,50 +202,62 @@ __global__ void __launch_bounds__(kSortThreads)
       }
       if (lane == 31) warp_sum[warp] = incl;
       __syncthreads();
-      if (warp == 0) {
-        uint32_t v = warp_sum[lane];
+      uint32_t earlier = lane < warp ? warp_sum[lane] : 0u;
 #pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-          const uint32_t up = __shfl_up_sync(0xffffffffu, v, off);
-          if (lane >= off) v += up;
-        }
-        warp_sum[lane] = v;  // inclusive over the warps
-      }
-      __syncthreads();
-      const uint32_t before = (warp > 0 ? warp_sum[warp - 1] : 0u) + incl - (c0 + c1);
+      for (int off = 16; off > 0; off >>= 1) earlier += __shfl_xor_sync(0xffffffffu, earlier, off);
+      const uint32_t before = earlier + incl - (c0 + c1);
       if (before < rank && rank <= before + c0 + c1) {  // one thread: the rank falls in its bins
         const bool in_first = rank <= before + c0;
-        chosen[0] = 2 * tid + (in_first ? 0 : 1);
-        chosen[1] = in_first ? before : before + c0;
-        chosen[2] = in_first ? c0 : c1;
+        chosen[pass & 1][0] = 2 * tid + (in_first ? 0 : 1);
+        chosen[pass & 1][1] = in_first ? before : before + c0;
+        chosen[pass & 1][2] = in_first ? c0 : c1;
       }
       __syncthreads();
-      prefix |= static_cast<uint64_t>(chosen[0]) << shift;
+      prefix |= static_cast<uint64_t>(chosen[pass & 1][0]) << shift;
       mask |= static_cast<uint64_t>(digit_mask) << shift;
-      rank -= chosen[1];
-      if (rank == chosen[2]) {  // all that still match are wanted: the bound is the largest key with this prefix
+      rank -= chosen[pass & 1][1];
+      bound = prefix;  // after the last pass the prefix is the key itself
+      if (rank == chosen[pass & 1][2]) {  // all that still match are wanted: the bound is the largest key with this prefix
         bound = prefix | ~mask;
         break;
       }
-      bound = prefix;  // after the last pass the prefix is the key itself
     }
   }
-  // Exactly `kept` keys are at most the bound.
-  for (int t = tid; t < len; t += kSortThreads) {
-    const uint64_t key = SortKey(row[t], static_cast<uint32_t>(t));
-    if (key <= bound) {
-      const uint32_t slot = atomicAdd(&n_taken, 1u);
-      if (slot < static_cast<uint32_t>(kMaxK)) keys[slot] = key;
-    }
+  // Exactly `kept` keys are at most the bound. A warp reserves the slots of its takers with one addition.
+  auto take = [&](bool wanted, uint64_t key) {  // every lane of the warp calls
+    const unsigned takers = __ballot_sync(0xffffffffu, wanted);
+    if (takers == 0u) return;
+    uint32_t first = 0;
+    if (lane == __ffs(takers) - 1) first = atomicAdd(&n_taken, static_cast<uint32_t>(__popc(takers)));
+    first = __shfl_sync(0xffffffffu, first, __ffs(takers) - 1);
+    const uint32_t slot = first + __popc(takers & ((1u << lane) - 1u));
+    if (wanted && slot < static_cast<uint32_t>(kMaxK)) keys[slot] = key;
+  };
+#pragma unroll
+  for (int j = 0; j < kHeldPerThread; ++j) {
+    const int t = tid + j * kSortThreads;
+    if (warp * 32 + j * kSortThreads >= len) break;
+    const uint64_t key = key_of(j, t);
+    take(t < len && key <= bound, key);
   }
-  int n_sort = 2;
-  while (n_sort < kept) n_sort <<= 1;
+  for (int t0 = warp * 32 + kHeldPerThread * kSortThreads; t0 < len; t0 += kSortThreads) {
+    const int t = t0 + lane;
+    const uint64_t key = t < len ? SortKey(row[t], static_cast<uint32_t>(t)) : ~0ull;
+    take(t < len && key <= bound, key);
+  }
   __syncthreads();
-  for (int i = kept + tid; i < n_sort; i += kSortThreads) keys[i] = kEmptyKey;
+  // The collected keys in order: a bitonic sort, ascending, of the list padded to a power of two. Element e
+  // belongs to thread e % 1024 (two elements a thread when k > 1024). Steps whose partner is less than 32 away
+  // stay inside a warp and run on registers with shuffles, a whole run of them between two barriers; only the
+  // steps with a partner 32 or more away (10 of the 45 for 512 keys) go through shared memory.
+  int padded = 32;
+  while (padded < kept) padded <<= 1;
+  for (int i = kept + tid; i < padded; i += kSortThreads) keys[i] = ~0ull;
   __syncthreads();
-  for (int size = 2; size <= n_sort; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < n_sort / 2; i += kSortThreads) {
+  for (int size = 2; size <= padded; size <<= 1) {
+    int stride = size >> 1;
+    for (; stride >= 32; stride >>= 1) {
+      for (int i = tid; i < padded / 2; i += kSortThreads) {
         const int lo = 2 * i - (i & (stride - 1));  // index of the pair's lower element
         const int hi = lo + stride;
         const bool ascending = (lo & size) == 0;
@@ -238,6 +269,18 @@ __global__ void __launch_bounds__(kSortThreads)
       }
       __syncthreads();
     }
+    for (int e = tid; e < padded; e += kSortThreads) {  // the same trip count for every lane of a warp
+      uint64_t mine = keys[e];
+      const bool ascending = (e & size) == 0;
+      for (int s2 = stride; s2 > 0; s2 >>= 1) {
+        const uint64_t other = __shfl_xor_sync(0xffffffffu, mine, s2);
+        const bool lower = (e & s2) == 0;  // this element is the pair's lower one
+        const bool take_other = lower ? ((mine > other) == ascending) : ((other > mine) == ascending);
+        if (take_other) mine = other;
+      }
+      keys[e] = mine;
+    }
+    __syncthreads();
   }
   for (int i = tid; i < kept; i += kSortThreads) index[b * k + i] = static_cast<int32_t>(keys[i] & 0xffffffffu);
 }

@@ -10,11 +10,14 @@
 // chain over the heads as the CUDA-core kernel: scale, ReLU, weight, sum. Per token the kernel moves 128 bytes
 // of key, 4 of key scale and 4 of score: it is bound by HBM, and the tensor cores make the arithmetic free.
 //
-// Persistent CTAs (one per SM) each take an equal run of the flat list of token tiles. Six warps: 0-3 epilogue
-// (warp w reads TMEM lanes 32 w ..), 4 TMA producer, 5 TMEM allocation and MMA issue. Four stages of
-// {keys 16 KB, Q 8 KB}; Q comes with every tile (it is 8 KB per sequence and lives in L2), which spares the
-// pipeline a special case where a CTA's run crosses into the next sequence. Two accumulators in TMEM, so the
-// epilogue of one tile runs under the loads and MMAs of the next.
+// Persistent CTAs (one per SM) each take an equal run of the flat list of token tiles. Ten warps: two epilogue
+// groups of four (warps 0-3 take the CTA's even tiles and accumulator 0, warps 4-7 the odd ones and accumulator
+// 1; warp w reads TMEM lanes 32 (w % 4) ..), warp 8 the TMA producer, warp 9 TMEM allocation and MMA issue. Four
+// stages of {keys 16 KB, Q 8 KB}; Q comes with every tile (it is 8 KB per sequence and lives in L2), which
+// spares the pipeline a special case where a CTA's run crosses into the next sequence. The epilogue is the
+// longest stage of a tile (some 1,300 cycles of dependent fp32 work per thread against 700 for a tile's loads), so
+// two groups alternate; what a role needs from memory for a tile (block-table entries, scales) it fetches one
+// tile ahead.
 //
 // The tensor core's sum of 128 exact FP8 products is rounded differently from a chain of fp32 fmas, so scores
 // agree with the CUDA-core kernel to a few units in the last place of the largest partial sum, not bit for
@@ -38,8 +41,9 @@ constexpr int kStages = 4;
 constexpr int kKeyBytes = kTokens * kDim;       // 16 KB
 constexpr int kQBytes = kHeadsPadded * kDim;    // 8 KB
 constexpr int kStageBytes = kKeyBytes + kQBytes;
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kThreads = 320;
+constexpr int kEpilogueThreads = 128;  // per group
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr int kTmemCols = 128;     // two accumulators of 64 columns
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 2048 /* barriers, scalars, coefficients */;
 
@@ -67,8 +71,8 @@ struct Shared {  // at most 2048 bytes
   uint32_t tmem_base;
   int32_t abort_flag;
   int32_t start_seq, start_tile, n_tiles;
-  float qs[2][kHeadsPadded];
-  float w[2][kHeadsPadded];
+  alignas(16) float qs[2][kHeadsPadded];
+  alignas(16) float w[2][kHeadsPadded];
 };
 
 static_assert(sizeof(Shared) <= 2048, "the tail of the shared-memory budget");
@@ -149,7 +153,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto bar = [&](const uint64_t* b) { return ptx::SmemAddr(b); };
 
   GridDependencyTrigger();
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       for (int s = 0; s < kStages; ++s) {
         ptx::MbarInit(bar(&sh->full[s]), 1);
@@ -166,27 +170,39 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncwarp();
     GridDependencyWait();
-    // This CTA's run [lo, hi) of the flat tile list: totals, then the sequence and tile at which lo falls.
+    // This CTA's run [lo, hi) of the flat tile list: totals, then the sequence and tile at which lo falls (a scan
+    // over the sequences, 32 at a time).
     long long total = 0;
     for (int i = lane; i < p.batch; i += 32) total += TilesOf(p.kv_len[i]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
     const long long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
-    if (lane == 0) {
-      long long before = 0;
-      int seq = 0;
-      for (; seq < p.batch; ++seq) {
-        const long long t = TilesOf(p.kv_len[seq]);
-        if (before + t > lo) break;
-        before += t;
+    long long before = 0, found_before = 0;
+    int found_seq = p.batch;
+    for (int c = 0; c < p.batch && found_seq == p.batch; c += 32) {
+      const int t = c + lane < p.batch ? TilesOf(p.kv_len[c + lane]) : 0;
+      int incl = t;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += up;
       }
-      sh->start_seq = seq;
-      sh->start_tile = static_cast<int32_t>(lo - before);
+      const unsigned hit = __ballot_sync(0xffffffffu, before + incl > lo);
+      if (hit != 0u) {
+        const int src = __ffs(hit) - 1;
+        found_seq = c + src;
+        found_before = before + __shfl_sync(0xffffffffu, incl - t, src);
+      }
+      before += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      sh->start_seq = found_seq;
+      sh->start_tile = static_cast<int32_t>(lo - found_before);
       sh->n_tiles = static_cast<int32_t>(hi - lo);
     }
     __syncwarp();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     ptx::TmemAlloc(ptx::SmemAddr(&sh->tmem_base), kTmemCols);
     ptx::TmemRelinquish();
   }
@@ -197,34 +213,47 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem = sh->tmem_base;
   const int start_seq = sh->start_seq, start_tile = sh->start_tile, n_tiles = sh->n_tiles;
 
-  if (warp == 4) {
-    // ---- producer: lane 0 brings Q, lanes 1 and 2 a half tile of keys each ----
+  if (warp == kProducerWarp) {
+    // ---- producer: lane 0 brings Q, lanes 1 and 2 a half tile of keys each (its pool row looked up a tile ahead) ----
     TileWalker walk(p.kv_len, p.batch, start_seq, start_tile, n_tiles);
-    int seq, tile, len;
+    struct Ahead {
+      int seq, tile, len;
+      int64_t row;
+    };
+    auto look = [&](Ahead* a) -> bool {
+      if (!walk.Next(&a->seq, &a->tile, &a->len)) return false;
+      a->row = 0;  // a half beyond the sequence's end still fills its stage: row 0, masked by the epilogue
+      if (lane == 1 || lane == 2) {
+        const int tok = a->tile * kTokens + (lane - 1) * kHalf;
+        if (tok < a->len) {
+          const int64_t column = tok / p.block_size;
+          const int64_t block = column < p.max_blocks ? p.block_table[static_cast<int64_t>(a->seq) * p.max_blocks + column] : -1;
+          a->row = block * p.block_size + tok % p.block_size;
+          if (block < 0 || a->row + kHalf > p.pool_rows) {
+            RecordError(p.status, B200KV_DEV_BAD_BLOCK, a->seq, static_cast<int32_t>(column), static_cast<int32_t>(block));
+            a->row = 0;
+          }
+        }
+      }
+      return true;
+    };
+    Ahead cur, next;
+    bool have = look(&next);
     bool ok = true;
     int issued = 0;
-    for (int i = 0; ok && walk.Next(&seq, &tile, &len); ++i) {
+    for (int i = 0; ok && have; ++i) {
       const int stage = i % kStages;
+      cur = next;
+      have = look(&next);
       if (i >= kStages) ok = __all_sync(0xffffffffu, Wait(bar(&sh->empty[stage]), ((i / kStages) & 1) ^ 1, sh, p.status, 0));
       if (!ok) break;
       const uint32_t dst = stage0 + stage * kStageBytes;
       const uint32_t full = bar(&sh->full[stage]);
       if (lane == 0) {
         ptx::MbarArriveExpectTx(full, kStageBytes);
-        ptx::TmaLoad2D(dst + kKeyBytes, &q_map, 0, seq * p.heads, full);
+        ptx::TmaLoad2D(dst + kKeyBytes, &q_map, 0, cur.seq * p.heads, full);
       } else if (lane < 3) {
-        const int tok = tile * kTokens + (lane - 1) * kHalf;
-        int64_t row = 0;  // a half beyond the sequence's end still fills its stage: row 0, masked by the epilogue
-        if (tok < len) {
-          const int64_t column = tok / p.block_size;
-          const int64_t block = column < p.max_blocks ? p.block_table[static_cast<int64_t>(seq) * p.max_blocks + column] : -1;
-          row = block * p.block_size + tok % p.block_size;
-          if (block < 0 || row + kHalf > p.pool_rows) {
-            RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, static_cast<int32_t>(column), static_cast<int32_t>(block));
-            row = 0;
-          }
-        }
-        ptx::TmaLoad2D(dst + (lane - 1) * (kHalf * kDim), &key_map, 0, static_cast<int32_t>(row), full);
+        ptx::TmaLoad2D(dst + (lane - 1) * (kHalf * kDim), &key_map, 0, static_cast<int32_t>(cur.row), full);
       }
       issued = i + 1;
     }
@@ -238,7 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ---- MMA issue: four K = 32 steps per tile into accumulator i % 2 ----
     const uint64_t key_desc0 = ptx::SmemDescSw128(stage0, 16, 1024);
     const uint64_t q_desc0 = ptx::SmemDescSw128(stage0 + kKeyBytes, 16, 1024);
@@ -261,37 +290,66 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
     }
   } else {
-    // ---- epilogue: thread = token ----
+    // ---- epilogue: thread = token; group g = warp / 4 takes tiles g, g + 2, ... of the CTA's run ----
+    // What a tile needs from memory besides its accumulator (the sequence's per-head coefficients, one per
+    // thread of the first 64, and this token's key scale behind a block-table lookup) is fetched one of the
+    // group's tiles ahead: two dependent loads would otherwise stand between every two tiles.
+    const int group = warp >> 2;
+    const int gtid = tid & (kEpilogueThreads - 1);
     TileWalker walk(p.kv_len, p.batch, start_seq, start_tile, n_tiles);
-    int seq, tile, len;
-    bool ok = true;
-    for (int i = 0; ok && walk.Next(&seq, &tile, &len); ++i) {
-      const int buf = i & 1;
-      // The sequence's per-head coefficients into shared memory and this token's key scale into a register,
-      // before the wait for the accumulator.
-      if (tid < kHeadsPadded) {
-        sh->qs[buf][tid] = tid < p.heads ? p.q_scale[seq * p.heads + tid] : 0.0f;
-        sh->w[buf][tid] = tid < p.heads ? __bfloat162float(p.w[seq * p.heads + tid]) : 0.0f;
+    {
+      int s0, t0, l0;
+      if (group == 1) walk.Next(&s0, &t0, &l0);  // the odd group starts at the run's second tile
+    }
+    struct Fetched {
+      int seq, tile, len;
+      float qs, w, ks;
+      bool valid;
+    };
+    auto fetch = [&](Fetched* f) -> bool {
+      if (!walk.Next(&f->seq, &f->tile, &f->len)) return false;
+      {
+        int s1, t1, l1;
+        walk.Next(&s1, &t1, &l1);  // the other group's tile
       }
-      const int tok = tile * kTokens + tid;
-      float ks = 0.0f;
-      bool valid = tok < len;
-      if (valid) {
+      f->qs = 0.0f;
+      f->w = 0.0f;
+      if (gtid < p.heads) {
+        f->qs = p.q_scale[f->seq * p.heads + gtid];
+        f->w = __bfloat162float(p.w[f->seq * p.heads + gtid]);
+      }
+      const int tok = f->tile * kTokens + gtid;
+      f->ks = 0.0f;
+      f->valid = tok < f->len;
+      if (f->valid) {
         const int64_t column = tok / p.block_size;
-        const int64_t block = column < p.max_blocks ? p.block_table[static_cast<int64_t>(seq) * p.max_blocks + column] : -1;
+        const int64_t block = column < p.max_blocks ? p.block_table[static_cast<int64_t>(f->seq) * p.max_blocks + column] : -1;
         const int64_t row = block * p.block_size + tok % p.block_size;
         if (block < 0 || row >= p.pool_rows) {
-          valid = false;  // recorded by the producer; the score below says that the token does not count
+          f->valid = false;  // recorded by the producer; the score below says that the token does not count
         } else {
-          ks = p.k_scale[row];
+          f->ks = p.k_scale[row];
         }
       }
-      ptx::NamedBarrier(1, kEpilogueThreads);
-      ok = __all_sync(0xffffffffu, Wait(bar(&sh->acc_full[buf]), (i >> 1) & 1, sh, p.status, 3));
+      return true;
+    };
+    Fetched cur, next;
+    bool have = fetch(&next);
+    bool ok = true;
+    const int buf = group;
+    for (int n = 0; ok && have; ++n) {  // the group's n-th tile is the run's tile 2 n + group
+      cur = next;
+      have = fetch(&next);
+      if (gtid < kHeadsPadded) {
+        sh->qs[buf][gtid] = cur.qs;
+        sh->w[buf][gtid] = cur.w;
+      }
+      ptx::NamedBarrier(1 + group, kEpilogueThreads);
+      ok = __all_sync(0xffffffffu, Wait(bar(&sh->acc_full[buf]), n & 1, sh, p.status, 3));
       if (!ok) break;
       ptx::TcFenceAfterSync();
       uint32_t lo[32], hi[32];
-      const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + buf * kHeadsPadded;
+      const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + buf * kHeadsPadded;
       ptx::TmemLd32(taddr, lo);
       ptx::TmemLd32(taddr + 32, hi);
       ptx::TmemWaitLd();
@@ -299,27 +357,40 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) ptx::MbarArrive(bar(&sh->acc_empty[buf]));
       float score = 0.0f;
-#pragma unroll
-      for (int h = 0; h < 32; ++h) {
+      const float4* qs4 = reinterpret_cast<const float4*>(sh->qs[buf]);
+      const float4* w4 = reinterpret_cast<const float4*>(sh->w[buf]);
+      // A head beyond the sequence's count is skipped, not multiplied by a zero weight: its column of the
+      // accumulator came from rows of Q that belong to the next sequence (or from nothing) and may hold anything.
+      auto head = [&](int h, float qs_h, float w_h, uint32_t dot) {
         if (h < p.heads) {
-          const float scaled = __fmul_rn(__fmul_rn(sh->qs[buf][h], ks), __uint_as_float(lo[h]));
-          score = __fmaf_rn(sh->w[buf][h], scaled > 0.0f ? scaled : 0.0f, score);
+          const float scaled = __fmul_rn(__fmul_rn(qs_h, cur.ks), __uint_as_float(dot));
+          score = __fmaf_rn(w_h, scaled > 0.0f ? scaled : 0.0f, score);
         }
+      };
+#pragma unroll
+      for (int h4 = 0; h4 < 8; ++h4) {
+        const float4 a = qs4[h4], c = w4[h4];
+        head(4 * h4, a.x, c.x, lo[4 * h4]);
+        head(4 * h4 + 1, a.y, c.y, lo[4 * h4 + 1]);
+        head(4 * h4 + 2, a.z, c.z, lo[4 * h4 + 2]);
+        head(4 * h4 + 3, a.w, c.w, lo[4 * h4 + 3]);
       }
 #pragma unroll
-      for (int h = 0; h < 32; ++h) {
-        if (32 + h < p.heads) {
-          const float scaled = __fmul_rn(__fmul_rn(sh->qs[buf][32 + h], ks), __uint_as_float(hi[h]));
-          score = __fmaf_rn(sh->w[buf][32 + h], scaled > 0.0f ? scaled : 0.0f, score);
-        }
+      for (int h4 = 0; h4 < 8; ++h4) {
+        const float4 a = qs4[8 + h4], c = w4[8 + h4];
+        head(32 + 4 * h4, a.x, c.x, hi[4 * h4]);
+        head(32 + 4 * h4 + 1, a.y, c.y, hi[4 * h4 + 1]);
+        head(32 + 4 * h4 + 2, a.z, c.z, hi[4 * h4 + 2]);
+        head(32 + 4 * h4 + 3, a.w, c.w, hi[4 * h4 + 3]);
       }
-      if (tok < len) p.scores[seq * p.score_stride + tok] = valid ? score : -INFINITY;
+      const int tok = cur.tile * kTokens + gtid;
+      if (tok < cur.len) p.scores[cur.seq * p.score_stride + tok] = cur.valid ? score : -INFINITY;
     }
   }
 
   ptx::TcFenceBeforeSync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     ptx::TcFenceAfterSync();
     ptx::TmemDealloc(tmem, kTmemCols);
   }

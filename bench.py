@@ -463,23 +463,42 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
         res[name] = {"rows_per_launch": n_rows, "algorithmic_bytes": nbytes, "us_per_launch": t * 1e6,
                      "achieved_gbs": nbytes / t * 1e-9, "frac_of_measured_hbm": nbytes / t * 1e-9 / hbm_peak}
         del xq, q8, sc
-    # The sparse-selection indexer on the step's shape: 32 sequences x 4,096 tokens of FP8 index keys (128 wide),
-    # 64 index heads, top 512. First version on CUDA cores: its bound is the fp32 arithmetic
-    # (32 x 4,096 x 64 x 128 fused multiply-adds), reported as time, with the key bytes it reads for scale.
+    # The sparse path on the step's shape: the indexer over 32 sequences x 4,096 tokens of FP8 index keys (128
+    # wide, 64 index heads, top 512), then attention over the 512 selected rows of each sequence. The score kernel
+    # reads 132 bytes per token (key + key scale) and writes 4; tensor-core variant (FP8 tcgen05) and the exact
+    # CUDA-core one. The attention gathers 32 x 512 rows of 1,152 bytes with tile::gather4 loads.
     n_rows = wl.blocks * BLOCK
-    key8 = torch.randint(0, 0x50, (2, n_rows, 128), dtype=torch.uint8, device="cuda")
+    key8 = torch.randint(0, 0x50, (8, n_rows, 128), dtype=torch.uint8, device="cuda")  # 8 x 17 MB: larger than L2
     q8 = torch.randint(0, 0x50, (BATCH, HEADS, 128), dtype=torch.uint8, device="cuda")
-    k_scale = torch.rand((2, n_rows), dtype=torch.float32, device="cuda") * 0.1 + 0.01
+    k_scale = torch.rand((8, n_rows), dtype=torch.float32, device="cuda") * 0.1 + 0.01
     q_scale = torch.rand((BATCH, HEADS), dtype=torch.float32, device="cuda") * 0.1 + 0.01
     w_idx = torch.randn((BATCH, HEADS), dtype=torch.float32, device="cuda").to(torch.bfloat16)
     # (the binding allocates its outputs and workspace per call: inside a captured graph those come from
     # the graph's private pool, so the replay measures the two kernels)
-    t = timeit(lambda i: b200kv.indexer_topk(q8, q_scale, w_idx, key8[i % 2], k_scale[i % 2], wl.table, wl.kv_len,
-                                             BLOCK, CONTEXT, 512, status=wl.status), 20)
-    res["indexer_topk"] = {"sequences": BATCH, "tokens_per_sequence": CONTEXT, "index_heads": HEADS, "k": 512,
-                           "us_per_launch": t * 1e6, "key_bytes": n_rows * 132,
-                           "gflop": 2.0 * BATCH * CONTEXT * HEADS * 128 * 1e-9,
-                           "tflops_fp32": 2.0 * BATCH * CONTEXT * HEADS * 128 / t * 1e-12}
+    idx_bytes = BATCH * CONTEXT * (128 + 4 + 4)
+    for name, variant in (("indexer_topk", b200kv.INDEXER_TCGEN05), ("indexer_topk_exact", b200kv.INDEXER_EXACT)):
+        t = timeit(lambda i: b200kv.indexer_topk(q8, q_scale, w_idx, key8[i % 8], k_scale[i % 8], wl.table, wl.kv_len,
+                                                 BLOCK, CONTEXT, 512, status=wl.status, variant=variant), 24)
+        res[name] = {"sequences": BATCH, "tokens_per_sequence": CONTEXT, "index_heads": HEADS, "k": 512,
+                     "kernels": "score (FP8 tcgen05) + radix select" if variant == b200kv.INDEXER_TCGEN05
+                                else "score (fp32 chains on CUDA cores) + radix select",
+                     "us_per_launch": t * 1e6, "score_bytes": idx_bytes,
+                     "gflop": 2.0 * BATCH * CONTEXT * HEADS * 128 * 1e-9,
+                     "tflops": 2.0 * BATCH * CONTEXT * HEADS * 128 / t * 1e-12}
+    index, n_sel = b200kv.indexer_topk(q8, q_scale, w_idx, key8[0], k_scale[0], wl.table, wl.kv_len, BLOCK, CONTEXT, 512,
+                                       status=wl.status)
+    rows_sel = b200kv.resolve_rows(wl.table, BLOCK, index, n_sel, wl.blocks * BLOCK, status=wl.status)
+    for name, variant in (("sparse_decode_512", b200kv.DECODE_TCGEN05), ("sparse_decode_512_simt", b200kv.DECODE_SIMT)):
+        t = timeit(lambda i: b200kv.mla_decode(wl.q[i % LAYERS], wl.views[i % LAYERS], None, n_sel, BLOCK, SCALE,
+                                               out=wl.out[i % LAYERS], workspace=wl.ws, variant=variant, status=wl.status,
+                                               row_index=rows_sel), 43)
+        sel_bytes = BATCH * 512 * ROW * 2 + BATCH * HEADS * (ROW + LATENT) * 2
+        res[name] = {"sequences": BATCH, "rows_per_sequence": 512, "algorithmic_bytes": sel_bytes,
+                     "kernel": "MlaDecodeTcKernel (tile::gather4 row loads) + MlaFinalizeKernel"
+                               if variant == b200kv.DECODE_TCGEN05 else "MlaDecodeSimtKernel over single-row blocks",
+                     "us_per_launch": t * 1e6, "achieved_gbs": sel_bytes / t * 1e-9,
+                     "frac_of_measured_hbm": sel_bytes / t * 1e-9 / hbm_peak}
+    del index, n_sel, rows_sel
     del src, out_l, out_r, trig, fused_src, key8, k_scale, lat_src, rope_src, flat_src, flat_dst
     return res
 
