@@ -270,6 +270,9 @@ __device__ __forceinline__ void IssueQkGroup(uint64_t q_desc, uint64_t kdesc, ui
   }
 }
 
+// kGathered: the tiles are runs of 64 entries of a list of pool rows (TcParams::row_index) instead of runs of 64
+// tokens of a block; a separate instantiation, so that the dense kernel's code is not touched by it.
+template <bool kGathered>
 __global__ void __launch_bounds__(kThreads, 1)
     MlaDecodeTcKernel(const __grid_constant__ CUtensorMap latent_map, const __grid_constant__ CUtensorMap rope_map,
                       const __grid_constant__ CUtensorMap q_map, TcParams p) {
@@ -347,43 +350,68 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   };
   // A tile of gathered rows (row_index in place of the block table): entries 64 t .. 64 t + 63 of the sequence's
-  // row list, four rows per load. Lane l takes rows 4 (l % 16) .. + 3 of the tile in the slabs of its parity (lanes
-  // 0-15: slabs 0, 2, 4, 6, 8; lanes 16-31: 1, 3, 5, 7): 144 loads of 512 bytes a tile, four or five a lane. The
-  // warp takes the tile group by group as PV gives the stage back, lane 0 announcing each group's bytes first.
-  // Entries past the sequence's length are not read (their rows load as row 0 and the softmax masks them); an
-  // entry inside it that is not a row of the pool is recorded and reads row 0.
-  auto issue_gathered = [&](int seq, int seq_len, int t, int g) -> bool {
-    const int stage = g % kStages;
-    const int first = t * kTile + 4 * (lane & 15);
-    int r[4];
+  // row list. The producer warp copies them with 16-byte asynchronous copies, doing the 128-byte swizzle in the
+  // address arithmetic: chunk c of tile row r goes to r * 128 + ((c ^ (r % 8)) * 16) of its slab, which is where
+  // a swizzled TMA load would have put it. An instruction of the warp moves four rows' 128 bytes of one slab
+  // (lane = row within the four x chunk), 144 instructions a tile. (The gathering form of the TMA load, four
+  // rows of one slab per instruction, was measured first: the TMA unit spends some 90 cycles on an instruction
+  // whatever its size, so 144 of them a tile made a tile five microseconds long.) The copies of a group arrive
+  // on the group's barrier, which in this mode counts the warp's 32 lanes instead of one announcement of bytes;
+  // they write through the generic proxy, so the warps that issue MMAs fence after their wait. The warp takes
+  // the tile group by group as PV gives the stage back. Entries past the sequence's length are not read (their
+  // rows load as row 0 and the softmax masks them); an entry inside it that is not a row of the pool is recorded
+  // and reads row 0.
+  // The row numbers of a tile are read a tile ahead (gathered_rows fills `rid` for the tile the next call of
+  // issue_gathered copies), so their latency lies under the previous tile's copies instead of in front of
+  // this tile's.
+  const int g_sub = lane >> 3;          // row within each run of four
+  const uint32_t g_chunk = lane & 7;    // 16-byte chunk of the slab's 128-byte row
+  int rid[kTile / 4];
+  auto gathered_rows = [&](int seq, int seq_len, int t) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int j = first + i;
+    for (int q = 0; q < kTile / 4; ++q) {
+      const int j = t * kTile + 4 * q + g_sub;
       int row = 0;
-      if (j < seq_len && j < p.row_index_stride) {
-        row = p.row_index[static_cast<int64_t>(seq) * p.row_index_stride + j];
-        if (row < 0 || row >= p.pool_rows) {
-          RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, j, row);
-          row = 0;
-        }
-      }
-      r[i] = row;
+      if (j < seq_len && j < p.row_index_stride) row = p.row_index[static_cast<int64_t>(seq) * p.row_index_stride + j];
+      rid[q] = row;
     }
-    const uint32_t dst = kv_addr + stage * kStageBytes + (lane & 15) * (4 * 128);
+  };
+  auto issue_gathered = [&](int seq, int g) -> bool {
+    const int stage = g % kStages;
+#pragma unroll
+    for (int q = 0; q < kTile / 4; ++q) {
+      if (rid[q] < 0 || rid[q] >= p.pool_rows) {
+        if (g_chunk == 0) RecordError(p.status, B200KV_DEV_BAD_BLOCK, seq, 4 * q + g_sub, rid[q]);
+        rid[q] = 0;
+      }
+    }
+    const char* latent_lane = p.pool_latent + g_chunk * 16;
+    const uint32_t dst_lane = kv_addr + stage * kStageBytes + g_sub * 128;
     bool ok = true;
+#pragma unroll 1
     for (int c = 0; c < kGroups && ok; ++c) {
       if (g >= kStages) {
-        ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_empty[stage][c]), ((g / kStages) & 1) ^ 1, misc, p.status, 10));
+        ok = __all_sync(0xffffffffu, BoundedSpin(bar(&misc->kv_empty[stage][c]), ((g / kStages) & 1) ^ 1, misc, p.status, 10));
         if (!ok) break;
       }
-      const uint32_t full = bar(&misc->kv_full[stage][c]);
-      if (lane == 0) ptx::MbarArriveExpectTx(full, (c == kGroups - 1 ? 3 : 2) * kSlabBytes);
-      __syncwarp();
-      const int slab = 2 * c + (lane >> 4);
-      ptx::TmaGather4Hint(dst + slab * kSlabBytes, &latent_map, 64 * slab, r[0], r[1], r[2], r[3], full, drop_policy);
-      if (c == kGroups - 1 && lane < 16) {
-        ptx::TmaGather4Hint(dst + 8 * kSlabBytes, &rope_map, 0, r[0], r[1], r[2], r[3], full, drop_policy);
+#pragma unroll 1
+      for (int k = 0; k < 2; ++k) {
+        const int slab = 2 * c + k;
+#pragma unroll
+        for (int q = 0; q < kTile / 4; ++q) {
+          // row r = 4 q + g_sub, so r % 8 = 4 (q % 2) + g_sub
+          ptx::CpAsync16(dst_lane + slab * kSlabBytes + q * 512 + ((g_chunk ^ (4 * (q & 1) + g_sub)) << 4),
+                         latent_lane + rid[q] * p.pool_latent_bytes + slab * 128);
+        }
       }
+      if (c == kGroups - 1) {
+#pragma unroll
+        for (int q = 0; q < kTile / 4; ++q) {
+          ptx::CpAsync16(dst_lane + 8 * kSlabBytes + q * 512 + ((g_chunk ^ (4 * (q & 1) + g_sub)) << 4),
+                         p.pool_rope + rid[q] * p.pool_rope_bytes + g_chunk * 16);
+        }
+      }
+      ptx::CpAsyncArriveOn(bar(&misc->kv_full[stage][c]));
     }
     return ok;
   };
@@ -430,7 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       for (int s = 0; s < kStages; ++s) {
         for (int k = 0; k < kGroups; ++k) {
-          ptx::MbarInit(bar(&misc->kv_full[s][k]), 1);
+          ptx::MbarInit(bar(&misc->kv_full[s][k]), kGathered ? 32 : 1);  // gathered: one arrival a lane
           ptx::MbarInit(bar(&misc->kv_empty[s][k]), 1);
         }
         ptx::MbarInit(bar(&misc->p_full[s]), kSoftmaxWarps);
@@ -534,7 +562,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int t_end = min(start_seq_tiles - (p.new_latent != nullptr ? 1 : 0), start_tile + static_cast<int>(hi - lo));
       static_assert(kStages == 2, "the first tiles' rows are looked up before the dependency wait, two of them");
       // (Gathered rows: every tile goes out from the main loop, which reads the row numbers after the wait.)
-      const int n_first = p.row_index != nullptr ? 0 : max(0, min(kStages, t_end - start_tile));
+      const int n_first = kGathered ? 0 : max(0, min(kStages, t_end - start_tile));
       const int64_t row0 = n_first > 0 ? tile_row(start_seq, begin, start_tile) : 0;
       const int64_t row1 = n_first > 1 ? tile_row(start_seq, begin, start_tile + 1) : 0;
       if (p.stable_tables != 0) GridDependencyWait();  // Q and the pool are the preceding kernels' to write
@@ -579,6 +607,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       int seg = 0;
       uint32_t n_appended = 0;
       bool fetch_pending = false;  // a new row's bulk load is in flight towards shared memory
+      bool rows_ahead = false;     // gathered rows: `rid` already holds the row numbers of the tile to come
       const bool loader = lane < 9;
       while (ok && walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len)) {
         // Q of this segment's sequence, once the previous segment's last QK has finished reading the
@@ -597,9 +626,24 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         for (int t = t_lo; t < t_hi; ++t, ++g) {
           if (g < pre_issued) continue;
-          if (p.row_index != nullptr) {
-            ok = issue_gathered(seq, seq_len, t, g);
+          if constexpr (kGathered) {
+            if (!rows_ahead) gathered_rows(seq, seq_len, t);  // the CTA's first tile
+            ok = issue_gathered(seq, g);
             if (!ok) break;
+            // The next tile's row numbers start on their way now: the next tile of this segment, or the first of
+            // the next segment (whose sequence and length the walker's copy below looks up).
+            rows_ahead = false;
+            if (t + 1 < t_hi) {
+              gathered_rows(seq, seq_len, t + 1);
+              rows_ahead = true;
+            } else {
+              SegmentWalker peek = walk;
+              int seq2, lo2, hi2, tiles2, len2;
+              if (peek.Next(&seq2, &lo2, &hi2, &tiles2, &len2)) {
+                gathered_rows(seq2, len2, lo2);
+                rows_ahead = true;
+              }
+            }
             continue;
           }
           const int64_t checked_row = tile_row_checked(seq, begin, t);
@@ -701,6 +745,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       // Values that steer this loop come from memory; broadcasting them from lane 0 is what tells the
       // compiler they are warp-uniform, which keeps the descriptor arithmetic on the uniform datapath.
       const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+      // Gathered rows were written by plain asynchronous copies (generic proxy); the MMAs read through the async
+      // proxy, so the issuing warp puts a proxy fence between its wait and its instructions.
 
       while (ok) {
         const int have = walk.Next(&seq, &t_lo, &t_hi, &seq_tiles, &seq_len) ? 1 : 0;
@@ -724,6 +770,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if (!ok) break;
             ptx::TcFenceAfterSync();
+            if constexpr (kGathered) ptx::FenceProxyAsyncShared();
             const uint64_t kdesc = DescAt(k_desc0, stage * kStageBytes);
             const uint32_t d = tmem_u + kTmemColS + kTile * buf;
             // Twelve k-steps per slab group, each group as soon as its slabs have landed (compile-time
@@ -735,6 +782,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if (!ok) break;
             ptx::TcFenceAfterSync();
+            if constexpr (kGathered) ptx::FenceProxyAsyncShared();
             IssueQkGroup<2, 2>(q_desc, kdesc, d);
             ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][2]), kv_parity, misc, p.status, 27));
             if (ok && first_of_segment) {
@@ -742,6 +790,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if (!ok) break;
             ptx::TcFenceAfterSync();
+            if constexpr (kGathered) ptx::FenceProxyAsyncShared();
             IssueQkGroup<4, 2>(q_desc, kdesc, d);
             ok = __all_sync(0xffffffffu, BoundedWait(bar(&misc->kv_full[stage][3]), kv_parity, misc, p.status, 28));
             if (ok && first_of_segment) {
@@ -749,6 +798,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if (!ok) break;
             ptx::TcFenceAfterSync();
+            if constexpr (kGathered) ptx::FenceProxyAsyncShared();
             IssueQkGroup<6, 3>(q_desc, kdesc, d);
             if (ptx::ElectOne()) {
               ptx::TcCommit(bar(&misc->s_full[buf]));
@@ -767,6 +817,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                             BoundedWait(bar(&misc->p_full[stage]), (g / kStages) & 1, misc, p.status, 21));
             if (!ok) break;
             ptx::TcFenceAfterSync();
+            if constexpr (kGathered) ptx::FenceProxyAsyncShared();
             const uint32_t stage_off = stage * kStageBytes;
             const uint64_t pdesc = DescAt(k_desc0, stage_off + 8 * kSlabBytes);  // K-major: row = head, 32 B per k-step
             const uint64_t vdesc = DescAt(v_desc0, stage_off);
@@ -1608,15 +1659,20 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   int device = 0;
   if (int32_t rc = CheckCuda(cudaGetDevice(&device), "cudaGetDevice")) return rc;
   if (device != configured_device) {
-    if (int32_t rc = CheckCuda(cudaFuncSetAttribute(MlaDecodeTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int32_t rc = CheckCuda(cudaFuncSetAttribute(MlaDecodeTcKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                     kSmemBytes),
                                "tcgen05 decode smem opt-in")) {
+      return rc;
+    }
+    if (int32_t rc = CheckCuda(cudaFuncSetAttribute(MlaDecodeTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    kSmemBytes),
+                               "tcgen05 decode (gathered rows) smem opt-in")) {
       return rc;
     }
     configured_device = device;
   }
   CUtensorMap latent_map, rope_map;
-  const int32_t box_rows = a.row_index != nullptr ? 1 : kTile;  // gathered rows come four single-row boxes at a time
+  const int32_t box_rows = kTile;
   if (int32_t rc = GetRowMap(a.pool.latent, a.pool.latent_row_stride, a.pool.pool_rows, kLatent, box_rows, &latent_map)) return rc;
   if (int32_t rc = GetRowMap(a.pool.rope, a.pool.rope_row_stride, a.pool.pool_rows, kRope, box_rows, &rope_map)) return rc;
 
@@ -1660,8 +1716,11 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.ws_l = p.ws_m + slots * kHeads;
   p.status = status;
 
-  if (int32_t rc = CheckCuda(LaunchOverlapped(MlaDecodeTcKernel, dim3(n_ctas), dim3(kThreads), kSmemBytes, stream,
-                                              latent_map, rope_map, q_map, p),
+  if (int32_t rc = CheckCuda(a.row_index != nullptr
+                                 ? LaunchOverlapped(MlaDecodeTcKernel<true>, dim3(n_ctas), dim3(kThreads), kSmemBytes,
+                                                    stream, latent_map, rope_map, q_map, p)
+                                 : LaunchOverlapped(MlaDecodeTcKernel<false>, dim3(n_ctas), dim3(kThreads), kSmemBytes,
+                                                    stream, latent_map, rope_map, q_map, p),
                              "tcgen05 decode launch")) {
     return rc;
   }

@@ -123,15 +123,14 @@ __device__ __forceinline__ void TmaLoad2DHint(uint32_t dst, const CUtensorMap* m
       : "memory");
 }
 
-// Four rows of a 2-D tensor (its map's box is one row of 64 columns), given by their row numbers, into four
-// consecutive 128-byte rows of shared memory: the gathering form of the tiled load. x is the column.
-__device__ __forceinline__ void TmaGather4Hint(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t r0, int32_t r1,
-                                               int32_t r2, int32_t r3, uint32_t bar, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, "
-      "{%2, %3, %4, %5, %6}], [%7], %8;" ::"r"(dst),
-      "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar), "l"(policy)
-      : "memory");
+// 16 bytes global -> shared, asynchronously, by the calling thread (the non-bulk copy: it writes through the
+// generic proxy), and the arrival on an mbarrier that is triggered once all such copies the thread has issued
+// so far have landed. The arrival is one of the barrier's expected count (it adds nothing to it).
+__device__ __forceinline__ void CpAsync16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void CpAsyncArriveOn(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // Untiled bulk copy, global -> this CTA's shared memory (both 16-byte aligned, a multiple of 16 bytes),

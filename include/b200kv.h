@@ -167,9 +167,9 @@ typedef struct b200kv_decode_args {
    * (device int32, row stride row_index_stride elements; what b200kv_resolve_rows writes) instead of walking
    * block_table, which is then ignored together with block_size and max_blocks; kv_begin and the fused append
    * must be null. An entry that is not a row of the pool is recorded as B200KV_DEV_BAD_BLOCK. The tensor-core
-   * kernel takes the rows four at a time with the gathering form of the tiled TMA load (tile::gather4), 64 rows
-   * a tile, so a top-k selection runs on the same pipeline as a dense history; the CUDA-core kernel treats the
-   * list as a table of single-row blocks.
+   * kernel brings the rows in, 64 a tile, with 16-byte asynchronous copies that place them as a swizzled TMA
+   * load would, so a top-k selection runs on the same tcgen05 pipeline as a dense history; the CUDA-core kernel
+   * treats the list as a table of single-row blocks.
    */
   const int32_t* row_index;
   int64_t row_index_stride;

@@ -224,8 +224,8 @@ def test_attention_over_a_selected_subset_of_tokens():
 @pytest.mark.parametrize("variant", VARIANTS)
 @pytest.mark.parametrize("max_ctas", [0, 3], ids=["all-sms", "3-ctas"])
 def test_attention_over_gathered_rows(variant, max_ctas):
-    """The row list itself as the call's argument (row_index): the tensor-core kernel loads the listed rows four
-    at a time with the gathering TMA load; the CUDA-core kernel reads the list as single-row blocks. Selections of
+    """The row list itself as the call's argument (row_index): the tensor-core kernel copies the listed rows
+    into its swizzled stages with 16-byte asynchronous copies; the CUDA-core kernel reads the list as single-row blocks. Selections of
     512 tokens in arbitrary order out of long, fragmented histories, a short one (17 rows: one partial tile), an
     empty one, one of exactly a tile, and one whose list is longer than the others (stride larger than any count).
     Against the float64 statement on the same rows, and the two kernels agree on what the rows are: a repeated
