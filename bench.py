@@ -466,7 +466,7 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
     # The sparse path on the step's shape: the indexer over 32 sequences x 4,096 tokens of FP8 index keys (128
     # wide, 64 index heads, top 512), then attention over the 512 selected rows of each sequence. The score kernel
     # reads 132 bytes per token (key + key scale) and writes 4; tensor-core variant (FP8 tcgen05) and the exact
-    # CUDA-core one. The attention gathers 32 x 512 rows of 1,152 bytes with tile::gather4 loads.
+    # CUDA-core one. The attention gathers 32 x 512 rows of 1,152 bytes with 16-byte asynchronous copies.
     n_rows = wl.blocks * BLOCK
     key8 = torch.randint(0, 0x50, (8, n_rows, 128), dtype=torch.uint8, device="cuda")  # 8 x 17 MB: larger than L2
     q8 = torch.randint(0, 0x50, (BATCH, HEADS, 128), dtype=torch.uint8, device="cuda")
@@ -494,7 +494,7 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
                                                row_index=rows_sel), 43)
         sel_bytes = BATCH * 512 * ROW * 2 + BATCH * HEADS * (ROW + LATENT) * 2
         res[name] = {"sequences": BATCH, "rows_per_sequence": 512, "algorithmic_bytes": sel_bytes,
-                     "kernel": "MlaDecodeTcKernel (tile::gather4 row loads) + MlaFinalizeKernel"
+                     "kernel": "MlaDecodeTcKernel<gathered> (cp.async rows, swizzled) + MlaFinalizeKernel"
                                if variant == b200kv.DECODE_TCGEN05 else "MlaDecodeSimtKernel over single-row blocks",
                      "us_per_launch": t * 1e6, "achieved_gbs": sel_bytes / t * 1e-9,
                      "frac_of_measured_hbm": sel_bytes / t * 1e-9 / hbm_peak}
