@@ -74,6 +74,8 @@ class DecodeArgs(Structure):
         ("flags", ctypes.c_uint32),
         ("row_index", c_void_p),
         ("row_index_stride", c_int64),
+        ("out_fp8", c_void_p),
+        ("out_scale", c_void_p),
     ]
 
 
@@ -345,13 +347,14 @@ def decode_workspace_bytes(batch: int, heads: int = HEADS, max_ctas: int = 0) ->
 
 def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: float, out=None, lse=None,
                kv_begin=None, partial=None, workspace=None, variant: int = DECODE_AUTO, max_ctas: int = 0,
-               status=None, stream=None, new_rows=None, stable_tables: bool = False, row_index=None) -> None:
+               status=None, stream=None, new_rows=None, stable_tables: bool = False, row_index=None, quantised=None) -> None:
     """q bf16 [B, H, 576]; out bf16 [B, H, 512]; lse fp32 [B, H]; partial = (o fp32 [B,H,512], m, l).
     new_rows = (latent bf16 [B, 512], rope bf16 [B, 64]): the append fused into the launch, each sequence's
     new row written at its position kv_len - 1 before the attention reads it. stable_tables: the block table
     and the lengths were not written by the kernel just before this call on the stream (B200KV_DECODE_STABLE_TABLES).
     row_index int32 [B, max_selected]: attend over these pool rows (kv_len = how many per sequence) instead of the
-    block table, which may then be None."""
+    block table, which may then be None. quantised = (fp8 uint8 [B, H, 512], scales uint8 [B, H, 16]): the output's MX
+    quantisation written by the same launch."""
     args = DecodeArgs()
     args.q = _ptr(q)
     args.q_seq_stride = q.stride(0)
@@ -361,6 +364,8 @@ def mla_decode(q, view: PoolView, block_table, kv_len, block_size: int, scale: f
     args.max_blocks = 0 if block_table is None else block_table.stride(0)
     if row_index is not None:
         args.row_index, args.row_index_stride = _ptr(row_index), row_index.stride(0)
+    if quantised is not None:
+        args.out_fp8, args.out_scale = _ptr(quantised[0]), _ptr(quantised[1])
     args.kv_len = _ptr(kv_len)
     args.kv_begin = _ptr(kv_begin)
     args.batch = q.shape[0]
@@ -419,9 +424,7 @@ def mla_decode_static(q, view: PoolView, block_table, kv_len, block_size: int, s
     args.q_head_stride = q.stride(1)
     args.pool = view
     args.block_table = _ptr(block_table)
-    args.max_blocks = 0 if block_table is None else block_table.stride(0)
-    if row_index is not None:
-        args.row_index, args.row_index_stride = _ptr(row_index), row_index.stride(0)
+    args.max_blocks = block_table.stride(0)
     args.kv_len = _ptr(kv_len)
     args.kv_begin = _ptr(kv_begin)
     args.batch = q.shape[0]

@@ -122,6 +122,10 @@ int32_t ValidateDecodeArgs(const b200kv_decode_args& a, const char* who) {
       return B200KV_ERR_INVALID;
     }
   }
+  if ((a.out_fp8 == nullptr) != (a.out_scale == nullptr) || (a.out_fp8 != nullptr && (want_partial || a.heads != B200KV_HEADS))) {
+    SetLastError("%s refused: out_fp8 and out_scale come together, with out (not partial_*) and 64 heads", who);
+    return B200KV_ERR_INVALID;
+  }
   const bool table_ok = a.row_index != nullptr ||
                         (a.block_size > 0 && a.max_blocks > 0 && a.pool.pool_rows % a.block_size == 0);
   if (a.batch < 0 || a.heads <= 0 || !table_ok ||
@@ -163,7 +167,7 @@ extern "C" int64_t b200kv_fault_clear(void) {
   return fired;
 }
 
-extern "C" int32_t b200kv_abi_version(void) { return 4; }
+extern "C" int32_t b200kv_abi_version(void) { return 5; }
 
 extern "C" size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas) {
   if (batch <= 0 || heads <= 0) return 0;
@@ -203,15 +207,17 @@ extern "C" int32_t b200kv_mla_decode(const b200kv_decode_args* args, void* strea
     return a.workspace == nullptr ? B200KV_ERR_NULLPTR : B200KV_ERR_INVALID;
   }
   if (use_tc) return LaunchMlaDecodeTc(a, ctas, static_cast<cudaStream_t>(stream), status, nullptr);
+  b200kv_decode_args simt = a;
   if (a.row_index != nullptr) {  // the CUDA-core kernel reads a row list as a table of single-row blocks
-    b200kv_decode_args as_table = a;
-    as_table.block_table = a.row_index;
-    as_table.max_blocks = a.row_index_stride;
-    as_table.block_size = 1;
-    as_table.row_index = nullptr;
-    return LaunchMlaDecodeSimt(as_table, static_cast<cudaStream_t>(stream), status);
+    simt.block_table = a.row_index;
+    simt.max_blocks = a.row_index_stride;
+    simt.block_size = 1;
+    simt.row_index = nullptr;
   }
-  return LaunchMlaDecodeSimt(a, static_cast<cudaStream_t>(stream), status);
+  if (int32_t rc = LaunchMlaDecodeSimt(simt, static_cast<cudaStream_t>(stream), status)) return rc;
+  if (a.out_fp8 == nullptr) return B200KV_OK;
+  const int64_t cols = static_cast<int64_t>(a.heads) * B200KV_LATENT_DIM;
+  return b200kv_mx_quant_e4m3(a.out, cols, a.batch, cols, a.out_fp8, cols, a.out_scale, cols / 32, stream);
 }
 
 extern "C" int32_t b200kv_mla_decode_peer(const b200kv_decode_args* args, void* const* peer_buffers, int32_t world,

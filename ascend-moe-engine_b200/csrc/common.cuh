@@ -41,6 +41,33 @@ __device__ __forceinline__ void StoreStream16(void* p, int4 v) {
                : "memory");
 }
 
+// MX (block-32) quantisation to FP8 E4M3 with an E8M0 scale, the arithmetic of the reference's attn_quant stage
+// (src/pipeline/pipeline.cpp:250-258) as every kernel of this library that quantises applies it. A block's scale
+// is 2^e, e = floor(log2 amax) - 8 clamped to [-127, 127] and stored as e + 127; a block that holds a NaN gets
+// scale 0xff and every value of it the code sign | 0x7f.
+struct MxScale {
+  uint32_t code;  // the E8M0 byte
+  float inv;      // 2^-e
+};
+__device__ __forceinline__ MxScale MxScaleOf(float amax, bool has_nan) {
+  MxScale s;
+  if (has_nan) {
+    s.code = 0xffu;
+    s.inv = 0.0f;
+    return s;
+  }
+  // floor(log2 amax) from the exponent field: a subnormal maximum (field 0) is below 2^-126, where the
+  // clamp to -127 applies anyway, and an infinite one (field 255) takes the upper clamp.
+  const int field = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);
+  int e = field == 0 ? -127 : (field == 255 ? 127 : field - 127 - 8);
+  e = e < -127 ? -127 : e;
+  s.code = static_cast<uint32_t>(e + 127);
+  // 2^-e as a float (2^-127 is the subnormal 0x00400000); the product is exact wherever it matters:
+  // it can only round where the result is far below the smallest FP8 value, and overflow saturates.
+  s.inv = __uint_as_float(e == 127 ? 0x00400000u : static_cast<uint32_t>(127 - e) << 23);
+  return s;
+}
+
 // Programmatic dependent launch: a kernel launched with LaunchOverlapped may be scheduled while its
 // predecessor in the stream is still draining; it must call GridDependencyWait() before it reads anything
 // the predecessor wrote. A kernel lets its successor start early with GridDependencyTrigger(). Both are

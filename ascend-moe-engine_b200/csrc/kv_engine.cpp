@@ -314,12 +314,13 @@ extern "C" int32_t b200kv_engine_layer_attend(b200kv_engine* e, int32_t layer, c
   // The step's table and lengths were uploaded before the first layer; from the second layer on the kernel
   // before this one on the stream is the producer, which does not write them.
   a.flags = B200KV_DECODE_STABLE_TABLES;
+  // Stage 10, the attention output [sequences, 64 x 512] as FP8 E4M3 with one E8M0 scale per 32 values, rides in
+  // the attention call: the kernel that writes `out` quantises what it writes.
+  a.out_fp8 = out_fp8;
+  a.out_scale = out_fp8 != nullptr ? out_scales : nullptr;
+  if (out_fp8 != nullptr && out_scales == nullptr) return Refuse("engine_layer_attend: out_fp8 without out_scales");
   if (int32_t rc = b200kv_arena_workspace_fits(e->arena, b200kv_mla_decode_workspace_bytes(a.batch, a.heads, 0))) return rc;
-  if (int32_t rc = b200kv_mla_decode(&a, stream, e->d_status)) return rc;
-  if (out_fp8 == nullptr) return B200KV_OK;
-  // Stage 10: the attention output [sequences, 64 x 512] as FP8 E4M3 with one E8M0 scale per 32 values.
-  const int64_t cols = static_cast<int64_t>(B200KV_HEADS) * B200KV_LATENT_DIM;
-  return b200kv_mx_quant_e4m3(out, cols, e->step_seqs, cols, out_fp8, cols, out_scales, cols / 32, stream);
+  return b200kv_mla_decode(&a, stream, e->d_status);
 }
 
 extern "C" int32_t b200kv_engine_end_step(b200kv_engine* e) {

@@ -252,23 +252,15 @@ __global__ void __launch_bounds__(256)
         nan |= __shfl_xor_sync(0xffffffffu, nan, off);
       }
       uint32_t out[2];
-      uint8_t scale;
+      const MxScale block = MxScaleOf(amax, nan != 0);
+      const uint8_t scale = static_cast<uint8_t>(block.code);
       if (nan) {
-        scale = 0xff;
         out[0] = (((w[0] >> 8) & 0x80u) | 0x7fu) | ((((w[0] >> 24) & 0x80u) | 0x7fu) << 8) |
                  ((((w[1] >> 8) & 0x80u) | 0x7fu) << 16) | ((((w[1] >> 24) & 0x80u) | 0x7fu) << 24);
         out[1] = (((w[2] >> 8) & 0x80u) | 0x7fu) | ((((w[2] >> 24) & 0x80u) | 0x7fu) << 8) |
                  ((((w[3] >> 8) & 0x80u) | 0x7fu) << 16) | ((((w[3] >> 24) & 0x80u) | 0x7fu) << 24);
       } else {
-        // floor(log2 amax) from the exponent field: a subnormal maximum (field 0) is below 2^-126, where the
-        // clamp to -127 applies anyway, and an infinite one (field 255) takes the upper clamp.
-        const int field = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);
-        int e = field == 0 ? -127 : (field == 255 ? 127 : field - 127 - 8);
-        e = e < -127 ? -127 : e;
-        scale = static_cast<uint8_t>(e + 127);
-        // 2^-e as a float (2^-127 is the subnormal 0x00400000); the product is exact wherever it matters:
-        // it can only round where the result is far below the smallest FP8 value, and overflow saturates.
-        const float inv = __uint_as_float(e == 127 ? 0x00400000u : static_cast<uint32_t>(127 - e) << 23);
+        const float inv = block.inv;
         uint32_t b[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {

@@ -28,6 +28,7 @@
 // Every wait is bounded: when a wait runs out the kernel records B200KV_DEV_TIMEOUT in the status
 // word, raises a CTA-wide abort flag, waits (bounded) for its own TMA loads, frees TMEM and returns.
 #include <cuda.h>
+#include <cuda_fp8.h>
 
 #include <mutex>
 #include <unordered_map>
@@ -120,6 +121,8 @@ struct TcParams {
   int64_t row_index_stride;
   float scale_log2;  // scale * log2(e)
   __nv_bfloat16* out;
+  uint8_t* out_q;      // [B][64][512] FP8 E4M3 of out, MX block 32 along a head's row; or null
+  uint8_t* out_scale;  // [B][64][16] E8M0
   float* lse;
   float* user_o;  // caller's partial buffers (shard mode) or null
   float* user_m;
@@ -1114,7 +1117,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // over peer memory, and the same threads then wait (bounded) for the other ranks' words of their columns,
 // merge them and write the final rows: the exchange protocol of kv_peer.cu without a kernel, and a pass over
 // the partial, in between. A thread waits only for words that other GPUs' kernels write.
-template <int kGroups, bool kPeer = false>
+template <int kGroups, bool kPeer = false, bool kQuant = false>
 __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2)
     MlaFinalizeKernel(TcParams p, int32_t n_ctas, PeerRing ring) {
   static_assert(!kPeer || kGroups == 8, "the peer form is built on the few-sequences variant");
@@ -1188,6 +1191,24 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
   const long long mine = shared_meta[4];
   const int cf = static_cast<int>(shared_meta[5]), cl = static_cast<int>(shared_meta[6]), cp = static_cast<int>(shared_meta[7]);
   const bool want_partial = p.user_o != nullptr;
+  // The output's MX quantisation (the reference's next stage, attn_quant: src/pipeline/pipeline.cpp:250-258) as
+  // this kernel's epilogue: the 32 lanes of a warp hold 32 consecutive columns of one head's row, which is one
+  // block; they agree on its maximum with shuffles and each writes its byte. The value quantised is the bf16
+  // the kernel writes to `out`, so the bytes equal those of the stand-alone quantiser run on `out`. (kQuant: an
+  // instantiation of its own; the kernel without it is unchanged.)
+  auto write_quantised = [&](int64_t out_row, int dv, __nv_bfloat16 y) {  // every lane of the warp calls
+    const float x = __bfloat162float(y);
+    // One warp reduction over the bit images of |x|: they order like the values, and a NaN's image is above
+    // infinity's, so the maximum also tells whether the block holds one.
+    const uint32_t top = __reduce_max_sync(0xffffffffu, __float_as_uint(x) & 0x7fffffffu);
+    const int nan = top > 0x7f800000u ? 1 : 0;
+    const float amax = __uint_as_float(top);
+    const MxScale block = MxScaleOf(amax, nan != 0);
+    const uint32_t code = nan != 0 ? (((__float_as_uint(x) >> 24) & 0x80u) | 0x7fu)
+                                   : static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fmul_rn(x, block.inv), __NV_SATFINITE, __NV_E4M3));
+    p.out_q[out_row * kLatent + dv] = static_cast<uint8_t>(code);
+    if (lane == 0) p.out_scale[out_row * (kLatent / 32) + dv / 32] = static_cast<uint8_t>(block.code);
+  };
   const CostCut cut{CostCut::Total(total, nonempty), n_ctas};
   // Slot of CTA c's part of this sequence, or -1: the CTA holds a part if its first tile inside the sequence
   // lies before the next CTA's run. When every CTA's share of the cost is at least 5 units it holds at least
@@ -1206,7 +1227,20 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
   // below are what that kernel wrote, so they wait for its completion.
   GridDependencyTrigger();
   GridDependencyWait();
-  if (!kPeer && mine > 0 && cf == cl) return;  // written directly by the decode kernel
+  if (!kPeer && mine > 0 && cf == cl) {  // written directly by the decode kernel
+    if (kQuant && group == 0) {  // ... whose rows this CTA's columns are read back from and quantised
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int q = 0; q < kPasses; ++q) {
+          const int64_t out_row = static_cast<int64_t>(b) * kHeads + 4 * hq + i;
+          const int dv = dv0 + tl + kGroupThreads * q;
+          write_quantised(out_row, dv, p.out[out_row * kLatent + dv]);
+        }
+      }
+    }
+    return;
+  }
 
   float acc[kPasses][4];
 #pragma unroll
@@ -1403,11 +1437,14 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
         merged[i] = fmaf(merged[i], carry, __uint_as_float(static_cast<uint32_t>(w[i])) * weight);
       }
     }
+    ok = __all_sync(0xffffffffu, ok);  // (one warp is left here; the quantiser below shuffles across all of it)
     if (ok) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float inv = total_l[i] > 0.0f ? 1.0f / total_l[i] : 0.0f;
-        p.out[(row_first + i) * kLatent + dv_first] = __float2bfloat16_rn(merged[i] * inv);
+        const __nv_bfloat16 y = __float2bfloat16_rn(merged[i] * inv);
+        p.out[(row_first + i) * kLatent + dv_first] = y;
+        if constexpr (kQuant) write_quantised(row_first + i, dv_first, y);
       }
       if (owns_ml && p.lse != nullptr) {
         float lse_value = -INFINITY;
@@ -1442,7 +1479,9 @@ __global__ void __launch_bounds__(kGroups == 1 ? 128 : 256, kGroups == 1 ? 7 : 2
       if (want_partial) {
         p.user_o[at] = acc[q][i];
       } else {
-        p.out[at] = __float2bfloat16_rn(acc[q][i] * inv);
+        const __nv_bfloat16 y = __float2bfloat16_rn(acc[q][i] * inv);
+        p.out[at] = y;
+        if constexpr (kQuant) write_quantised(row0 + i, dv_first + kGroupThreads * q, y);
       }
     }
   }
@@ -1704,6 +1743,8 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   p.block_size = a.block_size;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.out = static_cast<__nv_bfloat16*>(a.out);
+  p.out_q = static_cast<uint8_t*>(a.out_fp8);
+  p.out_scale = static_cast<uint8_t*>(a.out_scale);
   p.lse = a.lse;
   p.user_o = a.partial_o;
   p.user_m = a.partial_m;
@@ -1726,19 +1767,24 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
   }
   // A handful of long sequences: 256 CTAs per sequence, the parts shared out among a CTA's eight warps, so that
   // the merge still fills the GPU. Batches: 32 CTAs per sequence, every thread walking the sequence's few parts.
+  const bool quant = p.out_q != nullptr;
+  const dim3 grid_few(static_cast<unsigned>(a.batch) * 16 * (kLatent / 32)), grid_many(static_cast<unsigned>(a.batch) * 16 * (kLatent / 256));
+  cudaError_t launched;
+  const char* what = "decode finalize launch";
   if (a.batch < 16) {
     if (ring != nullptr) {
-      return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<8, true>, dim3(static_cast<unsigned>(a.batch) * 16 * (kLatent / 32)),
-                                        dim3(256), 0, stream, p, n_ctas, *ring),
-                       "decode finalize + peer merge launch");
+      what = "decode finalize + peer merge launch";
+      launched = quant ? LaunchOverlapped(MlaFinalizeKernel<8, true, true>, grid_few, dim3(256), 0, stream, p, n_ctas, *ring)
+                       : LaunchOverlapped(MlaFinalizeKernel<8, true, false>, grid_few, dim3(256), 0, stream, p, n_ctas, *ring);
+    } else {
+      launched = quant ? LaunchOverlapped(MlaFinalizeKernel<8, false, true>, grid_few, dim3(256), 0, stream, p, n_ctas, PeerRing{})
+                       : LaunchOverlapped(MlaFinalizeKernel<8, false, false>, grid_few, dim3(256), 0, stream, p, n_ctas, PeerRing{});
     }
-    return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<8>, dim3(static_cast<unsigned>(a.batch) * 16 * (kLatent / 32)), dim3(256), 0,
-                                      stream, p, n_ctas, PeerRing{}),
-                     "decode finalize launch");
+  } else {
+    launched = quant ? LaunchOverlapped(MlaFinalizeKernel<1, false, true>, grid_many, dim3(128), 0, stream, p, n_ctas, PeerRing{})
+                     : LaunchOverlapped(MlaFinalizeKernel<1, false, false>, grid_many, dim3(128), 0, stream, p, n_ctas, PeerRing{});
   }
-  return CheckCuda(LaunchOverlapped(MlaFinalizeKernel<1>, dim3(static_cast<unsigned>(a.batch) * 16 * (kLatent / 256)), dim3(128), 0,
-                                    stream, p, n_ctas, PeerRing{}),
-                   "decode finalize launch");
+  return CheckCuda(launched, what);
 }
 
 }  // namespace b200kv

@@ -499,6 +499,25 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
                      "us_per_launch": t * 1e6, "achieved_gbs": sel_bytes / t * 1e-9,
                      "frac_of_measured_hbm": sel_bytes / t * 1e-9 / hbm_peak}
     del index, n_sel, rows_sel
+    # Attention with its output's MX quantisation (the reference's stage 10 behind stage 9): written by the merge
+    # kernel itself against a quantiser launch of its own behind the attention.
+    aq8 = torch.empty((BATCH, HEADS, LATENT), dtype=torch.uint8, device="cuda")
+    asc = torch.empty((BATCH, HEADS, LATENT // 32), dtype=torch.uint8, device="cuda")
+
+    def attend(i, fused_quant):
+        layer = i % LAYERS
+        b200kv.mla_decode(wl.q[layer], wl.views[layer], wl.table, wl.kv_len, BLOCK, SCALE, out=wl.out[layer],
+                          workspace=wl.ws, variant=b200kv.DECODE_TCGEN05, status=wl.status, stable_tables=True,
+                          quantised=(aq8, asc) if fused_quant else None)
+        if not fused_quant:
+            b200kv.mx_quant_e4m3(wl.out[layer].view(BATCH, HEADS * LATENT), aq8.view(BATCH, -1), asc.view(BATCH, -1))
+
+    for name, fused_quant in (("attention_quant_fused", True), ("attention_then_quant", False)):
+        t = timeit(lambda i: attend(i, fused_quant), 43)
+        res[name] = {"what": "decode + merge with the MX quantisation as the merge kernel's epilogue" if fused_quant
+                             else "decode + merge, then b200kv_mx_quant_e4m3 on the 32 output rows",
+                     "us_per_layer": t * 1e6}
+    del aq8, asc
     del src, out_l, out_r, trig, fused_src, key8, k_scale, lat_src, rope_src, flat_src, flat_dst
     return res
 

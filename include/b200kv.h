@@ -173,6 +173,16 @@ typedef struct b200kv_decode_args {
    */
   const int32_t* row_index;
   int64_t row_index_stride;
+  /*
+   * The output quantised as well (both null = no): out_fp8 [batch][heads][512] FP8 E4M3 and out_scale
+   * [batch][heads][16] E8M0, block-32 MX along a head's row, bit for bit what b200kv_mx_quant_e4m3 gives on `out`
+   * viewed as [batch][heads * 512]: the reference's stage after attention (attn_quant,
+   * src/pipeline/pipeline.cpp:250-258) as the epilogue of the kernel that writes `out`, instead of a launch of its
+   * own that reads `out` back. Needs `out` (not the partial_* form). The CUDA-core path runs the stand-alone
+   * quantiser behind the attention.
+   */
+  void* out_fp8;
+  void* out_scale;
 } b200kv_decode_args;
 #define B200KV_DECODE_STABLE_TABLES 1u
 

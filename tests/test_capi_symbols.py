@@ -31,7 +31,7 @@ def test_library_loads_and_exports_declared_symbols():
     assert len(names) >= 20, names
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, f"declared in include/*.h but not exported: {missing}"
-    assert b200kv.lib.b200kv_abi_version() == 4
+    assert b200kv.lib.b200kv_abi_version() == 5
 
 
 def test_host_side_argument_refusals():

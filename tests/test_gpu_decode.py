@@ -281,6 +281,49 @@ def test_gathered_rows_outside_the_pool_are_recorded_not_read():
     assert err.value.code == b200kv.ERR_INVALID
 
 
+@pytest.mark.parametrize("case", ["batch-split", "few-long", "many-short", "simt"])
+def test_output_quantised_by_the_launch_that_writes_it(case):
+    """out_fp8 / out_scale: the MX quantisation of the attention output as the epilogue of the merge kernel (and,
+    for sequences a single CTA covers, of the read-back of what the decode kernel wrote). Bit for bit the
+    stand-alone quantiser on `out`, which is bit for bit the oracle's. Sequences cut over several CTAs (the
+    32-CTAs-per-sequence merge), a few long ones (the 256-CTAs-per-sequence merge), many short ones with empty
+    ones among them (whole sequences per CTA), and the CUDA-core path (quantiser behind the attention)."""
+    from gpu_util import from_dev_bf16, status_ok, to_dev_bf16, to_dev_i32
+
+    bs = 64
+    kv_len = {"batch-split": np.array([2000 + 37 * i for i in range(20)], dtype=np.int32),
+              "few-long": np.array([9000, 1, 4097], dtype=np.int32),
+              "many-short": np.array([(i * 37) % 130 for i in range(200)], dtype=np.int32),
+              "simt": np.array([300, 0, 65, 1000], dtype=np.int32)}[case]
+    variant = b200kv.DECODE_SIMT if case == "simt" else b200kv.DECODE_TCGEN05
+    B = len(kv_len)
+    blocks = int(sum(scenarios.blocks_for(int(n), bs) for n in kv_len)) + 3
+    table = scenarios.fragmented_tables(kv_len, bs, blocks)
+    pool = to_dev_bf16(kvo.make_pool(blocks * bs))
+    q = to_dev_bf16(kvo.make_q(B, scale=2.0 / 24.0))
+    out = torch.full((B, 64, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+    q8 = torch.full((B, 64, 512), 0x55, dtype=torch.uint8, device="cuda")
+    sc = torch.full((B, 64, 16), 0x55, dtype=torch.uint8, device="cuda")
+    ws = torch.empty(b200kv.decode_workspace_bytes(B, 64, 0), dtype=torch.uint8, device="cuda")
+    status = b200kv.new_status()
+    b200kv.mla_decode(q, b200kv.pool_view(pool), to_dev_i32(table), to_dev_i32(kv_len), bs, 1.0 / 24.0, out=out,
+                      workspace=ws, variant=variant, status=status, quantised=(q8, sc))
+    status_ok(status)
+    want8 = torch.empty((B, 64 * 512), dtype=torch.uint8, device="cuda")
+    want_sc = torch.empty((B, 64 * 16), dtype=torch.uint8, device="cuda")
+    b200kv.mx_quant_e4m3(out.view(B, 64 * 512), want8, want_sc)
+    torch.cuda.synchronize()
+    assert torch.equal(q8.view(B, -1), want8), "FP8 codes differ from the stand-alone quantiser's"
+    assert torch.equal(sc.view(B, -1), want_sc), "scales differ from the stand-alone quantiser's"
+    o8, osc = kvo.mx_quant_e4m3(from_dev_bf16(out).reshape(B, -1))
+    assert np.array_equal(q8.view(B, -1).cpu().numpy(), o8) and np.array_equal(sc.view(B, -1).cpu().numpy(), osc)
+    with pytest.raises(b200kv.B200KVError) as err:  # the two buffers come together
+        args_q = (q8, None)
+        b200kv.mla_decode(q, b200kv.pool_view(pool), to_dev_i32(table), to_dev_i32(kv_len), bs, 1.0 / 24.0, out=out,
+                          workspace=ws, variant=variant, status=status, quantised=args_q)
+    assert err.value.code == b200kv.ERR_INVALID
+
+
 @pytest.mark.parametrize("seed", range(4))
 def test_random_batches_and_grid_sizes_match_the_reference(seed):
     """Many small random batches (lengths around the tile and block edges, empty sequences, one long sequence)
