@@ -329,11 +329,12 @@ extern "C" int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* st
                  b200kv_indexer_workspace_bytes(a.batch, a.max_kv_len));
     return B200KV_ERR_INVALID;
   }
-  const bool tc_ok = IndexerTcSupports(a.heads, a.block_size, a.key_stride, a.pool_rows);
+  const bool tc_ok = IndexerTcSupports(a.heads, a.block_size, a.key_stride, a.pool_rows) &&
+                     (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0;  // its TMA loads want a 16-byte aligned query
   if ((a.variant != B200KV_INDEXER_AUTO && a.variant != B200KV_INDEXER_EXACT && a.variant != B200KV_INDEXER_TCGEN05) ||
       (a.variant == B200KV_INDEXER_TCGEN05 && !tc_ok)) {
-    SetLastError("indexer_topk refused: variant %d (the tensor-core score kernel needs heads <= 64 and block_size %% 64 == 0; "
-                 "heads %d, block_size %d)", a.variant, a.heads, a.block_size);
+    SetLastError("indexer_topk refused: variant %d (the tensor-core score kernel needs heads <= 64, block_size %% 64 == 0 and a "
+                 "16-byte aligned q; heads %d, block_size %d)", a.variant, a.heads, a.block_size);
     return B200KV_ERR_INVALID;
   }
   const bool use_tc = tc_ok && a.variant != B200KV_INDEXER_EXACT;
