@@ -106,6 +106,7 @@ class IndexerArgs(Structure):
         ("block_size", c_int32), ("max_kv_len", c_int64), ("k", c_int32),
         ("index_out", c_void_p), ("n_selected_out", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
         ("variant", c_int32),
+        ("rows_out", c_void_p),
     ]
 
 
@@ -302,11 +303,12 @@ def gather(view: PoolView, block_table, kv_len, block_size: int, out_latent, out
 
 
 def indexer_topk(q_fp8, q_scale, weights, key_pool, k_scale, block_table, kv_len, block_size: int, max_kv_len: int,
-                 k: int, status=None, stream=None, variant: int = INDEXER_AUTO, scores_out=None):
+                 k: int, status=None, stream=None, variant: int = INDEXER_AUTO, scores_out=None, rows_out=None):
     """The k best-scoring tokens of every sequence: q_fp8 uint8 [B, H, 128], q_scale fp32 [B, H], weights bf16
     [B, H], key_pool uint8 [rows, >=128], k_scale fp32 [rows] -> (index int32 [B, k], n_selected int32 [B]).
     variant: INDEXER_EXACT for the bit-reproducible CUDA-core scores, INDEXER_TCGEN05 for the tensor cores.
-    scores_out: a list that receives the workspace as an fp32 [B, stride] tensor of the scores (for tests)."""
+    scores_out: a list that receives the workspace as an fp32 [B, stride] tensor of the scores (for tests).
+    rows_out int32 [B, k]: also receives the selection as pool rows (see resolve_rows)."""
     import torch
 
     batch, heads = int(q_fp8.shape[0]), int(q_fp8.shape[1])
@@ -320,6 +322,7 @@ def indexer_topk(q_fp8, q_scale, weights, key_pool, k_scale, block_table, kv_len
     a.batch, a.block_size, a.max_kv_len, a.k = batch, block_size, max_kv_len, k
     a.index_out, a.n_selected_out, a.workspace, a.workspace_bytes = _ptr(index), _ptr(n_sel), _ptr(ws), ws.numel()
     a.variant = variant
+    a.rows_out = _ptr(rows_out)
     check(lib.b200kv_indexer_topk(ctypes.byref(a), _stream_handle(stream), _ptr(status)))
     if scores_out is not None:
         scores_out.append(ws.view(torch.float32).view(batch, -1))

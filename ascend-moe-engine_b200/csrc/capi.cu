@@ -167,7 +167,7 @@ extern "C" int64_t b200kv_fault_clear(void) {
   return fired;
 }
 
-extern "C" int32_t b200kv_abi_version(void) { return 5; }
+extern "C" int32_t b200kv_abi_version(void) { return 6; }
 
 extern "C" size_t b200kv_mla_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t max_ctas) {
   if (batch <= 0 || heads <= 0) return 0;

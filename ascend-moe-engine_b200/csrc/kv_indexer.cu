@@ -136,7 +136,8 @@ constexpr int kHeldPerThread = 8;
 
 __global__ void __launch_bounds__(kSortThreads)
     IndexerSelectKernel(const float* scores, int64_t score_stride, const int32_t* kv_len, int32_t k, int32_t* index,
-                        int32_t* n_selected) {
+                        int32_t* n_selected, const int32_t* block_table, int64_t max_blocks, int32_t block_size,
+                        int64_t pool_rows, int32_t* rows_out, int32_t* status) {
   GridDependencyTrigger();
   __shared__ uint64_t keys[kMaxK];
   __shared__ uint32_t hist[kRadixBins];
@@ -152,7 +153,10 @@ __global__ void __launch_bounds__(kSortThreads)
   const int kept = len < k ? len : k;
   const float* row = scores + b * score_stride;
   if (tid == 0) n_selected[b] = kept;
-  for (int i = kept + tid; i < k; i += kSortThreads) index[b * k + i] = -1;
+  for (int i = kept + tid; i < k; i += kSortThreads) {
+    index[b * k + i] = -1;
+    if (rows_out != nullptr) rows_out[b * k + i] = -1;
+  }
   if (kept == 0) return;
   // High word of the key (ascending = better) of this thread's tokens tid, tid + 1024, ...: the first eight held.
   uint32_t held[kHeldPerThread];
@@ -282,7 +286,22 @@ __global__ void __launch_bounds__(kSortThreads)
     }
     __syncthreads();
   }
-  for (int i = tid; i < kept; i += kSortThreads) index[b * k + i] = static_cast<int32_t>(keys[i] & 0xffffffffu);
+  for (int i = tid; i < kept; i += kSortThreads) {
+    const int32_t t = static_cast<int32_t>(keys[i] & 0xffffffffu);
+    index[b * k + i] = t;
+    if (rows_out != nullptr) {  // the selection as pool rows, what ResolveRowsKernel would make of it
+      const int64_t column = t / block_size;
+      const int64_t block = column < max_blocks ? block_table[static_cast<int64_t>(b) * max_blocks + column] : -1;
+      const int64_t r = block * block_size + t % block_size;
+      int32_t row = -1;
+      if (block < 0 || r >= pool_rows) {
+        RecordError(status, B200KV_DEV_BAD_BLOCK, b, i, t);
+      } else {
+        row = static_cast<int32_t>(r);
+      }
+      rows_out[b * k + i] = row;
+    }
+  }
 }
 
 }  // namespace
@@ -369,6 +388,7 @@ extern "C" int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* st
   }
   return CheckCuda(LaunchOverlapped(IndexerSelectKernel, dim3(static_cast<unsigned>(a.batch)), dim3(kSortThreads), 0, s,
                                     static_cast<const float*>(p.scores), p.score_stride, a.kv_len, a.k, a.index_out,
-                                    a.n_selected_out),
+                                    a.n_selected_out, a.block_table, a.max_blocks, a.block_size, a.pool_rows, a.rows_out,
+                                    static_cast<int32_t*>(status)),
                    "indexer top-k launch");
 }

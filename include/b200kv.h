@@ -241,6 +241,13 @@ typedef struct b200kv_indexer_args {
   void* workspace;
   size_t workspace_bytes;
   int32_t variant; /* B200KV_INDEXER_AUTO, _EXACT or _TCGEN05 */
+  /*
+   * Optional: the selection as pool rows as well, device int32 [batch][k], rows_out[b][j] = block_table[b][t /
+   * block_size] * block_size + t % block_size for t = index_out[b][j] (-1 beyond n_selected_out[b]): what
+   * b200kv_resolve_rows makes of index_out with this block table, for a KV pool that shares the key cache's
+   * paging, written by the select kernel itself. Feed it to b200kv_decode_args.row_index.
+   */
+  int32_t* rows_out;
 } b200kv_indexer_args;
 #define B200KV_INDEXER_AUTO 0    /* tensor cores where the geometry allows, else CUDA cores            */
 #define B200KV_INDEXER_EXACT 1   /* CUDA cores: the fixed fp32 chains, reproducible bit for bit         */

@@ -31,7 +31,7 @@ def test_library_loads_and_exports_declared_symbols():
     assert len(names) >= 20, names
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, f"declared in include/*.h but not exported: {missing}"
-    assert b200kv.lib.b200kv_abi_version() == 5
+    assert b200kv.lib.b200kv_abi_version() == 6
 
 
 def test_host_side_argument_refusals():
@@ -107,7 +107,7 @@ def test_ctypes_structures_match_the_header_layout(tmp_path):
 
     cases = [("b200kv_pool_view", "pool_rows", b200kv.PoolView), ("b200kv_decode_args", "flags", b200kv.DecodeArgs),
              ("b200kv_decode_args", "row_index_stride", b200kv.DecodeArgs), ("b200kv_decode_args", "out_scale", b200kv.DecodeArgs),
-             ("b200kv_indexer_args", "variant", b200kv.IndexerArgs), ("b200kv_producer_args", "rstd_out", b200kv.ProducerArgs)]
+             ("b200kv_indexer_args", "rows_out", b200kv.IndexerArgs), ("b200kv_producer_args", "rstd_out", b200kv.ProducerArgs)]
     lines = "".join(f'  printf("%zu %zu\\n", sizeof({c}), offsetof({c}, {f}));\n' for c, f, _ in cases)
     src = tmp_path / "layout.c"
     src.write_text('#include <stddef.h>\n#include <stdio.h>\n#include "b200kv.h"\nint main(void) {\n' + lines +

@@ -339,10 +339,12 @@ def test_sparse_attention_pipeline_indexer_then_resolved_rows_then_decode():
     pool = kvo.make_pool(key.shape[0])                    # the latent KV pool shares the index cache's paging
     q = kvo.make_q(B)
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    rows_direct = torch.full((B, k), -9, dtype=torch.int32, device="cuda")
     index, n_sel = b200kv.indexer_topk(d(q8), d(qs), to_dev_bf16(w), d(key), d(ks), to_dev_i32(table), to_dev_i32(kv_len),
-                                       bs, max(lens), k)
+                                       bs, max(lens), k, rows_out=rows_direct)
     rows = b200kv.resolve_rows(to_dev_i32(table), bs, index, n_sel, pool.shape[0])
     torch.cuda.synchronize()
+    assert torch.equal(rows, rows_direct), "the select kernel's own rows differ from resolve_rows on its positions"
     exp_scores, _, exp_n = kvo.indexer_topk(q8, qs, w, key, ks, table, kv_len, bs, k)
     got_index = index.cpu().numpy()
     _check_selection_up_to_rounding(got_index, n_sel.cpu().numpy(), None, exp_scores, exp_n, kv_len, k, eps_rel=1e-6)
