@@ -498,6 +498,21 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
                                if variant == b200kv.DECODE_TCGEN05 else "MlaDecodeSimtKernel over single-row blocks",
                      "us_per_launch": t * 1e6, "achieved_gbs": sel_bytes / t * 1e-9,
                      "frac_of_measured_hbm": sel_bytes / t * 1e-9 / hbm_peak}
+    # The sparse step as the model would run it per layer: indexer (scores, selection, pool rows) then the gathered
+    # decode, two calls and four kernels.
+    rows_buf = torch.empty((BATCH, 512), dtype=torch.int32, device="cuda")
+
+    def sparse_layer(i):
+        layer = i % LAYERS
+        _, n_s = b200kv.indexer_topk(q8, q_scale, w_idx, key8[i % 8], k_scale[i % 8], wl.table, wl.kv_len, BLOCK, CONTEXT, 512,
+                                     status=wl.status, rows_out=rows_buf)
+        b200kv.mla_decode(wl.q[layer], wl.views[layer], None, n_s, BLOCK, SCALE, out=wl.out[layer], workspace=wl.ws,
+                          variant=b200kv.DECODE_TCGEN05, status=wl.status, row_index=rows_buf)
+
+    t = timeit(sparse_layer, 24)
+    res["sparse_layer_top512"] = {"what": "indexer (FP8 tcgen05 scores, select, rows) + attention over the 32 x 512 selected rows",
+                                  "us_per_layer": t * 1e6}
+    del rows_buf
     del index, n_sel, rows_sel
     # Attention with its output's MX quantisation (the reference's stage 10 behind stage 9): written by the merge
     # kernel itself against a quantiser launch of its own behind the attention.
