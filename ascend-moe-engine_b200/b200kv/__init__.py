@@ -325,7 +325,8 @@ def indexer_topk(q_fp8, q_scale, weights, key_pool, k_scale, block_table, kv_len
     a.rows_out = _ptr(rows_out)
     check(lib.b200kv_indexer_topk(ctypes.byref(a), _stream_handle(stream), _ptr(status)))
     if scores_out is not None:
-        scores_out.append(ws.view(torch.float32).view(batch, -1))
+        stride = (max_kv_len + 3) & ~3  # the scores lie first in the workspace, [batch][stride] fp32
+        scores_out.append(ws[: batch * stride * 4].view(torch.float32).view(batch, stride))
     return index, n_sel
 
 

@@ -133,68 +133,117 @@ __device__ __forceinline__ uint64_t SortKey(float score, uint32_t position) {
 // in registers, so sequences of up to 8,192 tokens are read from memory once; work is linear in the length.
 constexpr int kRadixBins = 2048;
 constexpr int kHeldPerThread = 8;
+constexpr int kSelectChunk = kHeldPerThread * kSortThreads;  // 8,192 tokens: what one CTA reads once and keeps
 
-__global__ void __launch_bounds__(kSortThreads)
-    IndexerSelectKernel(const float* scores, int64_t score_stride, const int32_t* kv_len, int32_t k, int32_t* index,
-                        int32_t* n_selected, const int32_t* block_table, int64_t max_blocks, int32_t block_size,
-                        int64_t pool_rows, int32_t* rows_out, int32_t* status) {
+// Long sequences in two levels, so that more than one CTA works on a sequence: the k best of every chunk of
+// 8,192 tokens (kLevel 1: one CTA a chunk, its keys written unsorted to the candidate area), then the k best
+// of the candidates (kLevel 2: one CTA a sequence, elements are the 64-bit keys themselves). The k best of the
+// whole are among the k best of each chunk, so the result is that of one level (kLevel 0), which sequences of
+// up to a chunk use.
+struct SelectParams {
+  const float* scores;
+  int64_t score_stride;
+  const int32_t* kv_len;
+  int32_t k;
+  int32_t chunks;           // per sequence (levels 1 and 2)
+  uint64_t* candidates;     // [batch][chunks][k] keys (levels 1 and 2)
+  int32_t* index;           // [batch][k]
+  int32_t* n_selected;      // [batch]
+  const int32_t* block_table;
+  int64_t max_blocks;
+  int32_t block_size;
+  int64_t pool_rows;
+  int32_t* rows_out;        // [batch][k] or null
+  int32_t* status;
+};
+
+template <int kLevel>
+__global__ void __launch_bounds__(kSortThreads) IndexerSelectKernel(SelectParams p) {
   GridDependencyTrigger();
   __shared__ uint64_t keys[kMaxK];
   __shared__ uint32_t hist[kRadixBins];
   __shared__ uint32_t warp_sum[32];
-  __shared__ uint32_t chosen[2][3];  // per pass parity: digit, tokens before it, tokens in it
+  __shared__ uint32_t chosen[2][3];  // per pass parity: digit, elements before it, elements in it
   __shared__ uint32_t n_taken;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < kRadixBins; i += kSortThreads) hist[i] = 0;
   if (tid == 0) n_taken = 0;
   GridDependencyWait();
-  const int b = blockIdx.x;
-  const int len = kv_len[b];
-  const int kept = len < k ? len : k;
-  const float* row = scores + b * score_stride;
-  if (tid == 0) n_selected[b] = kept;
-  for (int i = kept + tid; i < k; i += kSortThreads) {
-    index[b * k + i] = -1;
-    if (rows_out != nullptr) rows_out[b * k + i] = -1;
+  const int b = kLevel == 1 ? blockIdx.y : blockIdx.x;
+  const int chunk = kLevel == 1 ? blockIdx.x : 0;
+  const int len = p.kv_len[b];
+  const int k = p.k;
+  // The elements this CTA selects among, n of them, and how many it keeps.
+  const int first = kLevel == 1 ? chunk * kSelectChunk : 0;  // first token (levels 0 and 1)
+  int n;
+  if (kLevel == 0) {
+    n = len;
+  } else if (kLevel == 1) {
+    n = len - first < kSelectChunk ? len - first : kSelectChunk;
+    if (n < 0) n = 0;
+  } else {
+    n = p.chunks * k;
+  }
+  const int kept = kLevel == 2 ? (len < k ? len : k) : (n < k ? n : k);
+  const float* row = p.scores + b * p.score_stride + first;
+  const uint64_t* cand_in = p.candidates + static_cast<int64_t>(b) * p.chunks * k;
+  uint64_t* cand_out = p.candidates + (static_cast<int64_t>(b) * p.chunks + chunk) * k;
+  if (kLevel != 1) {
+    if (tid == 0) p.n_selected[b] = kept;
+    for (int i = kept + tid; i < k; i += kSortThreads) {
+      p.index[b * k + i] = -1;
+      if (p.rows_out != nullptr) p.rows_out[b * k + i] = -1;
+    }
+  } else {
+    for (int i = kept + tid; i < k; i += kSortThreads) cand_out[i] = ~0ull;  // empties sort last
   }
   if (kept == 0) return;
-  // High word of the key (ascending = better) of this thread's tokens tid, tid + 1024, ...: the first eight held.
+  // Levels 0 and 1: the high word of the key (ascending = better) of this thread's elements tid, tid + 1024, ...,
+  // the first eight held in registers. Level 2 reads its few keys from memory every time.
   uint32_t held[kHeldPerThread];
+  if (kLevel != 2) {
 #pragma unroll
-  for (int j = 0; j < kHeldPerThread; ++j) {
-    const int t = tid + j * kSortThreads;
-    held[j] = t < len ? static_cast<uint32_t>(SortKey(row[t], 0u) >> 32) : 0u;
+    for (int j = 0; j < kHeldPerThread; ++j) {
+      const int e = tid + j * kSortThreads;
+      held[j] = e < n ? static_cast<uint32_t>(SortKey(row[e], 0u) >> 32) : 0u;
+    }
   }
-  auto key_of = [&](int j, int t) -> uint64_t {  // j = t / 1024 (compile-time inside unrolled loops)
-    return (static_cast<uint64_t>(held[j]) << 32) | static_cast<uint32_t>(t);
+  auto held_key = [&](int j, int e) -> uint64_t {  // j = e / 1024 (compile-time inside unrolled loops)
+    return (static_cast<uint64_t>(held[j]) << 32) | static_cast<uint32_t>(first + e);
   };
+  auto read_key = [&](int e) -> uint64_t {
+    return kLevel == 2 ? cand_in[e] : SortKey(row[e], static_cast<uint32_t>(first + e));
+  };
+  constexpr int kFirstRead = kLevel == 2 ? 0 : kSelectChunk;  // elements from here on are read, not held
   __syncthreads();  // the histogram is clear
 
-  uint64_t bound = ~0ull;  // every token is wanted when the sequence has at most k
-  if (len > kept) {
+  uint64_t bound = ~0ull;  // every element is wanted when there are at most `kept`
+  if (n > kept) {
     uint64_t prefix = 0, mask = 0;
-    uint32_t rank = static_cast<uint32_t>(kept);  // 1-based rank, among the tokens that match `prefix`, of the key wanted
+    uint32_t rank = static_cast<uint32_t>(kept);  // 1-based rank, among the elements that match `prefix`, of the key wanted
     for (int pass = 0; pass < 6; ++pass) {
       const int shift = pass == 0 ? 53 : pass == 1 ? 42 : pass == 2 ? 32 : pass == 3 ? 21 : pass == 4 ? 10 : 0;
       const uint32_t digit_mask = (pass == 2 || pass == 5) ? 1023u : 2047u;
       // (Scores of one sequence are close together, so in the top digits most tokens fall into a few bins;
       // shared-memory atomics on one address still cost less here than finding a warp's equal digits first with
       // match.any, which was measured: 2.5 us more per launch.)
+      if (kLevel != 2) {
 #pragma unroll
-      for (int j = 0; j < kHeldPerThread; ++j) {
-        const int t = tid + j * kSortThreads;
-        if (t < len) {
-          const uint64_t key = key_of(j, t);
-          if ((key & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
+        for (int j = 0; j < kHeldPerThread; ++j) {
+          const int e = tid + j * kSortThreads;
+          if (e < n) {
+            const uint64_t key = held_key(j, e);
+            if ((key & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
+          }
         }
       }
-      for (int t = tid + kHeldPerThread * kSortThreads; t < len; t += kSortThreads) {
-        const uint64_t key = SortKey(row[t], static_cast<uint32_t>(t));
+      for (int e = tid + kFirstRead; e < n; e += kSortThreads) {
+        const uint64_t key = read_key(e);
         if ((key & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
       }
       __syncthreads();
       // Thread t owns bins 2t and 2t + 1 (and clears them for the next pass); a scan over the threads gives the
-      // tokens before its bins: shuffles inside the warp, and every warp adds up the warps before it for itself.
+      // elements before its bins: shuffles inside the warp, and every warp adds up the warps before it for itself.
       const uint32_t c0 = hist[2 * tid], c1 = hist[2 * tid + 1];
       hist[2 * tid] = 0;
       hist[2 * tid + 1] = 0;
@@ -231,25 +280,31 @@ __global__ void __launch_bounds__(kSortThreads)
   auto take = [&](bool wanted, uint64_t key) {  // every lane of the warp calls
     const unsigned takers = __ballot_sync(0xffffffffu, wanted);
     if (takers == 0u) return;
-    uint32_t first = 0;
-    if (lane == __ffs(takers) - 1) first = atomicAdd(&n_taken, static_cast<uint32_t>(__popc(takers)));
-    first = __shfl_sync(0xffffffffu, first, __ffs(takers) - 1);
-    const uint32_t slot = first + __popc(takers & ((1u << lane) - 1u));
+    uint32_t slot0 = 0;
+    if (lane == __ffs(takers) - 1) slot0 = atomicAdd(&n_taken, static_cast<uint32_t>(__popc(takers)));
+    slot0 = __shfl_sync(0xffffffffu, slot0, __ffs(takers) - 1);
+    const uint32_t slot = slot0 + __popc(takers & ((1u << lane) - 1u));
     if (wanted && slot < static_cast<uint32_t>(kMaxK)) keys[slot] = key;
   };
+  if (kLevel != 2) {
 #pragma unroll
-  for (int j = 0; j < kHeldPerThread; ++j) {
-    const int t = tid + j * kSortThreads;
-    if (warp * 32 + j * kSortThreads >= len) break;
-    const uint64_t key = key_of(j, t);
-    take(t < len && key <= bound, key);
+    for (int j = 0; j < kHeldPerThread; ++j) {
+      const int e = tid + j * kSortThreads;
+      if (warp * 32 + j * kSortThreads >= n) break;
+      const uint64_t key = held_key(j, e);
+      take(e < n && key <= bound, key);
+    }
   }
-  for (int t0 = warp * 32 + kHeldPerThread * kSortThreads; t0 < len; t0 += kSortThreads) {
-    const int t = t0 + lane;
-    const uint64_t key = t < len ? SortKey(row[t], static_cast<uint32_t>(t)) : ~0ull;
-    take(t < len && key <= bound, key);
+  for (int e0 = warp * 32 + kFirstRead; e0 < n; e0 += kSortThreads) {
+    const int e = e0 + lane;
+    const uint64_t key = e < n ? read_key(e) : ~0ull;
+    take(e < n && key <= bound, key);
   }
   __syncthreads();
+  if (kLevel == 1) {  // the chunk's best, in any order: the next level selects and sorts
+    for (int i = tid; i < kept; i += kSortThreads) cand_out[i] = keys[i];
+    return;
+  }
   // The collected keys in order: a bitonic sort, ascending, of the list padded to a power of two. Element e
   // belongs to thread e % 1024 (two elements a thread when k > 1024). Steps whose partner is less than 32 away
   // stay inside a warp and run on registers with shuffles, a whole run of them between two barriers; only the
@@ -288,18 +343,18 @@ __global__ void __launch_bounds__(kSortThreads)
   }
   for (int i = tid; i < kept; i += kSortThreads) {
     const int32_t t = static_cast<int32_t>(keys[i] & 0xffffffffu);
-    index[b * k + i] = t;
-    if (rows_out != nullptr) {  // the selection as pool rows, what ResolveRowsKernel would make of it
-      const int64_t column = t / block_size;
-      const int64_t block = column < max_blocks ? block_table[static_cast<int64_t>(b) * max_blocks + column] : -1;
-      const int64_t r = block * block_size + t % block_size;
-      int32_t row = -1;
-      if (block < 0 || r >= pool_rows) {
-        RecordError(status, B200KV_DEV_BAD_BLOCK, b, i, t);
+    p.index[b * k + i] = t;
+    if (p.rows_out != nullptr) {  // the selection as pool rows, what ResolveRowsKernel would make of it
+      const int64_t column = t / p.block_size;
+      const int64_t block = column < p.max_blocks ? p.block_table[static_cast<int64_t>(b) * p.max_blocks + column] : -1;
+      const int64_t r = block * p.block_size + t % p.block_size;
+      int32_t out_row = -1;
+      if (block < 0 || r >= p.pool_rows) {
+        RecordError(p.status, B200KV_DEV_BAD_BLOCK, b, i, t);
       } else {
-        row = static_cast<int32_t>(r);
+        out_row = static_cast<int32_t>(r);
       }
-      rows_out[b * k + i] = row;
+      p.rows_out[b * k + i] = out_row;
     }
   }
 }
@@ -317,9 +372,20 @@ int32_t LaunchIndexerScoreTc(const void* q, const float* q_scale, const void* we
 
 using namespace b200kv;
 
+namespace {
+// Scores [batch][stride] fp32, then (sequences longer than one chunk) the candidate keys [batch][chunks][kMaxK].
+int64_t ScoreStrideOf(int64_t max_kv_len) { return (max_kv_len + 3) & ~3ll; }
+int64_t ChunksOf(int64_t max_kv_len) { return (max_kv_len + kSelectChunk - 1) / kSelectChunk; }
+size_t ScoreBytesOf(int32_t batch, int64_t max_kv_len) {
+  return (static_cast<size_t>(batch) * static_cast<size_t>(ScoreStrideOf(max_kv_len)) * sizeof(float) + 15) & ~static_cast<size_t>(15);
+}
+}  // namespace
+
 extern "C" size_t b200kv_indexer_workspace_bytes(int32_t batch, int64_t max_kv_len) {
   if (batch <= 0 || max_kv_len <= 0) return 0;
-  return static_cast<size_t>(batch) * static_cast<size_t>((max_kv_len + 3) & ~3ll) * sizeof(float);
+  const int64_t chunks = ChunksOf(max_kv_len);
+  return ScoreBytesOf(batch, max_kv_len) +
+         (chunks > 1 ? static_cast<size_t>(batch) * static_cast<size_t>(chunks) * kMaxK * sizeof(uint64_t) : 0);
 }
 
 extern "C" int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* stream, b200kv_status_word* status) {
@@ -371,7 +437,7 @@ extern "C" int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* st
   p.kv_len = a.kv_len;
   p.block_size = a.block_size;
   p.scores = static_cast<float*>(a.workspace);
-  p.score_stride = (a.max_kv_len + 3) & ~3ll;
+  p.score_stride = ScoreStrideOf(a.max_kv_len);
   p.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (use_tc) {
@@ -386,9 +452,30 @@ extern "C" int32_t b200kv_indexer_topk(const b200kv_indexer_args* args, void* st
       return rc;
     }
   }
-  return CheckCuda(LaunchOverlapped(IndexerSelectKernel, dim3(static_cast<unsigned>(a.batch)), dim3(kSortThreads), 0, s,
-                                    static_cast<const float*>(p.scores), p.score_stride, a.kv_len, a.k, a.index_out,
-                                    a.n_selected_out, a.block_table, a.max_blocks, a.block_size, a.pool_rows, a.rows_out,
-                                    static_cast<int32_t*>(status)),
-                   "indexer top-k launch");
+  SelectParams sp{};
+  sp.scores = p.scores;
+  sp.score_stride = p.score_stride;
+  sp.kv_len = a.kv_len;
+  sp.k = a.k;
+  sp.chunks = static_cast<int32_t>(ChunksOf(a.max_kv_len));
+  sp.candidates = reinterpret_cast<uint64_t*>(static_cast<char*>(a.workspace) + ScoreBytesOf(a.batch, a.max_kv_len));
+  sp.index = a.index_out;
+  sp.n_selected = a.n_selected_out;
+  sp.block_table = a.block_table;
+  sp.max_blocks = a.max_blocks;
+  sp.block_size = a.block_size;
+  sp.pool_rows = a.pool_rows;
+  sp.rows_out = a.rows_out;
+  sp.status = static_cast<int32_t*>(status);
+  if (sp.chunks <= 1) {
+    return CheckCuda(LaunchOverlapped(IndexerSelectKernel<0>, dim3(static_cast<unsigned>(a.batch)), dim3(kSortThreads), 0, s, sp),
+                     "indexer top-k launch");
+  }
+  if (int32_t rc = CheckCuda(LaunchOverlapped(IndexerSelectKernel<1>, dim3(static_cast<unsigned>(sp.chunks), static_cast<unsigned>(a.batch)),
+                                              dim3(kSortThreads), 0, s, sp),
+                             "indexer top-k (chunks) launch")) {
+    return rc;
+  }
+  return CheckCuda(LaunchOverlapped(IndexerSelectKernel<2>, dim3(static_cast<unsigned>(a.batch)), dim3(kSortThreads), 0, s, sp),
+                   "indexer top-k (candidates) launch");
 }

@@ -1765,13 +1765,16 @@ int32_t LaunchMlaDecodeTc(const b200kv_decode_args& a, int32_t n_ctas, cudaStrea
                              "tcgen05 decode launch")) {
     return rc;
   }
-  // A handful of long sequences: 256 CTAs per sequence, the parts shared out among a CTA's eight warps, so that
-  // the merge still fills the GPU. Batches: 32 CTAs per sequence, every thread walking the sequence's few parts.
+  // One or two long sequences: 256 CTAs per sequence, the parts shared out among a CTA's eight warps, so that
+  // the merge still fills the GPU. Batches: 32 CTAs per sequence, every thread walking the sequence's parts.
   const bool quant = p.out_q != nullptr;
   const dim3 grid_few(static_cast<unsigned>(a.batch) * 16 * (kLatent / 32)), grid_many(static_cast<unsigned>(a.batch) * 16 * (kLatent / 256));
   cudaError_t launched;
   const char* what = "decode finalize launch";
-  if (a.batch < 16) {
+  // (The 256-CTA form runs two CTAs per SM: one sequence is one wave, two are two, and from three on the
+  // 32-CTA form, whose threads walk a sequence's parts eight at a time, is the shorter one. The exchange across
+  // GPUs exists in the 256-CTA form only.)
+  if (a.batch < 3 || ring != nullptr) {
     if (ring != nullptr) {
       what = "decode finalize + peer merge launch";
       launched = quant ? LaunchOverlapped(MlaFinalizeKernel<8, true, true>, grid_few, dim3(256), 0, stream, p, n_ctas, *ring)

@@ -513,6 +513,35 @@ def measure_move_kernels(torch, b200kv, wl: Workload, hbm_peak: float, use_graph
     res["sparse_layer_top512"] = {"what": "indexer (FP8 tcgen05 scores, select, rows) + attention over the 32 x 512 selected rows",
                                   "us_per_layer": t * 1e6}
     del rows_buf
+    # Where the selection pays: 8 sequences of 32,768 tokens. Dense attention reads 302 MB a layer; the sparse layer
+    # reads 34.6 MB of index keys and 8 x 512 rows.
+    b2, ctx2 = 8, 32768
+    rows2 = b2 * ctx2
+    pool2 = torch.empty((2, rows2, ROW), dtype=torch.bfloat16, device="cuda")
+    b200kv.fill_normal_bf16(pool2, SEED, 21)
+    table2 = torch.randperm(rows2 // BLOCK, device="cuda").to(torch.int32).view(b2, ctx2 // BLOCK).contiguous()
+    lens2 = torch.full((b2,), ctx2, dtype=torch.int32, device="cuda")
+    key2 = torch.randint(0, 0x50, (2, rows2, 128), dtype=torch.uint8, device="cuda")
+    ks2 = torch.rand((2, rows2), dtype=torch.float32, device="cuda") * 0.1 + 0.01
+    ws2 = torch.empty(b200kv.decode_workspace_bytes(b2), dtype=torch.uint8, device="cuda")
+    out2 = torch.empty((b2, HEADS, LATENT), dtype=torch.bfloat16, device="cuda")
+    rows_buf2 = torch.empty((b2, 512), dtype=torch.int32, device="cuda")
+    views2 = [b200kv.pool_view(pool2[i]) for i in range(2)]
+
+    def dense_long(i):
+        b200kv.mla_decode(wl.q[i % LAYERS][:b2], views2[i % 2], table2, lens2, BLOCK, SCALE, out=out2, workspace=ws2,
+                          variant=b200kv.DECODE_TCGEN05, status=wl.status, stable_tables=True)
+
+    def sparse_long(i):
+        _, n_s = b200kv.indexer_topk(q8[:b2], q_scale[:b2], w_idx[:b2], key2[i % 2], ks2[i % 2], table2, lens2, BLOCK, ctx2, 512,
+                                     status=wl.status, rows_out=rows_buf2)
+        b200kv.mla_decode(wl.q[i % LAYERS][:b2], views2[i % 2], None, n_s, BLOCK, SCALE, out=out2, workspace=ws2,
+                          variant=b200kv.DECODE_TCGEN05, status=wl.status, row_index=rows_buf2)
+
+    t_dense, t_sparse = timeit(dense_long, 8), timeit(sparse_long, 8)
+    res["long_context_8x32k"] = {"dense_attention_us_per_layer": t_dense * 1e6, "sparse_layer_top512_us_per_layer": t_sparse * 1e6,
+                                 "dense_bytes": rows2 * ROW * 2, "sparse_bytes": rows2 * 136 + b2 * 512 * ROW * 2}
+    del pool2, key2, ks2, ws2, out2, rows_buf2, table2, lens2, views2
     del index, n_sel, rows_sel
     # Attention with its output's MX quantisation (the reference's stage 10 behind stage 9): written by the merge
     # kernel itself against a quantiser launch of its own behind the attention.
