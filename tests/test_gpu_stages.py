@@ -235,8 +235,12 @@ def _indexer_inputs(B, H, lens, bs, seed):
     return test_stage_oracle._indexer_case(B, H, lens, bs, seed)
 
 
-@pytest.mark.parametrize("lens,k", [([4096, 300, 5000, 17, 0, 9000], 512), ([70, 64], 2048), ([12000], 100)])
+@pytest.mark.parametrize("lens,k", [([4096, 300, 5000, 17, 0, 9000], 512), ([70, 64], 2048), ([12000], 100),
+                                    ([9000, 8193, 8192, 40000], 2048)])
 def test_indexer_selection_matches_oracle_bit_for_bit(lens, k):
+    """Exact scores: the selection equals the oracle's, position for position. Sequences of up to 8,192 tokens are
+    selected by one CTA, longer ones in two levels (the best of every 8,192-token chunk, then the best of those):
+    lengths on both sides of the chunk edge, a chunk that holds fewer tokens than k, five chunks."""
     B, H, bs = len(lens), 64, 64
     q, qs, w, key, ks, table, kv_len = _indexer_inputs(B, H, lens, bs, seed=11 + k)
     # ties on purpose: two tokens with identical keys and scales
