@@ -20,7 +20,7 @@ OUT = os.path.join(HERE, "b200kv", "libb200kv.so")
 
 SOURCES = [
     "capi.cu",
-    "kv_move.cu",
+    "kv_move.cu", "kv_gather_tma.cu",
     "mla_decode_simt.cu",
     "mla_decode_tc.cu",
     "kv_block_pool.cpp",

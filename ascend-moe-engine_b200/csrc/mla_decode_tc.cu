@@ -1662,6 +1662,30 @@ int32_t EncodeByteRowMap(const void* base, int64_t stride_bytes, int64_t rows, i
   return B200KV_OK;
 }
 
+// Row-major [rows][width] bf16 view, row stride `stride_bytes`; box = box_cols x box_rows, no swizzle (the box
+// lands in shared memory as plain rows of box_cols elements). For kernels that only move rows.
+int32_t EncodePlainBf16Map(const void* base, int64_t stride_bytes, int64_t rows, int32_t width, int32_t box_cols,
+                           int32_t box_rows, CUtensorMap* out) {
+  EncodeTiledFn encode = ResolveEncodeTiled();
+  if (encode == nullptr) {
+    SetLastError("cuTensorMapEncodeTiled could not be resolved from the CUDA driver");
+    return B200KV_ERR_RUNTIME;
+  }
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(stride_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    SetLastError("cuTensorMapEncodeTiled (plain rows) failed with CUresult %d (base %p, stride %lld, rows %lld, box %d x %d)",
+                 static_cast<int>(rc), base, static_cast<long long>(stride_bytes), static_cast<long long>(rows), box_cols, box_rows);
+    return B200KV_ERR_RUNTIME;
+  }
+  return B200KV_OK;
+}
+
 size_t TcWorkspaceBytes(int32_t n_ctas) {
   return static_cast<size_t>(n_ctas) * 2 * kHeads * (kLatent + 2) * sizeof(float);
 }

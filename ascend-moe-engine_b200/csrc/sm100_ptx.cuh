@@ -98,6 +98,20 @@ __device__ __forceinline__ void TmaPrefetchL2_2D(const CUtensorMap* map, int32_t
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 
+// Tiled 2D store, this CTA's shared memory -> global, as part of the calling thread's current bulk group; the
+// group is closed with BulkCommitGroup and BulkWaitGroupRead<N> returns when all but the N latest groups of the
+// thread have finished reading their shared memory (which may then be overwritten).
+__device__ __forceinline__ void TmaStore2D(const CUtensorMap* map, int32_t x, int32_t y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
+               "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void BulkCommitGroup() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void BulkWaitGroupRead() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+
 // L2 eviction-priority descriptors for the cache-hinted forms below.
 __device__ __forceinline__ uint64_t L2PolicyEvictLast() {
   uint64_t policy;
