@@ -13,7 +13,10 @@
 // out in boxes of 32, 16, 8, 4, 2 and 1 rows (one tensor map of the outputs per box height), each from its offset
 // in the stage. One thread per CTA drives three stages: the loads of tile i + 2 are issued before the stores
 // of tile i, and a stage is reused once the bulk group of its stores has finished reading it. Persistent CTAs,
-// one per SM (three stages of 72 KB), tiles dealt out round-robin over the flat list of all sequences' tiles.
+// one per SM (three stages of 72 KB), tiles dealt out round-robin over the flat list of all sequences' tiles:
+// the warp first lays the sequences' running tile counts into shared memory (a scan over the lengths), and the
+// driving thread finds the sequence of its k-th tile by bisection there. (A first version walked the sequences
+// one by one in that thread: 0.6 us a sequence, 164 us for 256 short sequences.)
 // Bit-exact by construction (bytes are copied); bound by HBM: 1,152 bytes read and written per row.
 #include <cuda.h>
 
@@ -34,7 +37,8 @@ constexpr int kRopeBoxBytes = kTileRows * B200KV_ROPE_DIM * 2;    // 8 KB
 constexpr int kStageBytes = 2 * kLatentBoxBytes + kRopeBoxBytes;  // 72 KB
 constexpr int kStages = 3;
 constexpr int kHeights = 7;  // store boxes of 64, 32, 16, 8, 4, 2, 1 rows
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 128;
+constexpr int kMaxBatch = 2048;  // sequences whose running tile counts fit beside the stages
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 128 + (kMaxBatch + 1) * 4;
 
 struct GatherMaps {
   CUtensorMap src_latent, src_rope;                  // the pool, boxes of 64 rows
@@ -57,44 +61,59 @@ __global__ void __launch_bounds__(32, 1) GatherTmaKernel(const __grid_constant__
   const uint32_t raw = ptx::SmemAddr(smem_raw);
   const uint32_t stage0 = (raw + 1023u) & ~1023u;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (stage0 - raw) + kStages * kStageBytes);
+  int* first_tile = reinterpret_cast<int*>(full + kStages);  // [batch + 1]: tiles of the sequences before b
   GridDependencyTrigger();
-  if (threadIdx.x != 0) return;  // one thread drives the copies; the rest of the warp has nothing to do
+  GridDependencyWait();
+  {
+    const int lane = threadIdx.x;
+    int running = 0;
+    for (int c = 0; c < p.batch; c += 32) {
+      const int i = c + lane;
+      const int len = i < p.batch ? p.kv_len[i] : 0;
+      int incl = len > 0 ? (len + kTileRows - 1) / kTileRows : 0;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += up;
+      }
+      if (i < p.batch) first_tile[i + 1] = running + incl;
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) first_tile[0] = 0;
+    __syncwarp();
+  }
+  if (threadIdx.x != 0) return;  // one thread drives the copies; the rest of the warp has nothing more to do
   for (int s = 0; s < kStages; ++s) ptx::MbarInit(ptx::SmemAddr(&full[s]), 1);
   ptx::FenceBarrierInit();
   ptx::PrefetchTensorMap(&maps.src_latent);
   ptx::PrefetchTensorMap(&maps.src_rope);
-  GridDependencyWait();
 
-  // This CTA's tiles: number cta, cta + G, ... of the flat list (sequence after sequence). The walk below is
-  // done twice in step, once for the loads (running kStages - 1 tiles ahead) and once for the stores.
+  // This CTA's tiles: number cta, cta + G, ... of the flat list (sequence after sequence). The list is walked
+  // twice in step, once for the loads (running kStages - 1 tiles ahead) and once for the stores.
   struct Walk {
-    int b, j, tiles;       // sequence, next tile of it for this CTA, its tile count
-    long long before;      // tiles of the sequences before b
+    int flat;  // the next tile of this CTA in the flat list
+    int b;     // a sequence at or before that tile's (the bisection starts there: tiles only move forward)
   };
   const int G = gridDim.x, cta = blockIdx.x;
+  const int total_tiles = first_tile[p.batch];
   auto start = [&](Walk* w) {
-    w->b = -1;
-    w->j = 0;
-    w->tiles = 0;
-    w->before = 0;
+    w->flat = cta;
+    w->b = 0;
   };
-  // Advances to this CTA's next tile; false at the end.
+  // This CTA's next tile; false at the end.
   auto next = [&](Walk* w, int* seq, int* tile, int* rows) -> bool {
-    for (;;) {
-      if (w->b >= 0 && w->j < w->tiles) {
-        const int len = p.kv_len[w->b];
-        *seq = w->b;
-        *tile = w->j;
-        *rows = min(kTileRows, len - w->j * kTileRows);
-        w->j += G;
-        return true;
-      }
-      if (w->b >= 0) w->before += w->tiles;
-      if (++w->b >= p.batch) return false;
-      const int len = p.kv_len[w->b];
-      w->tiles = len > 0 ? (len + kTileRows - 1) / kTileRows : 0;
-      w->j = static_cast<int>(((cta - w->before) % G + G) % G);
+    if (w->flat >= total_tiles) return false;
+    int lo = w->b, hi = p.batch - 1;  // the last sequence whose first tile is at or before flat
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (first_tile[mid] <= w->flat) lo = mid; else hi = mid - 1;
     }
+    w->b = lo;
+    *seq = lo;
+    *tile = w->flat - first_tile[lo];
+    *rows = min(kTileRows, p.kv_len[lo] - *tile * kTileRows);
+    w->flat += G;
+    return true;
   };
   bool good[kStages];  // whether the tile in a stage came through a usable table entry: a bad one is not stored
   auto issue_load = [&](int seq, int tile, int i) {
@@ -169,9 +188,9 @@ __global__ void __launch_bounds__(32, 1) GatherTmaKernel(const __grid_constant__
 
 }  // namespace
 
-bool GatherTmaSupports(const b200kv_pool_view& pool, int64_t block_size, int64_t out_latent_stride, int64_t out_rope_stride,
-                       int64_t total_rows) {
-  return block_size % kTileRows == 0 && pool.pool_rows <= INT32_MAX && total_rows <= INT32_MAX && pool.pool_rows >= kTileRows &&
+bool GatherTmaSupports(const b200kv_pool_view& pool, int64_t batch, int64_t block_size, int64_t out_latent_stride,
+                       int64_t out_rope_stride, int64_t total_rows) {
+  return batch <= kMaxBatch && block_size % kTileRows == 0 && pool.pool_rows <= INT32_MAX && total_rows <= INT32_MAX && pool.pool_rows >= kTileRows &&
          out_latent_stride % 8 == 0 && out_rope_stride % 8 == 0 && pool.latent_row_stride % 8 == 0 && pool.rope_row_stride % 8 == 0 &&
          (reinterpret_cast<uintptr_t>(pool.latent) & 15u) == 0 && (reinterpret_cast<uintptr_t>(pool.rope) & 15u) == 0;
 }

@@ -276,8 +276,8 @@ int32_t ValidatePoolView(const b200kv_pool_view* pool) { return CheckPool(pool);
 }  // namespace b200kv
 
 namespace b200kv {
-bool GatherTmaSupports(const b200kv_pool_view& pool, int64_t block_size, int64_t out_latent_stride, int64_t out_rope_stride,
-                       int64_t total_rows);
+bool GatherTmaSupports(const b200kv_pool_view& pool, int64_t batch, int64_t block_size, int64_t out_latent_stride,
+                       int64_t out_rope_stride, int64_t total_rows);
 int32_t LaunchGatherTma(const b200kv_pool_view& pool, const int32_t* block_table, int64_t max_blocks, const int32_t* kv_len,
                         int32_t batch, int32_t block_size, void* out_latent, int64_t out_latent_stride, void* out_rope,
                         int64_t out_rope_stride, const int64_t* out_row_offsets, int64_t total_rows, cudaStream_t stream,
@@ -337,7 +337,7 @@ extern "C" int32_t b200kv_gather(const b200kv_pool_view* pool, const int32_t* bl
   }
   // Blocks of a multiple of 64 tokens go through shared memory by TMA, 64 rows at a time (kv_gather_tma.cu); other
   // geometries row by row through registers.
-  if (GatherTmaSupports(*pool, block_size, out_latent_stride, out_rope_stride, total_rows)) {
+  if (GatherTmaSupports(*pool, batch, block_size, out_latent_stride, out_rope_stride, total_rows)) {
     return LaunchGatherTma(*pool, block_table, max_blocks, kv_len, static_cast<int32_t>(batch), static_cast<int32_t>(block_size),
                            out_latent, out_latent_stride, out_rope, out_rope_stride, out_row_offsets, total_rows,
                            static_cast<cudaStream_t>(stream), status);
