@@ -126,6 +126,11 @@ def test_append_zero_tokens_is_a_no_op():
     (128, [129, 1], False),
     (64, [1, 63, 64, 65, 200, 0, 7], True),
     (64, [4097] * 4, True),
+    (64, [1], False),                       # outputs smaller than a tile
+    (64, [0, 3], True),
+    (192, [500, 191, 193], True),           # blocks of three tiles
+    (16, [100, 5], True),                   # blocks smaller than a tile: the register kernel
+    (64, [(37 * i) % 150 for i in range(300)], True),   # many short sequences
 ])
 def test_gather_bit_exact(bs, kv_len, fragmented):
     kv_len = np.asarray(kv_len, dtype=np.int32)
