@@ -132,6 +132,7 @@ __device__ __forceinline__ uint64_t SortKey(float score, uint32_t position) {
 // A thread keeps the score images of its first eight tokens
 // in registers, so sequences of up to 8,192 tokens are read from memory once; work is linear in the length.
 constexpr int kRadixBins = 2048;
+constexpr int kBinsPerThread = kRadixBins / kSortThreads;
 constexpr int kHeldPerThread = 8;
 constexpr int kSelectChunk = kHeldPerThread * kSortThreads;  // 8,192 tokens: what one CTA reads once and keeps
 
@@ -242,12 +243,16 @@ __global__ void __launch_bounds__(kSortThreads) IndexerSelectKernel(SelectParams
         if ((key & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
       }
       __syncthreads();
-      // Thread t owns bins 2t and 2t + 1 (and clears them for the next pass); a scan over the threads gives the
+      // A thread owns a few consecutive bins (and clears them for the next pass); a scan over the threads gives the
       // elements before its bins: shuffles inside the warp, and every warp adds up the warps before it for itself.
-      const uint32_t c0 = hist[2 * tid], c1 = hist[2 * tid + 1];
-      hist[2 * tid] = 0;
-      hist[2 * tid + 1] = 0;
-      uint32_t incl = c0 + c1;
+      uint32_t count[kBinsPerThread], mine = 0;
+#pragma unroll
+      for (int i = 0; i < kBinsPerThread; ++i) {
+        count[i] = hist[kBinsPerThread * tid + i];
+        hist[kBinsPerThread * tid + i] = 0;
+        mine += count[i];
+      }
+      uint32_t incl = mine;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
         const uint32_t up = __shfl_up_sync(0xffffffffu, incl, off);
@@ -258,12 +263,17 @@ __global__ void __launch_bounds__(kSortThreads) IndexerSelectKernel(SelectParams
       uint32_t earlier = lane < warp ? warp_sum[lane] : 0u;
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) earlier += __shfl_xor_sync(0xffffffffu, earlier, off);
-      const uint32_t before = earlier + incl - (c0 + c1);
-      if (before < rank && rank <= before + c0 + c1) {  // one thread: the rank falls in its bins
-        const bool in_first = rank <= before + c0;
-        chosen[pass & 1][0] = 2 * tid + (in_first ? 0 : 1);
-        chosen[pass & 1][1] = in_first ? before : before + c0;
-        chosen[pass & 1][2] = in_first ? c0 : c1;
+      uint32_t before = earlier + incl - mine;
+      if (before < rank && rank <= before + mine) {  // one thread: the rank falls in its bins
+#pragma unroll
+        for (int i = 0; i < kBinsPerThread; ++i) {
+          if (before < rank && rank <= before + count[i]) {
+            chosen[pass & 1][0] = kBinsPerThread * tid + i;
+            chosen[pass & 1][1] = before;
+            chosen[pass & 1][2] = count[i];
+          }
+          before += count[i];
+        }
       }
       __syncthreads();
       prefix |= static_cast<uint64_t>(chosen[pass & 1][0]) << shift;
